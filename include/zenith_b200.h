@@ -1,0 +1,158 @@
+/*
+ * zenith_b200 — C ABI of the B200 (sm_100a) transformer-encoder kernels.
+ *
+ * Conventions (all entry points):
+ *   - plain C types only; every pointer is a DEVICE pointer unless the name ends in _host;
+ *   - buffers are caller-owned; nothing here allocates device memory and nothing synchronises
+ *     the device (the two zen_device_status_* calls excepted);
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream);
+ *   - the return value is 0 (ZEN_OK) or a ZEN_ERR_* code; nothing throws, nothing prints;
+ *   - a kernel-side wait that ran out (ZEN_ERR_TIMEOUT) is reported asynchronously through the
+ *     device status word, read with zen_device_status_read().
+ *
+ * Each declaration names the interface of the reference project (vibeswithkk/ZENITH, paths
+ * relative to that project) that it replaces.
+ */
+#ifndef ZENITH_B200_H_
+#define ZENITH_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ZEN_VERSION 100
+
+/* status codes */
+#define ZEN_OK 0
+#define ZEN_ERR_INVALID_ARG 1   /* null pointer, non-positive extent, bad enum */
+#define ZEN_ERR_UNSUPPORTED 2   /* shape / alignment / stride the kernels do not cover */
+#define ZEN_ERR_LAUNCH 3        /* cudaGetLastError() after the launch was not cudaSuccess */
+#define ZEN_ERR_TIMEOUT 4       /* a bounded device-side wait ran out (device status word) */
+#define ZEN_ERR_DRIVER 5        /* tensor-map encoding entry point unavailable or failed */
+#define ZEN_ERR_TOO_LARGE 6     /* request exceeds a fixed capacity of the entry point */
+
+/* element types of GEMM outputs */
+#define ZEN_DT_S32 0
+#define ZEN_DT_F32 1
+#define ZEN_DT_F16 2
+#define ZEN_DT_S8 3
+
+/* activation fused into a GEMM epilogue */
+#define ZEN_ACT_NONE 0
+#define ZEN_ACT_GELU 1 /* tanh form: 0.5 x (1 + tanh(0.7978845608 (x + 0.044715 x^3))) */
+#define ZEN_ACT_RELU 2
+
+/* rounding used when a value is quantized to int8 */
+#define ZEN_ROUND_NEAREST_EVEN 0 /* rint: zenith/optimization/qat.py:267, core/src/cuda_kernels.cu:926 */
+#define ZEN_ROUND_TRUNC 1        /* toward zero: zenith/optimization/quantization.py:49-53 */
+
+int zen_version(void);
+const char* zen_status_string(int status);
+
+/* Device status word: 0 or the first ZEN_ERR_* recorded by a kernel since the last clear.
+ * Both calls synchronise the current device. */
+int zen_device_status_read(int* status_host);
+int zen_device_status_clear(void);
+
+/* ------------------------------------------------------------------------------------------
+ * W8A8 Linear:  acc[m,n] = sum_k xq[m,k] * wq[n,k]   (int32, exact, tcgen05 kind::i8)
+ *   out_dtype S32 : out = acc
+ *   otherwise     : y = (float(acc) * x_scale) * w_scale[n] + bias[n]; y = act(y);
+ *                   F32: out = y;  F16: out = half(y);
+ *                   S8 : out = clamp(round(y / out_scale), -128, 127)
+ * xq [M,K] row-major (row stride ldx bytes == elements), wq [N,K] row-major (ldw), out row
+ * stride ldo elements.  w_scale may be NULL (treated as 1.0 for every n), bias may be NULL.
+ * K, ldx and ldw must be multiples of 16; xq, wq 16-byte aligned.
+ * Replaces core/src/cuda_kernels.cu:963-1049 (int8_matmul_kernel, fused_int8_linear_kernel),
+ * :918-958 (quantize / dequantize) and core/src/fused_kernels.cu:47-62,317-330 (bias+GELU
+ * epilogues that ran as separate kernels).
+ * ------------------------------------------------------------------------------------------ */
+int zen_linear_i8(const int8_t* xq, int64_t ldx, const int8_t* wq, int64_t ldw, int M, int N, int K, float x_scale,
+                  const float* w_scale, const float* bias, int act, int out_dtype, float out_scale, int round_mode,
+                  void* out, int64_t ldo, void* stream);
+
+/* Tuning hook: force the GEMM tile width (64, 128, 192 or 256; 0 restores automatic selection).
+ * Process-wide, not thread-safe; meant for benchmarks.  No counterpart in the reference. */
+int zen_gemm_set_tile_n(int tile_n);
+
+/* FP16 Linear: y = x[M,K] . w[N,K]^T (+ bias[n], fp32) ; act ; out F16 or F32.  fp32 accumulate,
+ * tcgen05 kind::f16.  K, ldx, ldw multiples of 8.
+ * Replaces core/src/fp16_kernels.cu:92-122 (linear_fp16 = cublasGemmEx + add_bias_fp16_kernel)
+ * and zenith/runtime/triton_kernels.py:118-207 (fused Linear+GELU). */
+int zen_linear_f16(const void* x, int64_t ldx, const void* w, int64_t ldw, int M, int N, int K, const float* bias,
+                   int act, int out_dtype, void* out, int64_t ldo, void* stream);
+
+/* C f32[M,N] = A f16[M,K] . B f16[K,N], all row-major contiguous (B is [K,N], not a [N,K] weight).
+ * N and K multiples of 8.  Replaces zenith::cuda_kernels::wmma_matmul_f16,
+ * core/src/cuda_kernels.cu:698-767 (bound as zenith_cuda.wmma_matmul,
+ * core/bindings/cuda_bindings.cpp:110-132). */
+int zen_wmma_matmul_f16(const void* A, const void* B, float* C, int M, int N, int K, void* stream);
+
+/* C f32[M,N] = A f32[M,K] . B f32[K,N] on the tensor cores in TF32 (the reference's cuBLAS
+ * handle runs in TF32 math mode, core/include/zenith/cublas_ops.hpp:51).  N, K multiples of 4.
+ * Replaces zenith::cuda_kernels::matmul_f32, core/src/cuda_kernels.cu:297-336 (zenith_cuda.matmul). */
+int zen_matmul_f32(const float* A, const float* B, float* C, int M, int N, int K, void* stream);
+
+/* Elementwise.  n = element count.
+ * gelu: core/src/cuda_kernels.cu:115-126,559-562 (gelu_f32), core/src/fp16_kernels.cu:128-147.
+ * relu: core/src/cuda_kernels.cu relu_f32 (zenith_cuda.relu). */
+int zen_gelu_f32(const float* x, float* y, int64_t n, void* stream);
+int zen_gelu_f16(const void* x, void* y, int64_t n, void* stream);
+int zen_relu_f32(const float* x, float* y, int64_t n, void* stream);
+
+/* bias + GELU over [rows, features]: core/src/fused_kernels.cu:47-62,347-353 (fused_bias_gelu). */
+int zen_bias_gelu_f32(const float* x, const float* bias, float* y, int rows, int features, void* stream);
+
+/* LayerNorm over the last dim of [rows, hidden]; biased variance, two-pass, fp32 statistics.
+ * core/src/cuda_kernels.cu:132-184,564-575 (layernorm_f32); core/src/fp16_kernels.cu:154-261. */
+int zen_layernorm_f32(const float* x, const float* gamma, const float* beta, float* y, int rows, int hidden, float eps,
+                      void* stream);
+int zen_layernorm_f16(const void* x, const void* gamma, const void* beta, void* y, int rows, int hidden, float eps,
+                      void* stream);
+
+/* y = LayerNorm(x + residual).  The f16 form can also emit yq = quantize(y, out_scale) as int8
+ * (yq may be NULL).  core/src/fused_kernels.cu:145-221,393-399 (fused_add_layernorm);
+ * core/src/cuda_kernels.cu:778-859 (fused_residual_layernorm_f32). */
+int zen_add_layernorm_f32(const float* x, const float* residual, const float* gamma, const float* beta, float* y,
+                          int rows, int hidden, float eps, void* stream);
+int zen_add_layernorm_f16(const void* x, const void* residual, const void* gamma, const void* beta, void* y,
+                          int8_t* yq, float out_scale, int round_mode, int rows, int hidden, float eps, void* stream);
+
+/* q = clamp(round(x / scale) + zero_point, -128, 127);  x = (q - zero_point) * scale.
+ * core/src/cuda_kernels.cu:918-958 (quantize_f32_to_int8, dequantize_int8_to_f32). */
+int zen_quantize_f32(const float* x, int8_t* q, int64_t n, float scale, int zero_point, int round_mode, void* stream);
+int zen_quantize_f16(const void* x, int8_t* q, int64_t n, float scale, int zero_point, int round_mode, void* stream);
+int zen_dequantize_f32(const int8_t* q, float* x, int64_t n, float scale, int zero_point, void* stream);
+
+/* Attention forward, O = softmax(scale * Q K^T  [masked]) V, fp16 in / fp16 out, fp32 softmax.
+ * Element (b,h,s,d) of Q sits at q + b*q_sb + h*q_sh + s*q_ss + d (strides in elements, d
+ * contiguous; strides multiples of 8) and likewise for K, V, O.  kv_lens[b] (NULL = S for all)
+ * masks keys >= kv_lens[b]; a row with no valid key yields zeros.  causal keeps key <= query.
+ * If oq != NULL the int8 copy clamp(round(o / o_scale)) is written with the O strides as well.
+ * head_dim 64 or 128.
+ * Replaces core/src/flash_attention.cu:55-355 (tiled_attention_kernel, fp16 twin),
+ * core/src/flash_attention_v2.cu:121-462 (causal), core/src/fp16_kernels.cu:416-456 (cuBLAS path). */
+int zen_flash_attention_f16(const void* q, const void* k, const void* v, void* o, int8_t* oq, float o_scale, int B,
+                            int H, int S, int D, int64_t q_sb, int64_t q_sh, int64_t q_ss, int64_t k_sb, int64_t k_sh,
+                            int64_t k_ss, int64_t v_sb, int64_t v_sh, int64_t v_ss, int64_t o_sb, int64_t o_sh,
+                            int64_t o_ss, const int32_t* kv_lens, int causal, float scale, void* stream);
+
+/* f32 <-> f16 converts (core/src/fp16_kernels.cu:53-77). */
+int zen_convert_f32_to_f16(const float* x, void* y, int64_t n, void* stream);
+int zen_convert_f16_to_f32(const void* x, float* y, int64_t n, void* stream);
+
+/* out[t,:] = LayerNorm(word[ids[t]] + pos[t % seq] + type[type_ids[t]]) in fp16, plus optional
+ * int8 copy.  ids/type_ids int32 [tokens]; type_ids may be NULL (row 0 of the type table).
+ * core/src/transformer_kernels.cu:236-262 (embedding_f32: word-table gather only). */
+int zen_embed_layernorm_f16(const int32_t* ids, const int32_t* type_ids, const void* word, const void* pos,
+                            const void* type, const void* gamma, const void* beta, void* y, int8_t* yq,
+                            float out_scale, int round_mode, int tokens, int seq, int hidden, int vocab, float eps,
+                            void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ZENITH_B200_H_ */

@@ -1,0 +1,178 @@
+// Host side of the tcgen05 GEMMs: tile selection, tensor maps, launches, C ABI.
+#include "gemm_tc.cuh"
+#include "tma_host.cuh"
+
+namespace zen {
+
+static int g_tile_n_override = 0;
+
+// Smallest estimated time: waves of persistent CTAs x (tile width + fixed per-tile cost).
+static int pick_bn(int M, int N, const int* allowed, int n_allowed) {
+  if (g_tile_n_override) {
+    for (int i = 0; i < n_allowed; ++i)
+      if (allowed[i] == g_tile_n_override) return g_tile_n_override;
+  }
+  const int sms = num_sms();
+  const int tiles_m = (M + GEMM_BM - 1) / GEMM_BM;
+  long best_cost = -1;
+  int best = allowed[0];
+  for (int i = 0; i < n_allowed; ++i) {
+    const int bn = allowed[i];
+    const long tiles = long(tiles_m) * ((N + bn - 1) / bn);
+    const long waves = (tiles + sms - 1) / sms;
+    const long cost = waves * (bn + 24);
+    if (best_cost < 0 || cost < best_cost) {
+      best_cost = cost;
+      best = bn;
+    }
+  }
+  return best;
+}
+
+template <int KIND, int BN, int STAGES, bool B_MN>
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams p, cudaStream_t stream) {
+  auto kernel = gemm_tc_kernel<KIND, BN, STAGES, B_MN>;
+  constexpr size_t smem = gemm_smem_bytes<BN, STAGES>();
+  static bool attr_set = false;  // per instantiation; setting twice is harmless
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) {
+      cudaGetLastError();
+      return ZEN_ERR_LAUNCH;
+    }
+    attr_set = true;
+  }
+  p.tiles_m = (p.M + GEMM_BM - 1) / GEMM_BM;
+  p.tiles_n = (p.N + BN - 1) / BN;
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int grid = tiles < num_sms() ? tiles : num_sms();
+  kernel<<<grid, GEMM_THREADS, smem, stream>>>(ta, tb, p);
+  return cudaGetLastError() == cudaSuccess ? ZEN_OK : ZEN_ERR_LAUNCH;
+}
+
+template <int KIND>
+static CUtensorMapDataType tmap_dtype() {
+  return KIND == KIND_I8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+         : KIND == KIND_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                            : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+}
+
+// A [M,K] (row stride lda elements); B K-major [N,K] (ldb) or MN-major [K,N] (ldb).
+template <int KIND, int BN, int STAGES, bool B_MN>
+static int run_gemm(const void* A, int64_t lda, const void* B, int64_t ldb, GemmParams p, cudaStream_t stream) {
+  constexpr int ELEM = GemmKind<KIND>::ELEM;
+  constexpr int BK = 128 / ELEM;
+  CUtensorMap ta, tb;
+  int st = encode_tmap_2d(&ta, tmap_dtype<KIND>(), A, uint64_t(p.K), uint64_t(p.M), uint64_t(lda) * ELEM, BK, GEMM_BM);
+  if (st != ZEN_OK) return st;
+  if (!B_MN) st = encode_tmap_2d(&tb, tmap_dtype<KIND>(), B, uint64_t(p.K), uint64_t(p.N), uint64_t(ldb) * ELEM, BK, BN);
+  else st = encode_tmap_2d(&tb, tmap_dtype<KIND>(), B, uint64_t(p.N), uint64_t(p.K), uint64_t(ldb) * ELEM, BK, BK);
+  if (st != ZEN_OK) return st;
+  p.num_k_blocks = (p.K + BK - 1) / BK;
+  return launch_gemm<KIND, BN, STAGES, B_MN>(ta, tb, p, stream);
+}
+
+}  // namespace zen
+
+using namespace zen;
+
+ZEN_DEFINE_TU_STATUS(gemm)
+
+extern "C" {
+
+int zen_version(void) { return ZEN_VERSION; }
+
+const char* zen_status_string(int s) {
+  switch (s) {
+    case ZEN_OK: return "ok";
+    case ZEN_ERR_INVALID_ARG: return "invalid argument";
+    case ZEN_ERR_UNSUPPORTED: return "unsupported shape, stride or alignment";
+    case ZEN_ERR_LAUNCH: return "kernel launch failed";
+    case ZEN_ERR_TIMEOUT: return "a bounded device-side wait ran out";
+    case ZEN_ERR_DRIVER: return "tensor-map encoding unavailable or failed";
+    case ZEN_ERR_TOO_LARGE: return "request exceeds a fixed capacity";
+    default: return "unknown status";
+  }
+}
+
+int zen_gemm_set_tile_n(int bn) {
+  if (bn != 0 && bn != 64 && bn != 128 && bn != 192 && bn != 256) return ZEN_ERR_INVALID_ARG;
+  g_tile_n_override = bn;
+  return ZEN_OK;
+}
+
+int zen_linear_i8(const int8_t* xq, int64_t ldx, const int8_t* wq, int64_t ldw, int M, int N, int K, float x_scale,
+                  const float* w_scale, const float* bias, int act, int out_dtype, float out_scale, int round_mode,
+                  void* out, int64_t ldo, void* stream) {
+  if (!xq || !wq || !out || M <= 0 || N <= 0 || K <= 0) return ZEN_ERR_INVALID_ARG;
+  if (out_dtype < ZEN_DT_S32 || out_dtype > ZEN_DT_S8 || act < ZEN_ACT_NONE || act > ZEN_ACT_RELU)
+    return ZEN_ERR_INVALID_ARG;
+  if (round_mode != ZEN_ROUND_NEAREST_EVEN && round_mode != ZEN_ROUND_TRUNC) return ZEN_ERR_INVALID_ARG;
+  if (out_dtype == ZEN_DT_S8 && !(out_scale > 0.0f)) return ZEN_ERR_INVALID_ARG;
+  if (K % 16 || ldx % 16 || ldw % 16 || ldx < K || ldw < K || ldo < N) return ZEN_ERR_UNSUPPORTED;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K;
+  p.out = out; p.ldo = ldo; p.out_dtype = out_dtype; p.act = act; p.round_mode = round_mode;
+  p.x_scale = x_scale; p.out_scale = out_scale; p.w_scale = w_scale; p.bias = bias;
+  static const int allowed[] = {64, 128, 192, 256};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (pick_bn(M, N, allowed, 4)) {
+    case 64: return run_gemm<KIND_I8, 64, 8, false>(xq, ldx, wq, ldw, p, s);
+    case 128: return run_gemm<KIND_I8, 128, 6, false>(xq, ldx, wq, ldw, p, s);
+    case 192: return run_gemm<KIND_I8, 192, 5, false>(xq, ldx, wq, ldw, p, s);
+    default: return run_gemm<KIND_I8, 256, 4, false>(xq, ldx, wq, ldw, p, s);
+  }
+}
+
+int zen_linear_f16(const void* x, int64_t ldx, const void* w, int64_t ldw, int M, int N, int K, const float* bias,
+                   int act, int out_dtype, void* out, int64_t ldo, void* stream) {
+  if (!x || !w || !out || M <= 0 || N <= 0 || K <= 0) return ZEN_ERR_INVALID_ARG;
+  if ((out_dtype != ZEN_DT_F32 && out_dtype != ZEN_DT_F16) || act < ZEN_ACT_NONE || act > ZEN_ACT_RELU)
+    return ZEN_ERR_INVALID_ARG;
+  if (K % 8 || ldx % 8 || ldw % 8 || ldx < K || ldw < K || ldo < N) return ZEN_ERR_UNSUPPORTED;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K;
+  p.out = out; p.ldo = ldo; p.out_dtype = out_dtype; p.act = act;
+  p.x_scale = 1.0f; p.out_scale = 1.0f; p.w_scale = nullptr; p.bias = bias;
+  static const int allowed[] = {64, 128, 192, 256};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (pick_bn(M, N, allowed, 4)) {
+    case 64: return run_gemm<KIND_F16, 64, 8, false>(x, ldx, w, ldw, p, s);
+    case 128: return run_gemm<KIND_F16, 128, 6, false>(x, ldx, w, ldw, p, s);
+    case 192: return run_gemm<KIND_F16, 192, 5, false>(x, ldx, w, ldw, p, s);
+    default: return run_gemm<KIND_F16, 256, 4, false>(x, ldx, w, ldw, p, s);
+  }
+}
+
+int zen_wmma_matmul_f16(const void* A, const void* B, float* C, int M, int N, int K, void* stream) {
+  if (!A || !B || !C || M <= 0 || N <= 0 || K <= 0) return ZEN_ERR_INVALID_ARG;
+  if (K % 8 || N % 8) return ZEN_ERR_UNSUPPORTED;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K;
+  p.out = C; p.ldo = N; p.out_dtype = ZEN_DT_F32; p.act = ZEN_ACT_NONE;
+  p.x_scale = 1.0f; p.out_scale = 1.0f;
+  static const int allowed[] = {64, 128, 256};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (pick_bn(M, N, allowed, 3)) {
+    case 64: return run_gemm<KIND_F16, 64, 8, true>(A, K, B, N, p, s);
+    case 128: return run_gemm<KIND_F16, 128, 6, true>(A, K, B, N, p, s);
+    default: return run_gemm<KIND_F16, 256, 4, true>(A, K, B, N, p, s);
+  }
+}
+
+int zen_matmul_f32(const float* A, const float* B, float* C, int M, int N, int K, void* stream) {
+  if (!A || !B || !C || M <= 0 || N <= 0 || K <= 0) return ZEN_ERR_INVALID_ARG;
+  if (K % 4 || N % 4) return ZEN_ERR_UNSUPPORTED;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K;
+  p.out = C; p.ldo = N; p.out_dtype = ZEN_DT_F32; p.act = ZEN_ACT_NONE;
+  p.x_scale = 1.0f; p.out_scale = 1.0f;
+  static const int allowed[] = {64, 128, 256};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (pick_bn(M, N, allowed, 3)) {
+    case 64: return run_gemm<KIND_TF32, 64, 8, true>(A, K, B, N, p, s);
+    case 128: return run_gemm<KIND_TF32, 128, 6, true>(A, K, B, N, p, s);
+    default: return run_gemm<KIND_TF32, 256, 4, true>(A, K, B, N, p, s);
+  }
+}
+
+}  // extern "C"

@@ -1,0 +1,323 @@
+// Persistent, warp-specialised tcgen05 GEMM for sm_100a:  D[M,N] = A[M,K] . B^T  with a fused
+// epilogue.  One kernel template serves the int8 (kind::i8, s32 accumulators), fp16
+// (kind::f16, f32 accumulators) and fp32-as-TF32 (kind::tf32) paths.
+//
+//   warp 0      : TMA producer  — 128-byte-swizzled tiles of A and B into a STAGES-deep ring
+//   warp 1      : allocates TMEM, issues tcgen05.mma (one lane), commits stage / accumulator barriers
+//   warps 2..5  : epilogue — tcgen05.ld of the accumulator (each warp its own 32-lane quadrant),
+//                 dequant / bias / activation / requant, 16-byte global stores
+//
+// TMEM holds two accumulators (2 x BN columns) so the epilogue of tile i overlaps the MMAs of
+// tile i+1.  CTAs are persistent: tile t = blockIdx.x + i * gridDim.x, M-fastest.
+//
+// A is always K-major ([M,K] row-major).  B is K-major ([N,K] row-major, a Linear weight) or,
+// with B_MN, MN-major ([K,N] row-major, the right operand of a plain matmul).
+// Out-of-range rows / columns / K are zero-filled by TMA on load and masked on store.
+#pragma once
+#include "zen_common.cuh"
+#include "det_math.h"
+
+namespace zen {
+
+enum { KIND_I8 = 0, KIND_F16 = 1, KIND_TF32 = 2 };
+
+struct GemmParams {
+  int M, N, K;
+  int tiles_m, tiles_n, num_k_blocks;
+  void* out;
+  int64_t ldo;
+  int out_dtype;
+  int act;
+  int round_mode;
+  float x_scale;
+  float out_scale;
+  const float* w_scale;
+  const float* bias;
+};
+
+template <int KIND>
+struct GemmKind;
+template <>
+struct GemmKind<KIND_I8> {
+  static constexpr int ELEM = 1;
+};
+template <>
+struct GemmKind<KIND_F16> {
+  static constexpr int ELEM = 2;
+};
+template <>
+struct GemmKind<KIND_TF32> {
+  static constexpr int ELEM = 4;
+};
+
+constexpr int GEMM_BM = 128;
+constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_EPI_WARPS = 4;
+
+template <int BN>
+__host__ __device__ constexpr uint32_t gemm_tmem_cols() {
+  return 2 * BN <= 32 ? 32u : 2 * BN <= 64 ? 64u : 2 * BN <= 128 ? 128u : 2 * BN <= 256 ? 256u : 512u;
+}
+
+template <int BN, int STAGES>
+__host__ __device__ constexpr size_t gemm_smem_bytes() {
+  // ring + barriers/flags (256 B) + per-epilogue-warp scale and bias rows + alignment slack
+  return size_t(STAGES) * (GEMM_BM * 128 + BN * 128) + 256 + size_t(GEMM_EPI_WARPS) * 2 * BN * 4 + 1024;
+}
+
+template <int KIND>
+__device__ __forceinline__ void issue_mma(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
+  if constexpr (KIND == KIND_I8) mma_i8_ss(d, a, b, idesc, acc);
+  else if constexpr (KIND == KIND_F16) mma_f16_ss(d, a, b, idesc, acc);
+  else mma_tf32_ss(d, a, b, idesc, acc);
+}
+
+// 16-byte stores of NV consecutive 32-bit words (dst 16-byte aligned)
+template <int NW>
+__device__ __forceinline__ void store_words(void* dst, const uint32_t* w) {
+  uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+  for (int i = 0; i < NW / 4; ++i) d4[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+}
+
+template <int KIND, int BN, int STAGES, bool B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+               const GemmParams p) {
+  constexpr int ELEM = GemmKind<KIND>::ELEM;
+  constexpr int BK = 128 / ELEM;  // elements per 128-byte swizzle row == K extent of one stage
+  constexpr int UK = 32 / ELEM;   // K extent of one tcgen05.mma
+  constexpr int A_BYTES = GEMM_BM * 128;
+  constexpr int B_BYTES = BN * 128;
+  constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr uint32_t TMEM_COLS = gemm_tmem_cols<BN>();
+  constexpr uint32_t IDESC =
+      KIND == KIND_I8 ? make_idesc(IDESC_C_S32, IDESC_S8, IDESC_S8, 0, B_MN ? 1 : 0, GEMM_BM, BN)
+      : KIND == KIND_F16 ? make_idesc(IDESC_C_F32, IDESC_F16, IDESC_F16, 0, B_MN ? 1 : 0, GEMM_BM, BN)
+                         : make_idesc(IDESC_C_F32, IDESC_TF32, IDESC_TF32, 0, B_MN ? 1 : 0, GEMM_BM, BN);
+  static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "BN");
+  static_assert(!B_MN || BN % BK == 0, "MN-major B is loaded in 128-byte wide boxes");
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint8_t* ctrl = smem + size_t(STAGES) * STAGE_BYTES;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(ctrl);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tfull_bar = empty_bar + STAGES;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* epi_rows = reinterpret_cast<float*>(ctrl + 256);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int nkb = p.num_k_blocks;
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+    for (int i = 0; i < STAGES; ++i) {
+      mbar_init(&full_bar[i], 1);
+      mbar_init(&empty_bar[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tfull_bar[i], 1);
+      mbar_init(&tempty_bar[i], GEMM_EPI_WARPS * 32);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % p.tiles_m) * GEMM_BM;
+        const int n0 = (tile / p.tiles_m) * BN;
+        for (int kb = 0; kb < nkb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + size_t(stage) * STAGE_BYTES;
+          uint8_t* sb = sa + A_BYTES;
+          mbar_arrive_expect_tx(&full_bar[stage], STAGE_BYTES);
+          tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * BK, m0);
+          if constexpr (!B_MN) {
+            tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * BK, n0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / BK; ++c)
+              tma_load_2d(sb + c * (BK * 128), &tmap_b, &full_bar[stage], n0 + c * BK, kb * BK);
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (!ok) {
+        // give copies already in flight time to land before the CTA's shared memory is released
+        for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1u, abort_flag)) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + uint32_t(acc * BN);
+        for (int kb = 0; kb < nkb; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(smem + size_t(stage) * STAGE_BYTES);
+          const uint32_t b_addr = a_addr + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UK; ++k) {
+            const uint64_t a_desc = make_smem_desc_sw128(a_addr + k * 32, 1024, 16);
+            const uint64_t b_desc = B_MN ? make_smem_desc_sw128(b_addr + k * (UK * 128), 1024, BK * 128)
+                                         : make_smem_desc_sw128(b_addr + k * 32, 1024, 16);
+            issue_mma<KIND>(d_tmem, a_desc, b_desc, IDESC, (kb | k) != 0 ? 1u : 0u);
+          }
+          tc_commit(&empty_bar[stage]);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok) tc_commit(&tfull_bar[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue
+    const int quad = warp & 3;  // TMEM lane quadrant this warp may read
+    float* s_scale = epi_rows + (warp - 2) * 2 * BN;
+    float* s_bias = s_scale + BN;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    const bool vec_ok = (reinterpret_cast<uintptr_t>(p.out) % 16 == 0) &&
+                        ((p.ldo * (p.out_dtype == ZEN_DT_S8 ? 1 : p.out_dtype == ZEN_DT_F16 ? 2 : 4)) % 16 == 0);
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+      const int m0 = (tile % p.tiles_m) * GEMM_BM;
+      const int n0 = (tile / p.tiles_m) * BN;
+      __syncwarp();
+      for (int i = lane; i < BN; i += 32) {
+        const int col = n0 + i;
+        s_scale[i] = (p.w_scale != nullptr && col < p.N) ? __ldg(p.w_scale + col) : 1.0f;
+        s_bias[i] = (p.bias != nullptr && col < p.N) ? __ldg(p.bias + col) : 0.0f;
+      }
+      __syncwarp();
+      if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag)) break;
+      tc_fence_after_sync();
+      const int row = m0 + quad * 32 + lane;
+      const bool row_ok = row < p.M;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        __syncwarp();
+        tmem_ld_32x32(tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * BN + c * 32), r);
+        tmem_wait_ld();
+        const int col0 = n0 + c * 32;
+        if (!row_ok || col0 >= p.N) continue;
+        const bool full = vec_ok && (col0 + 32 <= p.N);
+        const float* sc = s_scale + c * 32;
+        const float* bi = s_bias + c * 32;
+        float y[32];
+        if (KIND == KIND_I8 && p.out_dtype == ZEN_DT_S32) {
+          int32_t* o = static_cast<int32_t*>(p.out) + int64_t(row) * p.ldo + col0;
+          if (full) store_words<32>(o, r);
+          else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.N) o[j] = int32_t(r[j]);
+          }
+          continue;
+        }
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          float v;
+          if constexpr (KIND == KIND_I8) v = zen_det_dequant(int32_t(r[j]), p.x_scale, sc[j], bi[j]);
+          else v = p.bias != nullptr ? ZEN_ADD(__uint_as_float(r[j]), bi[j]) : __uint_as_float(r[j]);
+          y[j] = zen_det_act(v, p.act);
+        }
+        if (p.out_dtype == ZEN_DT_F32) {
+          float* o = static_cast<float*>(p.out) + int64_t(row) * p.ldo + col0;
+          if (full) store_words<32>(o, reinterpret_cast<const uint32_t*>(y));
+          else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.N) o[j] = y[j];
+          }
+        } else if (p.out_dtype == ZEN_DT_F16) {
+          __half* o = static_cast<__half*>(p.out) + int64_t(row) * p.ldo + col0;
+          if (full) {
+            uint32_t w[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              __half2 h = __floats2half2_rn(y[2 * j], y[2 * j + 1]);
+              w[j] = *reinterpret_cast<uint32_t*>(&h);
+            }
+            store_words<16>(o, w);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.N) o[j] = __float2half_rn(y[j]);
+          }
+        } else {  // ZEN_DT_S8
+          int8_t* o = static_cast<int8_t*>(p.out) + int64_t(row) * p.ldo + col0;
+          if (full) {
+            uint32_t w[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              uint32_t pk = 0;
+#pragma unroll
+              for (int b = 0; b < 4; ++b) {
+                const int q = zen_det_round_clamp_i8(ZEN_DIV(y[4 * j + b], p.out_scale), p.round_mode);
+                pk |= (uint32_t(q) & 0xffu) << (8 * b);
+              }
+              w[j] = pk;
+            }
+            store_words<8>(o, w);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.N) o[j] = int8_t(zen_det_round_clamp_i8(ZEN_DIV(y[j], p.out_scale), p.round_mode));
+          }
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&tempty_bar[acc]);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+}  // namespace zen

@@ -1,0 +1,34 @@
+// Device status word: folds the per-translation-unit words together for the host.
+#include "zen_common.cuh"
+
+extern "C" {
+int zen_tu_status_gemm(int* out, int clear);
+int zen_tu_status_rowwise(int* out, int clear);
+int zen_tu_status_flash_attn(int* out, int clear);
+}
+
+typedef int (*TuStatusFn)(int*, int);
+static const TuStatusFn kTuStatus[] = {zen_tu_status_gemm, zen_tu_status_rowwise, zen_tu_status_flash_attn};
+
+static int fold_status(int* out, int clear) {
+  if (cudaDeviceSynchronize() != cudaSuccess) {
+    cudaGetLastError();
+    return ZEN_ERR_LAUNCH;
+  }
+  int first = 0;
+  for (TuStatusFn fn : kTuStatus) {
+    int v = 0;
+    const int st = fn(&v, clear);
+    if (st != ZEN_OK) return st;
+    if (first == 0) first = v;
+  }
+  if (out) *out = first;
+  return ZEN_OK;
+}
+
+extern "C" int zen_device_status_read(int* status_host) {
+  if (!status_host) return ZEN_ERR_INVALID_ARG;
+  return fold_status(status_host, 0);
+}
+
+extern "C" int zen_device_status_clear(void) { return fold_status(nullptr, 1); }

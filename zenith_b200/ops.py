@@ -1,0 +1,347 @@
+"""Typed operators over ``torch`` CUDA tensors, each one C-ABI call on torch's current stream.
+
+torch is used for device memory and streams only; every computation below runs in the
+hand-written sm_100a kernels of ``libzenith_b200.so``.  There is no CPU path: a CPU tensor, a
+missing extension or a non-zero status raises.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import _capi
+from ._capi import (ACT_GELU, ACT_NONE, ACT_RELU, DT_F16, DT_F32, DT_S8, DT_S32, ROUND_NEAREST_EVEN,  # noqa: F401
+                    ROUND_TRUNC)
+
+_ACT = {"none": ACT_NONE, None: ACT_NONE, "gelu": ACT_GELU, "relu": ACT_RELU}
+_ROUND = {"nearest_even": ROUND_NEAREST_EVEN, "trunc": ROUND_TRUNC}
+_OUT = {torch.int32: DT_S32, torch.float32: DT_F32, torch.float16: DT_F16, torch.int8: DT_S8}
+
+# number of kernels this module has launched (read by the benchmark's `gpu_launches`)
+launch_count = 0
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _require(t: torch.Tensor, name: str, dtype=None, ndim=None) -> None:
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor")
+    if dtype is not None and t.dtype != dtype:
+        raise RuntimeError(f"{name} must be {dtype}, got {t.dtype}")
+    if ndim is not None and t.dim() != ndim:
+        raise RuntimeError(f"{name} must be {ndim}-D, got {t.dim()}-D")
+    if not t.is_contiguous():
+        raise RuntimeError(f"{name} must be contiguous")
+
+
+def _ptr(t) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _call(fn: str, *args) -> None:
+    global launch_count
+    _capi.call(fn, *args)
+    launch_count += 1
+
+
+# --------------------------------------------------------------------------------------------
+# GEMMs
+# --------------------------------------------------------------------------------------------
+def linear_int8(xq, wq, x_scale: float, w_scale=None, bias=None, *, act="none", out_dtype=torch.float32,
+                out_scale: float | None = None, round="nearest_even", out=None):
+    """W8A8 Linear: ``acc = xq @ wq.T`` in int32, then the fused epilogue.
+
+    ``out_dtype=torch.int32`` returns the raw accumulators.  Otherwise
+    ``y = (float(acc) * x_scale) * w_scale[n] + bias[n]``, optional activation, then fp32 / fp16
+    output or requantisation ``clamp(round(y / out_scale))`` to int8.
+    Follows core/src/cuda_kernels.cu:1010-1049 (fused_int8_linear_kernel) with per-output-channel
+    weight scales (zenith/optimization/qat.py:195-199).
+    """
+    _require(xq, "xq", torch.int8, 2)
+    _require(wq, "wq", torch.int8, 2)
+    M, K = xq.shape
+    N, K2 = wq.shape
+    if K != K2:
+        raise RuntimeError(f"inner dimensions differ: xq {tuple(xq.shape)} vs wq {tuple(wq.shape)}")
+    if w_scale is not None:
+        _require(w_scale, "w_scale", torch.float32, 1)
+        if w_scale.numel() != N:
+            raise RuntimeError("w_scale must have one entry per output channel")
+    if bias is not None:
+        _require(bias, "bias", torch.float32, 1)
+        if bias.numel() != N:
+            raise RuntimeError("bias must have one entry per output channel")
+    if out_dtype not in _OUT:
+        raise RuntimeError(f"unsupported out_dtype {out_dtype}")
+    if out_dtype == torch.int8 and out_scale is None:
+        raise RuntimeError("out_scale is required for int8 output")
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=xq.device)
+    else:
+        _require(out, "out", out_dtype, 2)
+    if M == 0 or N == 0:
+        return out
+    _call("zen_linear_i8", xq.data_ptr(), K, wq.data_ptr(), K, M, N, K, float(x_scale), _ptr(w_scale), _ptr(bias),
+          _ACT[act], _OUT[out_dtype], float(out_scale if out_scale is not None else 1.0), _ROUND[round],
+          out.data_ptr(), out.stride(0), _stream())
+    return out
+
+
+def linear_fp16(x, w, bias=None, *, act="none", out_dtype=torch.float16, out=None):
+    """``act(x @ w.T + bias)`` with fp16 operands, fp32 accumulation (core/src/fp16_kernels.cu:92-122)."""
+    _require(x, "x", torch.float16, 2)
+    _require(w, "w", torch.float16, 2)
+    M, K = x.shape
+    N, K2 = w.shape
+    if K != K2:
+        raise RuntimeError(f"inner dimensions differ: x {tuple(x.shape)} vs w {tuple(w.shape)}")
+    if bias is not None:
+        _require(bias, "bias", torch.float32, 1)
+    if out_dtype not in (torch.float16, torch.float32):
+        raise RuntimeError(f"unsupported out_dtype {out_dtype}")
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    if M == 0 or N == 0:
+        return out
+    _call("zen_linear_f16", x.data_ptr(), K, w.data_ptr(), K, M, N, K, _ptr(bias), _ACT[act], _OUT[out_dtype],
+          out.data_ptr(), out.stride(0), _stream())
+    return out
+
+
+def wmma_matmul(a, b):
+    """``C f32[M,N] = A f16[M,K] @ B f16[K,N]`` (core/bindings/cuda_bindings.cpp:110-132)."""
+    if not a.is_cuda or not b.is_cuda:
+        raise RuntimeError("Inputs must be CUDA tensors")
+    if a.dim() != 2 or b.dim() != 2:
+        raise RuntimeError("Inputs must be 2D")
+    if a.dtype != torch.float16 or b.dtype != torch.float16:
+        raise RuntimeError("Inputs must be FP16")
+    if a.shape[1] != b.shape[0]:
+        raise RuntimeError("Inner dimensions must match")
+    a = a.contiguous()
+    b = b.contiguous()
+    M, K = a.shape
+    N = b.shape[1]
+    c = torch.empty((M, N), dtype=torch.float32, device=a.device)
+    if M and N:
+        _call("zen_wmma_matmul_f16", a.data_ptr(), b.data_ptr(), c.data_ptr(), M, N, K, _stream())
+    return c
+
+
+def matmul_f32(a, b):
+    """``C = A @ B`` for fp32 operands on the tensor cores in TF32 (core/bindings/cuda_bindings.cpp:73-88)."""
+    if not a.is_cuda or not b.is_cuda:
+        raise RuntimeError("Inputs must be CUDA tensors")
+    if a.dim() != 2 or b.dim() != 2:
+        raise RuntimeError("Inputs must be 2D")
+    if a.shape[1] != b.shape[0]:
+        raise RuntimeError("Inner dimensions must match")
+    _require(a.contiguous(), "A", torch.float32)
+    a = a.contiguous()
+    b = b.contiguous()
+    _require(b, "B", torch.float32)
+    M, K = a.shape
+    N = b.shape[1]
+    c = torch.empty((M, N), dtype=torch.float32, device=a.device)
+    if M and N:
+        _call("zen_matmul_f32", a.data_ptr(), b.data_ptr(), c.data_ptr(), M, N, K, _stream())
+    return c
+
+
+# --------------------------------------------------------------------------------------------
+# elementwise / row kernels
+# --------------------------------------------------------------------------------------------
+def gelu(x):
+    """tanh-form GELU (core/src/cuda_kernels.cu:115-126), fp32 or fp16, any shape."""
+    if x.dtype == torch.float32:
+        _require(x, "input", torch.float32)
+        y = torch.empty_like(x)
+        if x.numel():
+            _call("zen_gelu_f32", x.data_ptr(), y.data_ptr(), x.numel(), _stream())
+        return y
+    _require(x, "input", torch.float16)
+    y = torch.empty_like(x)
+    if x.numel():
+        _call("zen_gelu_f16", x.data_ptr(), y.data_ptr(), x.numel(), _stream())
+    return y
+
+
+def relu(x):
+    _require(x, "input", torch.float32)
+    y = torch.empty_like(x)
+    if x.numel():
+        _call("zen_relu_f32", x.data_ptr(), y.data_ptr(), x.numel(), _stream())
+    return y
+
+
+def bias_gelu(x, bias):
+    """``gelu(x + bias[col])`` over [rows, features] (core/src/fused_kernels.cu:47-62)."""
+    _require(x, "input", torch.float32, 2)
+    _require(bias, "bias", torch.float32, 1)
+    y = torch.empty_like(x)
+    if x.numel():
+        _call("zen_bias_gelu_f32", x.data_ptr(), bias.data_ptr(), y.data_ptr(), x.shape[0], x.shape[1], _stream())
+    return y
+
+
+def layernorm(x, gamma, beta, eps: float = 1e-5):
+    """Row LayerNorm of a 2-D tensor, fp32 or fp16 (core/bindings/cuda_bindings.cpp:58-71)."""
+    if x.dtype not in (torch.float32, torch.float16):
+        raise RuntimeError("input must be fp32 or fp16")
+    _require(x, "input", x.dtype, 2)
+    _require(gamma, "gamma", x.dtype, 1)
+    _require(beta, "beta", x.dtype, 1)
+    y = torch.empty_like(x)
+    fn = "zen_layernorm_f32" if x.dtype == torch.float32 else "zen_layernorm_f16"
+    if x.numel():
+        _call(fn, x.data_ptr(), gamma.data_ptr(), beta.data_ptr(), y.data_ptr(), x.shape[0], x.shape[1], float(eps),
+              _stream())
+    return y
+
+
+def add_layernorm(x, residual, gamma, beta, eps: float = 1e-5, *, out_scale: float | None = None,
+                  round="nearest_even"):
+    """``LayerNorm(x + residual)`` (core/src/fused_kernels.cu:145-221).
+
+    With ``out_scale`` (fp16 only) also returns the int8 copy ``quantize(y, out_scale)``.
+    """
+    if x.dtype not in (torch.float32, torch.float16):
+        raise RuntimeError("input must be fp32 or fp16")
+    _require(x, "input", x.dtype, 2)
+    _require(residual, "residual", x.dtype, 2)
+    _require(gamma, "gamma", x.dtype, 1)
+    _require(beta, "beta", x.dtype, 1)
+    if residual.shape != x.shape:
+        raise RuntimeError("residual must have the shape of the input")
+    y = torch.empty_like(x)
+    rows, hidden = x.shape
+    if x.dtype == torch.float32:
+        if out_scale is not None:
+            raise RuntimeError("the int8 copy is available for fp16 inputs only")
+        if x.numel():
+            _call("zen_add_layernorm_f32", x.data_ptr(), residual.data_ptr(), gamma.data_ptr(), beta.data_ptr(),
+                  y.data_ptr(), rows, hidden, float(eps), _stream())
+        return y
+    yq = torch.empty(x.shape, dtype=torch.int8, device=x.device) if out_scale is not None else None
+    if x.numel():
+        _call("zen_add_layernorm_f16", x.data_ptr(), residual.data_ptr(), gamma.data_ptr(), beta.data_ptr(),
+              y.data_ptr(), _ptr(yq), float(out_scale or 1.0), _ROUND[round], rows, hidden, float(eps), _stream())
+    return y if yq is None else (y, yq)
+
+
+def quantize(x, scale: float, zero_point: int = 0, *, round="nearest_even"):
+    """``clamp(round(x / scale + zero_point), -128, 127)`` (core/src/cuda_kernels.cu:918-929)."""
+    if x.dtype not in (torch.float32, torch.float16):
+        raise RuntimeError("input must be fp32 or fp16")
+    _require(x, "input", x.dtype)
+    q = torch.empty(x.shape, dtype=torch.int8, device=x.device)
+    fn = "zen_quantize_f32" if x.dtype == torch.float32 else "zen_quantize_f16"
+    if x.numel():
+        _call(fn, x.data_ptr(), q.data_ptr(), x.numel(), float(scale), int(zero_point), _ROUND[round], _stream())
+    return q
+
+
+def dequantize(q, scale: float, zero_point: int = 0):
+    """``(q - zero_point) * scale`` (core/src/cuda_kernels.cu:941-950)."""
+    _require(q, "input", torch.int8)
+    x = torch.empty(q.shape, dtype=torch.float32, device=q.device)
+    if q.numel():
+        _call("zen_dequantize_f32", q.data_ptr(), x.data_ptr(), q.numel(), float(scale), int(zero_point), _stream())
+    return x
+
+
+def to_fp16(x):
+    _require(x, "input", torch.float32)
+    y = torch.empty(x.shape, dtype=torch.float16, device=x.device)
+    if x.numel():
+        _call("zen_convert_f32_to_f16", x.data_ptr(), y.data_ptr(), x.numel(), _stream())
+    return y
+
+
+def to_fp32(x):
+    _require(x, "input", torch.float16)
+    y = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+    if x.numel():
+        _call("zen_convert_f16_to_f32", x.data_ptr(), y.data_ptr(), x.numel(), _stream())
+    return y
+
+
+# --------------------------------------------------------------------------------------------
+# attention
+# --------------------------------------------------------------------------------------------
+def flash_attention_strided(q, k, v, out, B, H, S, D, q_strides, k_strides, v_strides, o_strides, *, kv_lens=None,
+                            causal=False, scale=None, out_q=None, out_scale=None):
+    """Attention over strided fp16 views: strides are (batch, head, seq) in elements, d contiguous."""
+    if kv_lens is not None:
+        _require(kv_lens, "kv_lens", torch.int32, 1)
+    scale = 1.0 / math.sqrt(D) if scale is None else float(scale)
+    _call("zen_flash_attention_f16", q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), _ptr(out_q),
+          float(out_scale or 1.0), B, H, S, D, *q_strides, *k_strides, *v_strides, *o_strides, _ptr(kv_lens),
+          1 if causal else 0, scale, _stream())
+    return out
+
+
+def flash_attention(q, k, v, *, causal: bool = False, kv_lens=None, scale: float | None = None):
+    """``softmax(scale * Q K^T) V`` for ``[batch, heads, seq, dim]`` tensors.
+
+    fp16 inputs run directly; fp32 inputs (the reference binding's dtype,
+    core/bindings/cuda_bindings.cpp:90-106) are converted to fp16 on the device, run on the
+    tensor cores with fp32 softmax and accumulation, and returned as fp32.
+    ``kv_lens[b]`` masks keys at positions >= kv_lens[b]; a row with no valid key yields zeros.
+    """
+    if not q.is_cuda:
+        raise RuntimeError("Q must be CUDA tensor")
+    if q.dim() != 4:
+        raise RuntimeError("Q must be 4D [batch, heads, seq, dim]")
+    if k.shape != q.shape or v.shape != q.shape:
+        raise RuntimeError("K and V must have the shape of Q")
+    B, H, S, D = q.shape
+    if q.dtype == torch.float32:
+        qh, kh, vh = (to_fp16(t.contiguous()) for t in (q, k, v))
+        oh = flash_attention(qh, kh, vh, causal=causal, kv_lens=kv_lens, scale=scale)
+        return to_fp32(oh)
+    for name, t in (("Q", q), ("K", k), ("V", v)):
+        _require(t, name, torch.float16, 4)
+    out = torch.empty_like(q)
+    st = (H * S * D, S * D, D)
+    flash_attention_strided(q, k, v, out, B, H, S, D, st, st, st, st, kv_lens=kv_lens, causal=causal, scale=scale)
+    return out
+
+
+# --------------------------------------------------------------------------------------------
+# embedding
+# --------------------------------------------------------------------------------------------
+def embed_layernorm(ids, type_ids, word, pos, typ, gamma, beta, eps: float, seq: int, *, out_scale=None,
+                    round="nearest_even"):
+    """``LayerNorm(word[ids] + pos[t % seq] + type[type_ids])`` in fp16, optional int8 copy.
+
+    The reference's embedding kernel gathers the word table only
+    (core/src/transformer_kernels.cu:236-262); position / type tables and the LayerNorm are the
+    BERT embedding block that precedes the encoder.
+    """
+    _require(ids, "ids", torch.int32, 1)
+    if type_ids is not None:
+        _require(type_ids, "type_ids", torch.int32, 1)
+    for name, t in (("word", word), ("pos", pos), ("type", typ)):
+        _require(t, name, torch.float16, 2)
+    _require(gamma, "gamma", torch.float16, 1)
+    _require(beta, "beta", torch.float16, 1)
+    tokens = ids.numel()
+    hidden = word.shape[1]
+    if pos.shape[0] < seq:
+        raise RuntimeError("position table shorter than the sequence")
+    y = torch.empty((tokens, hidden), dtype=torch.float16, device=word.device)
+    yq = torch.empty((tokens, hidden), dtype=torch.int8, device=word.device) if out_scale is not None else None
+    if tokens:
+        _call("zen_embed_layernorm_f16", ids.data_ptr(), _ptr(type_ids), word.data_ptr(), pos.data_ptr(),
+              typ.data_ptr(), gamma.data_ptr(), beta.data_ptr(), y.data_ptr(), _ptr(yq), float(out_scale or 1.0),
+              _ROUND[round], tokens, int(seq), hidden, word.shape[0], float(eps), _stream())
+    return y if yq is None else (y, yq)
+
+
+def set_gemm_tile_n(tile_n: int) -> None:
+    """Force the GEMM tile width (0 = automatic).  Benchmark hook."""
+    _capi.call("zen_gemm_set_tile_n", int(tile_n))
