@@ -85,6 +85,12 @@ int zen_gemm_set_tile_n(int tile_n);
 int zen_linear_f16(const void* x, int64_t ldx, const void* w, int64_t ldw, int M, int N, int K, const float* bias,
                    int act, int out_dtype, void* out, int64_t ldo, void* stream);
 
+/* FP32 Linear on the tensor cores in TF32: y = act(x[M,K] . w[N,K]^T + bias), fp32 in and out.
+ * K, ldx, ldw multiples of 4.  Replaces cuda.linear_gpu = cublasSgemm (TF32 math mode) +
+ * add_bias_kernel, python/src/bindings.cpp:1454-1496, core/include/zenith/cublas_ops.hpp:133-156. */
+int zen_linear_f32(const float* x, int64_t ldx, const float* w, int64_t ldw, int M, int N, int K, const float* bias,
+                   int act, float* out, int64_t ldo, void* stream);
+
 /* C f32[M,N] = A f16[M,K] . B f16[K,N], all row-major contiguous (B is [K,N], not a [N,K] weight).
  * N and K multiples of 8.  Replaces zenith::cuda_kernels::wmma_matmul_f16,
  * core/src/cuda_kernels.cu:698-767 (bound as zenith_cuda.wmma_matmul,
@@ -92,9 +98,13 @@ int zen_linear_f16(const void* x, int64_t ldx, const void* w, int64_t ldw, int M
 int zen_wmma_matmul_f16(const void* A, const void* B, float* C, int M, int N, int K, void* stream);
 
 /* C f32[M,N] = A f32[M,K] . B f32[K,N] on the tensor cores in TF32 (the reference's cuBLAS
- * handle runs in TF32 math mode, core/include/zenith/cublas_ops.hpp:51).  N, K multiples of 4.
+ * handle runs in TF32 math mode, core/include/zenith/cublas_ops.hpp:51).  B is first transposed
+ * into `workspace` (at least zen_matmul_f32_workspace_bytes(N, K) bytes of device memory, 16-byte
+ * aligned, caller-owned), then multiplied as a K-major operand.  K a multiple of 4.
  * Replaces zenith::cuda_kernels::matmul_f32, core/src/cuda_kernels.cu:297-336 (zenith_cuda.matmul). */
-int zen_matmul_f32(const float* A, const float* B, float* C, int M, int N, int K, void* stream);
+size_t zen_matmul_f32_workspace_bytes(int N, int K);
+int zen_matmul_f32(const float* A, const float* B, float* C, int M, int N, int K, void* workspace,
+                   size_t workspace_bytes, void* stream);
 
 /* Elementwise.  n = element count.
  * gelu: core/src/cuda_kernels.cu:115-126,559-562 (gelu_f32), core/src/fp16_kernels.cu:128-147.

@@ -1,0 +1,68 @@
+"""Batch sharding and the output gather on CPU ranks (gloo, world size 2 and 3, uneven shards, a rank
+that fails before the collective)."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from zenith_b200.dist import OutputGatherer, shard_bounds
+
+
+def test_shard_bounds_cover_the_batch():
+    for gb in (1, 7, 32, 256):
+        for w in (1, 2, 3, 4, 8):
+            parts = [shard_bounds(gb, w, r) for r in range(w)]
+            assert parts[0][0] == 0 and sum(c for _, c in parts) == gb
+            for (s0, c0), (s1, _) in zip(parts, parts[1:]):
+                assert s0 + c0 == s1
+            assert max(c for _, c in parts) - min(c for _, c in parts) <= 1
+    with pytest.raises(ValueError):
+        shard_bounds(8, 2, 2)
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, gb, fail_rank, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        seq, hidden = 4, 8
+        g = OutputGatherer(gb, seq, hidden, torch.float32, "cpu")
+        start, count = shard_bounds(gb, world, rank)
+        local = (torch.arange(start * seq, (start + count) * seq, dtype=torch.float32)[:, None]
+                 + torch.zeros(hidden)[None, :])
+        if rank == fail_rank:
+            with pytest.raises(RuntimeError):
+                g.gather(local[:-1])  # wrong shard size is refused before any collective starts
+            out[rank] = "refused"
+            return
+        if fail_rank is None:
+            full = g.gather(local)
+            want = torch.arange(gb * seq, dtype=torch.float32)[:, None] + torch.zeros(hidden)[None, :]
+            out[rank] = bool(torch.equal(full, want))
+        else:
+            out[rank] = "skipped"  # the host learns of the peer's failure before launching the collective
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,gb", [(2, 8), (2, 7), (3, 8)])
+def test_gather_even_and_uneven(world, gb):
+    with mp.Manager() as m:
+        out = m.dict()
+        mp.spawn(_worker, args=(world, _free_port(), gb, None, out), nprocs=world, join=True)
+        assert dict(out) == {r: True for r in range(world)}
+
+
+def test_bad_shard_is_refused_on_the_host():
+    with mp.Manager() as m:
+        out = m.dict()
+        mp.spawn(_worker, args=(2, _free_port(), 8, 1, out), nprocs=2, join=True)
+        assert out[1] == "refused"

@@ -1,0 +1,103 @@
+"""Encoder drivers on the device against the CPU oracles.
+
+fp16 encoder  : within 1e-2 (relative to the activation scale) of the fp32 oracle encoder.
+int8 encoder  : every int8 GEMM of every layer is checked BIT-EXACTLY against the oracle on the int8
+                inputs the device really produced (teacher forcing), the int8 copies are the exact
+                quantization of the fp16 tensors beside them, and the final hidden states track the
+                oracle's int8 encoder and the fp32 encoder.
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import encoder_ref as ER
+from oracle import oracle as O
+from zenith_b200.calibrate import activation_scales_from_ranges, calibrate, quantize_weights
+from zenith_b200.encoder import EncoderConfig, Fp16Encoder, Int8Encoder, Int8Scales, init_params
+
+pytestmark = pytest.mark.gpu
+
+CFG = EncoderConfig(layers=3, hidden=256, heads=4, ffn=512, vocab=2000, max_pos=128)
+
+
+def rng(seed):
+    return np.random.default_rng(seed)
+
+
+def batch(seed, B=3, S=96):
+    r = rng(seed)
+    ids = r.integers(0, CFG.vocab, (B, S))
+    lens = (S - r.integers(0, 33, B)).astype(np.int32)
+    return ids, lens
+
+
+def tdev(ids, lens, cuda):
+    return torch.from_numpy(ids).to(cuda), torch.from_numpy(lens).to(cuda)
+
+
+@pytest.fixture(scope="module")
+def params():
+    return init_params(CFG, 7, random_affine=True)
+
+
+def test_fp16_encoder_tracks_fp32_oracle(cuda, params):
+    enc = Fp16Encoder(CFG, params, cuda)
+    ids, lens = batch(1)
+    got = enc.forward(*tdev(ids, lens, cuda)).float().cpu().numpy()
+    want = ER.encoder_fp32(CFG, params, ids, lens)
+    assert np.max(np.abs(got - want)) < 1e-2 * np.abs(want).max() * 3  # 3 layers of fp16 storage
+    assert np.mean(np.abs(got - want)) < 2e-3
+    # CUDA-graph replay reproduces the eager pass bit for bit
+    eager = enc.out.clone()
+    enc.capture(*ids.shape)
+    enc.set_inputs(*tdev(ids, lens, cuda))
+    assert torch.equal(enc.replay(), eager)
+
+
+def test_device_calibration_matches_oracle_calibration(cuda, params):
+    batches = [batch(100 + i) for i in range(4)]
+    dev_scales = calibrate(CFG, params, [tdev(i, l, cuda) for i, l in batches], cuda)
+    cpu_scales = ER.calibrate_on_oracle(CFG, params, batches, quantize_weights, activation_scales_from_ranges, Int8Scales)
+    for a, b in zip(dev_scales.act, cpu_scales.act):
+        for k in a:
+            assert abs(a[k] - b[k]) / b[k] < 0.03  # fp16 vs fp32 activations
+    for a, b in zip(dev_scales.weights, cpu_scales.weights):
+        for k in a:
+            assert np.array_equal(a[k][0], b[k][0]) and np.array_equal(a[k][1], b[k][1])
+
+
+def test_int8_encoder_gemms_bit_exact_and_output_tracks_oracle(cuda, params):
+    batches = [batch(100 + i) for i in range(4)]
+    scales = ER.calibrate_on_oracle(CFG, params, batches, quantize_weights, activation_scales_from_ranges, Int8Scales)
+    enc = Int8Encoder(CFG, params, scales, cuda)
+    ids, lens = batch(2)
+    np_ = lambda t: t.cpu().numpy()
+    for li, buf in enc.forward_layerwise(*tdev(ids, lens, cuda)):
+        a, wq, lp = scales.act[li], scales.weights[li], params["layers"][li]
+        # int8 copies == quantization of the fp16 tensor written beside them
+        assert np.array_equal(np_(buf["xq"]), O.quantize(np_(buf["x"].float()), a["x"]))
+        assert np.array_equal(np_(buf["ctxq"]), O.quantize(np_(buf["ctx"].float()), a["ctx"]))
+        assert np.array_equal(np_(buf["h1q"]), O.quantize(np_(buf["h1"].float()), a["h1"]))
+        # each GEMM, on the device's own int8 inputs, bit-exact through its fused epilogue
+        want = O.linear_int8(np_(buf["xq"]), wq["wqkv"][0], a["x"], wq["wqkv"][1], lp["bqkv"], "none", "f16")
+        assert np.array_equal(np_(buf["qkv"]).view(np.uint16), want.view(np.uint16))
+        want = O.linear_int8(np_(buf["ctxq"]), wq["wo"][0], a["ctx"], wq["wo"][1], lp["bo"], "none", "f16")
+        assert np.array_equal(np_(buf["ao"]).view(np.uint16), want.view(np.uint16))
+        want = O.linear_int8(np_(buf["h1q"]), wq["w1"][0], a["h1"], wq["w1"][1], lp["b1"], "gelu", "s8", a["gelu"])
+        assert np.array_equal(np_(buf["gq"]), want)
+        want = O.linear_int8(np_(buf["gq"]), wq["w2"][0], a["gelu"], wq["w2"][1], lp["b2"], "none", "f16")
+        assert np.array_equal(np_(buf["o"]).view(np.uint16), want.view(np.uint16))
+        # float kernels on the device's own inputs, within tolerance
+        f16 = lambda k: lp[k].astype(np.float16).astype(np.float32)
+        want = O.add_layernorm(np_(buf["ao"].float()), np_(buf["x"].float()), f16("ln1_g"), f16("ln1_b"), CFG.eps)
+        assert np.max(np.abs(np_(buf["h1"].float()) - want)) < 1e-2
+    got = np_(enc.out.float())
+    want8 = ER.encoder_int8(CFG, params, scales, ids, lens).astype(np.float32)
+    want32 = ER.encoder_fp32(CFG, params, ids, lens)
+    assert np.mean(np.abs(got - want8)) < 5e-3 and np.max(np.abs(got - want8)) < 0.1
+    assert np.mean(np.abs(got - want32)) < 3e-2
+    # graph replay == eager
+    eager = enc.out.clone()
+    enc.capture(*ids.shape)
+    enc.set_inputs(*tdev(ids, lens, cuda))
+    assert torch.equal(enc.replay(), eager)

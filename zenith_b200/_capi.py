@@ -26,8 +26,10 @@ SIGNATURES = {
     "zen_gemm_set_tile_n": [_i],
     "zen_linear_i8": [_p, _i64, _p, _i64, _i, _i, _i, _f, _p, _p, _i, _i, _f, _i, _p, _i64, _p],
     "zen_linear_f16": [_p, _i64, _p, _i64, _i, _i, _i, _p, _i, _i, _p, _i64, _p],
+    "zen_linear_f32": [_p, _i64, _p, _i64, _i, _i, _i, _p, _i, _p, _i64, _p],
     "zen_wmma_matmul_f16": [_p, _p, _p, _i, _i, _i, _p],
-    "zen_matmul_f32": [_p, _p, _p, _i, _i, _i, _p],
+    "zen_matmul_f32_workspace_bytes": [_i, _i],
+    "zen_matmul_f32": [_p, _p, _p, _i, _i, _i, _p, C.c_size_t, _p],
     "zen_gelu_f32": [_p, _p, _i64, _p],
     "zen_gelu_f16": [_p, _p, _i64, _p],
     "zen_relu_f32": [_p, _p, _i64, _p],
@@ -44,7 +46,7 @@ SIGNATURES = {
     "zen_convert_f16_to_f32": [_p, _p, _i64, _p],
     "zen_embed_layernorm_f16": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _f, _i, _i, _i, _i, _i, _f, _p],
 }
-_RESTYPES = {"zen_status_string": C.c_char_p}
+_RESTYPES = {"zen_status_string": C.c_char_p, "zen_matmul_f32_workspace_bytes": C.c_size_t}
 
 _lib = None
 

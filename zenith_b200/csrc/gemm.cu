@@ -71,6 +71,30 @@ static int run_gemm(const void* A, int64_t lda, const void* B, int64_t ldb, Gemm
   return launch_gemm<KIND, BN, STAGES, B_MN>(ta, tb, p, stream);
 }
 
+// out[c, r] = in[r, c] for a row-major [rows, cols] fp32 matrix, 32 x 32 tiles through shared memory.
+__global__ void __launch_bounds__(256) transpose_f32_kernel(const float* __restrict__ in, float* __restrict__ out,
+                                                            int rows, int cols) {
+  __shared__ float tile[32][33];
+  const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  for (int i = ty; i < 32; i += 8) {
+    const int r = r0 + i, c = c0 + tx;
+    if (r < rows && c < cols) tile[i][tx] = in[size_t(r) * cols + c];
+  }
+  __syncthreads();
+  for (int i = ty; i < 32; i += 8) {
+    const int c = c0 + i, r = r0 + tx;
+    if (r < rows && c < cols) out[size_t(c) * rows + r] = tile[tx][i];
+  }
+}
+
+static int launch_transpose_f32(const float* in, float* out, int rows, int cols, cudaStream_t s) {
+  dim3 grid((cols + 31) / 32, (rows + 31) / 32);
+  if (grid.y > 65535) return ZEN_ERR_UNSUPPORTED;
+  transpose_f32_kernel<<<grid, 256, 0, s>>>(in, out, rows, cols);
+  return cudaGetLastError() == cudaSuccess ? ZEN_OK : ZEN_ERR_LAUNCH;
+}
+
 }  // namespace zen
 
 using namespace zen;
@@ -143,6 +167,24 @@ int zen_linear_f16(const void* x, int64_t ldx, const void* w, int64_t ldw, int M
   }
 }
 
+int zen_linear_f32(const float* x, int64_t ldx, const float* w, int64_t ldw, int M, int N, int K, const float* bias,
+                   int act, float* out, int64_t ldo, void* stream) {
+  if (!x || !w || !out || M <= 0 || N <= 0 || K <= 0) return ZEN_ERR_INVALID_ARG;
+  if (act < ZEN_ACT_NONE || act > ZEN_ACT_RELU) return ZEN_ERR_INVALID_ARG;
+  if (K % 4 || ldx % 4 || ldw % 4 || ldx < K || ldw < K || ldo < N) return ZEN_ERR_UNSUPPORTED;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K;
+  p.out = out; p.ldo = ldo; p.out_dtype = ZEN_DT_F32; p.act = act;
+  p.x_scale = 1.0f; p.out_scale = 1.0f; p.w_scale = nullptr; p.bias = bias;
+  static const int allowed[] = {64, 128, 256};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (pick_bn(M, N, allowed, 3)) {
+    case 64: return run_gemm<KIND_TF32, 64, 8, false>(x, ldx, w, ldw, p, s);
+    case 128: return run_gemm<KIND_TF32, 128, 6, false>(x, ldx, w, ldw, p, s);
+    default: return run_gemm<KIND_TF32, 256, 4, false>(x, ldx, w, ldw, p, s);
+  }
+}
+
 int zen_wmma_matmul_f16(const void* A, const void* B, float* C, int M, int N, int K, void* stream) {
   if (!A || !B || !C || M <= 0 || N <= 0 || K <= 0) return ZEN_ERR_INVALID_ARG;
   if (K % 8 || N % 8) return ZEN_ERR_UNSUPPORTED;
@@ -159,20 +201,22 @@ int zen_wmma_matmul_f16(const void* A, const void* B, float* C, int M, int N, in
   }
 }
 
-int zen_matmul_f32(const float* A, const float* B, float* C, int M, int N, int K, void* stream) {
-  if (!A || !B || !C || M <= 0 || N <= 0 || K <= 0) return ZEN_ERR_INVALID_ARG;
-  if (K % 4 || N % 4) return ZEN_ERR_UNSUPPORTED;
-  GemmParams p{};
-  p.M = M; p.N = N; p.K = K;
-  p.out = C; p.ldo = N; p.out_dtype = ZEN_DT_F32; p.act = ZEN_ACT_NONE;
-  p.x_scale = 1.0f; p.out_scale = 1.0f;
-  static const int allowed[] = {64, 128, 256};
+size_t zen_matmul_f32_workspace_bytes(int N, int K) {
+  if (N <= 0 || K <= 0) return 0;
+  return size_t(N) * size_t(K) * sizeof(float);
+}
+
+int zen_matmul_f32(const float* A, const float* B, float* C, int M, int N, int K, void* workspace,
+                   size_t workspace_bytes, void* stream) {
+  if (!A || !B || !C || !workspace || M <= 0 || N <= 0 || K <= 0) return ZEN_ERR_INVALID_ARG;
+  if (K % 4) return ZEN_ERR_UNSUPPORTED;
+  if (workspace_bytes < zen_matmul_f32_workspace_bytes(N, K) || reinterpret_cast<uintptr_t>(workspace) % 16)
+    return ZEN_ERR_INVALID_ARG;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  switch (pick_bn(M, N, allowed, 3)) {
-    case 64: return run_gemm<KIND_TF32, 64, 8, true>(A, K, B, N, p, s);
-    case 128: return run_gemm<KIND_TF32, 128, 6, true>(A, K, B, N, p, s);
-    default: return run_gemm<KIND_TF32, 256, 4, true>(A, K, B, N, p, s);
-  }
+  float* Bt = static_cast<float*>(workspace);
+  int st = launch_transpose_f32(B, Bt, K, N, s);
+  if (st != ZEN_OK) return st;
+  return zen_linear_f32(A, K, Bt, K, M, N, K, nullptr, ZEN_ACT_NONE, C, N, stream);
 }
 
 }  // extern "C"

@@ -1,0 +1,77 @@
+"""Multi-GPU execution of the encoder: batch-sharded replicas, one process per GPU.
+
+Every sequence is independent through the whole encoder (LayerNorm is per token, attention per
+sequence), so the global batch is split by rank, each rank holds a full weight replica and no
+collective sits inside a layer.  The only exchange is the gather of the final hidden states
+(``all_gather`` over NCCL on GPUs, gloo in CPU tests).  The reference has no distributed code; its
+one multi-GPU helper runs independent replicas from a thread pool (benchmarks/mlperf_suite.py:750-850).
+"""
+from __future__ import annotations
+
+import os
+
+import torch
+import torch.distributed as dist
+
+
+def shard_bounds(global_batch: int, world_size: int, rank: int) -> tuple[int, int]:
+    """``(start, count)`` of this rank's slice; the first ``global_batch % world_size`` ranks get one more."""
+    if world_size <= 0 or not 0 <= rank < world_size:
+        raise ValueError("bad rank / world size")
+    base, extra = divmod(global_batch, world_size)
+    count = base + (1 if rank < extra else 0)
+    start = rank * base + min(rank, extra)
+    return start, count
+
+
+def init_from_env(backend: str | None = None) -> tuple[int, int, int]:
+    """Initialise ``torch.distributed`` from torchrun's environment; returns (rank, local_rank, world)."""
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1 and not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29500")
+        if backend is None:
+            backend = "nccl" if torch.cuda.is_available() else "gloo"
+        kwargs = {}
+        if backend == "nccl":
+            torch.cuda.set_device(local_rank)
+            kwargs["device_id"] = torch.device("cuda", local_rank)
+        dist.init_process_group(backend=backend, rank=rank, world_size=world, **kwargs)
+    return rank, local_rank, world
+
+
+class OutputGatherer:
+    """Gathers per-rank hidden states ``[count_r * seq, hidden]`` into one ``[global_batch * seq, hidden]``
+    buffer that is allocated once.  Shards may be uneven: each rank's rows land at its own offset."""
+
+    def __init__(self, global_batch: int, seq: int, hidden: int, dtype, device, group=None):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.seq, self.hidden = seq, hidden
+        self.bounds = [shard_bounds(global_batch, self.world, r) for r in range(self.world)]
+        self.full = torch.empty((global_batch * seq, hidden), dtype=dtype, device=device)
+        self.even = len({c for _, c in self.bounds}) == 1
+        self.views = [self.full[s * seq:(s + c) * seq] for s, c in self.bounds]
+        # collectives need equal contributions: uneven shards travel padded to the largest shard
+        self.max_rows = max(c for _, c in self.bounds) * seq
+        if not self.even:
+            self.padded = torch.zeros((self.world * self.max_rows, hidden), dtype=dtype, device=device)
+            self.send = torch.zeros((self.max_rows, hidden), dtype=dtype, device=device)
+
+    def gather(self, local: torch.Tensor) -> torch.Tensor:
+        start, count = self.bounds[self.rank]
+        if tuple(local.shape) != (count * self.seq, self.hidden):
+            raise RuntimeError(f"rank {self.rank}: expected {(count * self.seq, self.hidden)}, got {tuple(local.shape)}")
+        if self.world == 1:
+            self.full.copy_(local)
+        elif self.even:
+            dist.all_gather_into_tensor(self.full, local.contiguous(), group=self.group)
+        else:
+            self.send[:count * self.seq].copy_(local)
+            dist.all_gather_into_tensor(self.padded, self.send, group=self.group)
+            for r, view in enumerate(self.views):
+                view.copy_(self.padded[r * self.max_rows:r * self.max_rows + view.shape[0]])
+        return self.full

@@ -1,0 +1,335 @@
+"""BERT-style post-LN encoder drivers over the sm_100a kernels: fp16 and W8A8 int8.
+
+These play the role of the reference's hand-written encoder drivers
+(benchmarks/bert_hybrid.py:96-145, benchmarks/bert_fp16_full.py:96-145): a fixed sequence of
+kernel launches per layer, here 7 (int8) or 7 (fp16) launches instead of ~27, with every layout
+change and elementwise op folded into a GEMM epilogue, the attention kernel or the LayerNorm
+kernel.  All buffers of a (batch, seq) shape are allocated once; ``forward`` only launches, so a
+whole pass can be captured in a CUDA graph (``capture`` / ``replay``).
+
+W8A8 dataflow per layer (fp16 residual stream ``x``, int8 copies ``*_q``, one per-tensor
+activation scale at each of the four GEMM inputs):
+
+    x_q  --QKV GEMM s8 (dequant+bias -> fp16 [T,3H])--> q,k,v --attention (fp16, key-padding mask,
+    int8 copy at s_ctx)--> ctx_q --out GEMM (dequant+bias -> fp16)--> +x, LayerNorm (fp16 + int8 copy
+    at s_h1) --> h1_q --FFN1 GEMM (dequant+bias+GELU+requant at s_gelu)--> g_q --FFN2 GEMM (dequant+
+    bias -> fp16)--> +h1, LayerNorm (fp16 + int8 copy at the next layer's s_x).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from . import _capi, ops
+from ._capi import ACT_GELU, ACT_NONE, DT_F16, DT_S8, ROUND_NEAREST_EVEN
+
+
+@dataclass
+class EncoderConfig:
+    layers: int = 12
+    hidden: int = 768
+    heads: int = 12
+    ffn: int = 3072
+    vocab: int = 30522
+    max_pos: int = 512
+    type_vocab: int = 2
+    eps: float = 1e-12
+
+    @property
+    def head_dim(self) -> int:
+        return self.hidden // self.heads
+
+
+BERT_BASE = EncoderConfig()
+BERT_LARGE = EncoderConfig(layers=24, hidden=1024, heads=16, ffn=4096)
+
+LAYER_WEIGHTS = ("wqkv", "wo", "w1", "w2")
+ACT_POINTS = ("x", "ctx", "h1", "gelu")
+
+
+def init_params(cfg: EncoderConfig, seed: int = 1234, random_affine: bool = False) -> dict:
+    """Random-init fp32 master weights: N(0, 0.02) matrices and embeddings, zero biases, unit
+    LayerNorm — or, with ``random_affine``, small random biases and LayerNorm parameters."""
+    rng = np.random.default_rng(seed)
+    H, F = cfg.hidden, cfg.ffn
+
+    def mat(*shape):
+        return (rng.standard_normal(shape) * 0.02).astype(np.float32)
+
+    def bias(n):
+        return (rng.standard_normal(n) * 0.02).astype(np.float32) if random_affine else np.zeros(n, np.float32)
+
+    def gamma(n):
+        return (1 + 0.1 * rng.standard_normal(n)).astype(np.float32) if random_affine else np.ones(n, np.float32)
+
+    def beta(n):
+        return (0.1 * rng.standard_normal(n)).astype(np.float32) if random_affine else np.zeros(n, np.float32)
+
+    p = {"word": mat(cfg.vocab, H), "pos": mat(cfg.max_pos, H), "type": mat(cfg.type_vocab, H),
+         "emb_ln_g": gamma(H), "emb_ln_b": beta(H), "layers": []}
+    for _ in range(cfg.layers):
+        p["layers"].append({
+            "wqkv": mat(3 * H, H), "bqkv": bias(3 * H), "wo": mat(H, H), "bo": bias(H),
+            "ln1_g": gamma(H), "ln1_b": beta(H), "w1": mat(F, H), "b1": bias(F), "w2": mat(H, F), "b2": bias(H),
+            "ln2_g": gamma(H), "ln2_b": beta(H)})
+    return p
+
+
+def _dev(a, dtype, device):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(device=device, dtype=dtype)
+
+
+class _EncoderBase:
+    """Shared plumbing: embedding tables, per-shape buffers, the launch list, CUDA-graph capture."""
+
+    def __init__(self, cfg: EncoderConfig, params: dict, device):
+        if cfg.head_dim not in (64, 128):
+            raise RuntimeError("head_dim must be 64 or 128")
+        self.cfg = cfg
+        self.device = torch.device(device)
+        d = self.device
+        self.word = _dev(params["word"], torch.float16, d)
+        self.pos = _dev(params["pos"], torch.float16, d)
+        self.type = _dev(params["type"], torch.float16, d)
+        self.emb_g = _dev(params["emb_ln_g"], torch.float16, d)
+        self.emb_b = _dev(params["emb_ln_b"], torch.float16, d)
+        self._shape = None
+        self._launches: list = []
+        self._graph = None
+        self.launches_per_forward = 0
+
+    # -- per-shape state --------------------------------------------------------------------
+    def _prepare(self, B: int, S: int) -> None:
+        if self._shape == (B, S):
+            return
+        if S > self.cfg.max_pos:
+            raise RuntimeError("sequence longer than the position table")
+        self._shape = (B, S)
+        self._graph = None
+        d = self.device
+        self.ids = torch.zeros(B * S, dtype=torch.int32, device=d)
+        self.kv_lens = torch.full((B,), S, dtype=torch.int32, device=d)
+        self._launches = []
+        self._build(B, S)
+        self.launches_per_forward = len(self._launches)
+
+    def _add(self, fn: str, *args) -> None:
+        self._launches.append((getattr(_capi.lib(), fn), fn, args))
+
+    def _run(self) -> None:
+        stream = torch.cuda.current_stream().cuda_stream
+        for f, name, args in self._launches:
+            st = f(*args, stream)
+            if st != 0:
+                _capi.check(name, st)
+        ops.launch_count += len(self._launches)
+
+    # -- public ------------------------------------------------------------------------------
+    def set_inputs(self, ids, kv_lens=None) -> None:
+        """Copy token ids ([B,S] integer tensor, any device) and key lengths into the static buffers."""
+        B, S = ids.shape
+        self._prepare(B, S)
+        self.ids.copy_(ids.reshape(-1), non_blocking=True)
+        if kv_lens is not None:
+            self.kv_lens.copy_(kv_lens, non_blocking=True)
+        else:
+            self.kv_lens.fill_(S)
+
+    def forward(self, ids, kv_lens=None) -> torch.Tensor:
+        """Hidden states ``[B*S, hidden]`` fp16 (a static buffer, overwritten by the next call)."""
+        self.set_inputs(ids, kv_lens)
+        self._run()
+        return self.out
+
+    def capture(self, B: int, S: int) -> None:
+        """Capture one pass for shape (B, S) into a CUDA graph; feed it with ``set_inputs`` + ``replay``."""
+        self._prepare(B, S)
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            self._run()  # warm-up: sets kernel attributes, loads modules
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self._run()
+        self._graph = g
+
+    def replay(self) -> torch.Tensor:
+        if self._graph is None:
+            raise RuntimeError("capture() first")
+        self._graph.replay()
+        ops.launch_count += len(self._launches)
+        return self.out
+
+
+class Fp16Encoder(_EncoderBase):
+    """fp16 weights and activations, fp32 accumulation and statistics."""
+
+    def __init__(self, cfg: EncoderConfig, params: dict, device="cuda:0"):
+        super().__init__(cfg, params, device)
+        d = self.device
+        self.layers = []
+        for lp in params["layers"]:
+            L = {k: _dev(lp[k], torch.float16, d) for k in LAYER_WEIGHTS}
+            L.update({k: _dev(lp[k], torch.float32, d) for k in ("bqkv", "bo", "b1", "b2")})
+            L.update({k: _dev(lp[k], torch.float16, d) for k in ("ln1_g", "ln1_b", "ln2_g", "ln2_b")})
+            self.layers.append(L)
+        self.taps: dict | None = None  # filled by forward_with_taps
+
+    def _build(self, B: int, S: int) -> None:
+        cfg, d = self.cfg, self.device
+        T, H, F, nh, hd = B * S, cfg.hidden, cfg.ffn, cfg.heads, cfg.head_dim
+        f16 = dict(dtype=torch.float16, device=d)
+        self.x = [torch.empty((T, H), **f16) for _ in range(2)]
+        self.qkv = torch.empty((T, 3 * H), **f16)
+        self.ctx = torch.empty((T, H), **f16)
+        self.ao = torch.empty((T, H), **f16)
+        self.h1 = torch.empty((T, H), **f16)
+        self.g = torch.empty((T, F), **f16)
+        self.o = torch.empty((T, H), **f16)
+        self._add("zen_embed_layernorm_f16", self.ids.data_ptr(), None, self.word.data_ptr(), self.pos.data_ptr(),
+                  self.type.data_ptr(), self.emb_g.data_ptr(), self.emb_b.data_ptr(), self.x[0].data_ptr(), None, 1.0,
+                  ROUND_NEAREST_EVEN, T, S, H, cfg.vocab, cfg.eps)
+        qs = (S * 3 * H, hd, 3 * H)
+        os_ = (S * H, hd, H)
+        cur = 0
+        for L in self.layers:
+            x, xn = self.x[cur], self.x[cur ^ 1]
+            self._add("zen_linear_f16", x.data_ptr(), H, L["wqkv"].data_ptr(), H, T, 3 * H, H, L["bqkv"].data_ptr(),
+                      ACT_NONE, DT_F16, self.qkv.data_ptr(), 3 * H)
+            self._add("zen_flash_attention_f16", self.qkv.data_ptr(), self.qkv.data_ptr() + 2 * H,
+                      self.qkv.data_ptr() + 4 * H, self.ctx.data_ptr(), None, 1.0, B, nh, S, hd, *qs, *qs, *qs, *os_,
+                      self.kv_lens.data_ptr(), 0, 1.0 / math.sqrt(hd))
+            self._add("zen_linear_f16", self.ctx.data_ptr(), H, L["wo"].data_ptr(), H, T, H, H, L["bo"].data_ptr(),
+                      ACT_NONE, DT_F16, self.ao.data_ptr(), H)
+            self._add("zen_add_layernorm_f16", self.ao.data_ptr(), x.data_ptr(), L["ln1_g"].data_ptr(),
+                      L["ln1_b"].data_ptr(), self.h1.data_ptr(), None, 1.0, ROUND_NEAREST_EVEN, T, H, cfg.eps)
+            self._add("zen_linear_f16", self.h1.data_ptr(), H, L["w1"].data_ptr(), H, T, F, H, L["b1"].data_ptr(),
+                      ACT_GELU, DT_F16, self.g.data_ptr(), F)
+            self._add("zen_linear_f16", self.g.data_ptr(), F, L["w2"].data_ptr(), F, T, H, F, L["b2"].data_ptr(),
+                      ACT_NONE, DT_F16, self.o.data_ptr(), H)
+            self._add("zen_add_layernorm_f16", self.o.data_ptr(), self.h1.data_ptr(), L["ln2_g"].data_ptr(),
+                      L["ln2_b"].data_ptr(), xn.data_ptr(), None, 1.0, ROUND_NEAREST_EVEN, T, H, cfg.eps)
+            cur ^= 1
+        self.out = self.x[cur]
+
+    def forward_with_taps(self, ids, kv_lens=None) -> dict:
+        """One pass that also returns, per layer, (min, max) of the four tensors that feed a GEMM in the
+        W8A8 dataflow: layer input ``x``, attention output ``ctx``, post-LN ``h1`` and GELU output
+        ``gelu``.  Cold path used by calibration: runs layer by layer and reads back 8 floats per layer."""
+        self.set_inputs(ids, kv_lens)
+        stream = torch.cuda.current_stream().cuda_stream
+        taps = {p: [] for p in ACT_POINTS}
+        per_layer = 7
+        f, name, args = self._launches[0]
+        _capi.check(name, f(*args, stream))
+        cur = 0
+        for li in range(len(self.layers)):
+            taps["x"].append(torch.aminmax(self.x[cur]))
+            for f, name, args in self._launches[1 + li * per_layer: 1 + (li + 1) * per_layer]:
+                _capi.check(name, f(*args, stream))
+            taps["ctx"].append(torch.aminmax(self.ctx))
+            taps["h1"].append(torch.aminmax(self.h1))
+            taps["gelu"].append(torch.aminmax(self.g))
+            cur ^= 1
+        ops.launch_count += len(self._launches)
+        return {p: [(float(lo), float(hi)) for lo, hi in v] for p, v in taps.items()}
+
+
+@dataclass
+class Int8Scales:
+    """Per-layer activation scales (one float per point) and the quantized weights."""
+
+    act: list  # [{"x":..,"ctx":..,"h1":..,"gelu":..}] per layer
+    weights: list  # [{"wqkv": (int8 [N,K], float32 [N]), ...}] per layer
+
+
+class Int8Encoder(_EncoderBase):
+    """W8A8 encoder: int8 GEMM operands, int32 accumulation, fp16 residual stream / LayerNorm / softmax."""
+
+    def __init__(self, cfg: EncoderConfig, params: dict, scales: Int8Scales, device="cuda:0"):
+        super().__init__(cfg, params, device)
+        d = self.device
+        self.act_scales = scales.act
+        self.layers = []
+        for lp, wq in zip(params["layers"], scales.weights):
+            L = {}
+            for k in LAYER_WEIGHTS:
+                L[k] = _dev(wq[k][0], torch.int8, d)
+                L[k + "_s"] = _dev(wq[k][1], torch.float32, d)
+            L.update({k: _dev(lp[k], torch.float32, d) for k in ("bqkv", "bo", "b1", "b2")})
+            L.update({k: _dev(lp[k], torch.float16, d) for k in ("ln1_g", "ln1_b", "ln2_g", "ln2_b")})
+            self.layers.append(L)
+
+    def _build(self, B: int, S: int) -> None:
+        cfg, d = self.cfg, self.device
+        T, H, F, nh, hd = B * S, cfg.hidden, cfg.ffn, cfg.heads, cfg.head_dim
+        f16 = dict(dtype=torch.float16, device=d)
+        s8 = dict(dtype=torch.int8, device=d)
+        self.x = [torch.empty((T, H), **f16) for _ in range(2)]
+        self.xq = [torch.empty((T, H), **s8) for _ in range(2)]
+        self.qkv = torch.empty((T, 3 * H), **f16)
+        self.ctx = torch.empty((T, H), **f16)
+        self.ctxq = torch.empty((T, H), **s8)
+        self.ao = torch.empty((T, H), **f16)
+        self.h1 = torch.empty((T, H), **f16)
+        self.h1q = torch.empty((T, H), **s8)
+        self.gq = torch.empty((T, F), **s8)
+        self.o = torch.empty((T, H), **f16)
+        sc = self.act_scales
+        self._add("zen_embed_layernorm_f16", self.ids.data_ptr(), None, self.word.data_ptr(), self.pos.data_ptr(),
+                  self.type.data_ptr(), self.emb_g.data_ptr(), self.emb_b.data_ptr(), self.x[0].data_ptr(),
+                  self.xq[0].data_ptr(), sc[0]["x"], ROUND_NEAREST_EVEN, T, S, H, cfg.vocab, cfg.eps)
+        qs = (S * 3 * H, hd, 3 * H)
+        os_ = (S * H, hd, H)
+        cur = 0
+        n_layers = len(self.layers)
+        for li, L in enumerate(self.layers):
+            a = sc[li]
+            x, xq, xn, xqn = self.x[cur], self.xq[cur], self.x[cur ^ 1], self.xq[cur ^ 1]
+            last = li == n_layers - 1
+            self._add("zen_linear_i8", xq.data_ptr(), H, L["wqkv"].data_ptr(), H, T, 3 * H, H, a["x"],
+                      L["wqkv_s"].data_ptr(), L["bqkv"].data_ptr(), ACT_NONE, DT_F16, 1.0, ROUND_NEAREST_EVEN,
+                      self.qkv.data_ptr(), 3 * H)
+            self._add("zen_flash_attention_f16", self.qkv.data_ptr(), self.qkv.data_ptr() + 2 * H,
+                      self.qkv.data_ptr() + 4 * H, self.ctx.data_ptr(), self.ctxq.data_ptr(), a["ctx"], B, nh, S, hd,
+                      *qs, *qs, *qs, *os_, self.kv_lens.data_ptr(), 0, 1.0 / math.sqrt(hd))
+            self._add("zen_linear_i8", self.ctxq.data_ptr(), H, L["wo"].data_ptr(), H, T, H, H, a["ctx"],
+                      L["wo_s"].data_ptr(), L["bo"].data_ptr(), ACT_NONE, DT_F16, 1.0, ROUND_NEAREST_EVEN,
+                      self.ao.data_ptr(), H)
+            self._add("zen_add_layernorm_f16", self.ao.data_ptr(), x.data_ptr(), L["ln1_g"].data_ptr(),
+                      L["ln1_b"].data_ptr(), self.h1.data_ptr(), self.h1q.data_ptr(), a["h1"], ROUND_NEAREST_EVEN, T, H,
+                      cfg.eps)
+            self._add("zen_linear_i8", self.h1q.data_ptr(), H, L["w1"].data_ptr(), H, T, F, H, a["h1"],
+                      L["w1_s"].data_ptr(), L["b1"].data_ptr(), ACT_GELU, DT_S8, a["gelu"], ROUND_NEAREST_EVEN,
+                      self.gq.data_ptr(), F)
+            self._add("zen_linear_i8", self.gq.data_ptr(), F, L["w2"].data_ptr(), F, T, H, F, a["gelu"],
+                      L["w2_s"].data_ptr(), L["b2"].data_ptr(), ACT_NONE, DT_F16, 1.0, ROUND_NEAREST_EVEN,
+                      self.o.data_ptr(), H)
+            self._add("zen_add_layernorm_f16", self.o.data_ptr(), self.h1.data_ptr(), L["ln2_g"].data_ptr(),
+                      L["ln2_b"].data_ptr(), xn.data_ptr(), None if last else xqn.data_ptr(),
+                      1.0 if last else sc[li + 1]["x"], ROUND_NEAREST_EVEN, T, H, cfg.eps)
+            cur ^= 1
+        self.out = self.x[cur]
+
+    def forward_layerwise(self, ids, kv_lens=None):
+        """Generator for tests: runs the pass one layer at a time and yields ``(layer, buffers)`` after
+        each layer, where ``buffers`` are the live device tensors of that layer (inputs and outputs of
+        every kernel), so that each kernel can be checked in isolation on the inputs it really saw."""
+        self.set_inputs(ids, kv_lens)
+        stream = torch.cuda.current_stream().cuda_stream
+        f, name, args = self._launches[0]
+        _capi.check(name, f(*args, stream))
+        cur = 0
+        for li in range(len(self.layers)):
+            for f, name, args in self._launches[1 + li * 7: 1 + (li + 1) * 7]:
+                _capi.check(name, f(*args, stream))
+            torch.cuda.synchronize()
+            yield li, {"x": self.x[cur], "xq": self.xq[cur], "qkv": self.qkv, "ctx": self.ctx, "ctxq": self.ctxq,
+                       "ao": self.ao, "h1": self.h1, "h1q": self.h1q, "gq": self.gq, "o": self.o,
+                       "x_next": self.x[cur ^ 1], "xq_next": self.xq[cur ^ 1]}
+            cur ^= 1

@@ -41,6 +41,11 @@ def _ptr(t) -> int | None:
     return None if t is None else t.data_ptr()
 
 
+def launch_count_add(n: int) -> None:
+    global launch_count
+    launch_count += n
+
+
 def _call(fn: str, *args) -> None:
     global launch_count
     _capi.call(fn, *args)
@@ -111,6 +116,23 @@ def linear_fp16(x, w, bias=None, *, act="none", out_dtype=torch.float16, out=Non
     return out
 
 
+def linear_fp32(x, w, bias=None, *, act="none"):
+    """``act(x @ w.T + bias)`` in fp32 storage, TF32 tensor-core math (python/src/bindings.cpp:1454-1496)."""
+    _require(x, "x", torch.float32, 2)
+    _require(w, "w", torch.float32, 2)
+    M, K = x.shape
+    N, K2 = w.shape
+    if K != K2:
+        raise RuntimeError(f"inner dimensions differ: x {tuple(x.shape)} vs w {tuple(w.shape)}")
+    if bias is not None:
+        _require(bias, "bias", torch.float32, 1)
+    out = torch.empty((M, N), dtype=torch.float32, device=x.device)
+    if M and N:
+        _call("zen_linear_f32", x.data_ptr(), K, w.data_ptr(), K, M, N, K, _ptr(bias), _ACT[act], out.data_ptr(), N,
+              _stream())
+    return out
+
+
 def wmma_matmul(a, b):
     """``C f32[M,N] = A f16[M,K] @ B f16[K,N]`` (core/bindings/cuda_bindings.cpp:110-132)."""
     if not a.is_cuda or not b.is_cuda:
@@ -147,7 +169,11 @@ def matmul_f32(a, b):
     N = b.shape[1]
     c = torch.empty((M, N), dtype=torch.float32, device=a.device)
     if M and N:
-        _call("zen_matmul_f32", a.data_ptr(), b.data_ptr(), c.data_ptr(), M, N, K, _stream())
+        nbytes = _capi.lib().zen_matmul_f32_workspace_bytes(N, K)
+        workspace = torch.empty(nbytes, dtype=torch.uint8, device=a.device)  # B transposed to [N, K]
+        _call("zen_matmul_f32", a.data_ptr(), b.data_ptr(), c.data_ptr(), M, N, K, workspace.data_ptr(), nbytes,
+              _stream())
+        launch_count_add(1)
     return c
 
 
