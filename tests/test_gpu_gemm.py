@@ -102,8 +102,8 @@ def test_int8_linearity_and_checksum_at_encoder_size(cuda):
     w = torch.randint(-128, 128, (3072, 768), dtype=torch.int8, generator=g).to(cuda)
     f = lambda t: ops.linear_int8(t, w, 1.0, out_dtype=torch.int32)
     assert torch.equal(f(a) + f(b2), f(a + b2))  # integer GEMM is linear (a + b stays in int8 range)
-    colsum = w.to(torch.int64).sum(dim=0)  # [K]
-    assert torch.equal(f(a).to(torch.int64).sum(dim=1), a.to(torch.int64) @ colsum)
+    colsum = w.double().sum(dim=0)  # [K]; every value below is an integer < 2^53, exact in fp64
+    assert torch.equal(f(a).double().sum(dim=1), a.double() @ colsum)
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 64, 64), (256, 320, 520), (100, 72, 80), (4096, 768, 768), (1, 8, 8)])

@@ -38,10 +38,10 @@ struct FaParams {
   int q_perm[3], k_perm[3], v_perm[3];
 };
 
-template <int D>
+template <int D, int KV_STAGES>
 constexpr size_t fa_smem_bytes() {
-  // Q + 2 K + 2 V tiles (128 x D fp16 each) + P (128 x 128 fp16) + control + alignment slack
-  return size_t(5) * FA_BQ * D * 2 + FA_BQ * FA_BKV * 2 + 256 + 1024;
+  // Q + KV_STAGES x (K + V) tiles (128 x D fp16 each) + P (128 x 128 fp16) + control + alignment slack
+  return size_t(1 + 2 * KV_STAGES) * FA_BQ * D * 2 + FA_BQ * FA_BKV * 2 + 256 + 1024;
 }
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -60,8 +60,11 @@ __device__ __forceinline__ void fa_tma_tile(uint8_t* dst, const CUtensorMap* map
   tma_load_4d(dst, map, bar, c[0], c[1], c[2], c[3]);
 }
 
-template <int D>
-__global__ void __launch_bounds__(FA_THREADS, 1)
+// KV_STAGES = 2 double-buffers K and V for long sequences; KV_STAGES = 1 serves sequences of at most
+// one key block (S <= 128, the encoder's case) with a footprint small enough for two CTAs per SM, so
+// that one CTA's softmax overlaps the other's loads and MMAs.
+template <int D, int KV_STAGES>
+__global__ void __launch_bounds__(FA_THREADS, (D == 64 && KV_STAGES == 1) ? 2 : 1)
 flash_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                   const __grid_constant__ CUtensorMap tmap_v, const FaParams p) {
   constexpr int DC = D / 64;                 // 128-byte column chunks per row
@@ -74,9 +77,9 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint8_t* sQ = smem;
-  uint8_t* sK = sQ + TILE_BYTES;      // 2 stages
-  uint8_t* sV = sK + 2 * TILE_BYTES;  // 2 stages
-  uint8_t* sP = sV + 2 * TILE_BYTES;  // 2 chunks of 64 keys
+  uint8_t* sK = sQ + TILE_BYTES;              // KV_STAGES stages
+  uint8_t* sV = sK + KV_STAGES * TILE_BYTES;  // KV_STAGES stages
+  uint8_t* sP = sV + KV_STAGES * TILE_BYTES;  // 2 chunks of 64 keys
   uint8_t* ctrl = sP + FA_BQ * FA_BKV * 2;
   uint64_t* q_full = reinterpret_cast<uint64_t*>(ctrl);
   uint64_t* k_full = q_full + 1;    // [2]
@@ -137,8 +140,8 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
 #pragma unroll
       for (int dc = 0; dc < DC; ++dc) fa_tma_tile(sQ + dc * CHUNK_BYTES, &tmap_q, q_full, p.q_perm, dc * 64, q0, h, b);
       for (int j = 0; j < n_blocks && ok; ++j) {
-        const int st = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
+        const int st = j % KV_STAGES;
+        const uint32_t ph = (j / KV_STAGES) & 1;
         if (!mbar_wait(&k_empty[st], ph ^ 1u, abort_flag)) { ok = false; break; }
         mbar_arrive_expect_tx(&k_full[st], TILE_BYTES);
 #pragma unroll
@@ -158,8 +161,8 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
     // ---------------------------------------------------------------- MMA issuer
     if (lane == 0 && n_blocks > 0) {
       auto issue_qk = [&](int j) -> bool {
-        const int st = j & 1;
-        if (!mbar_wait(&k_full[st], (j >> 1) & 1, abort_flag)) return false;
+        const int st = j % KV_STAGES;
+        if (!mbar_wait(&k_full[st], (j / KV_STAGES) & 1, abort_flag)) return false;
         tc_fence_after_sync();
         const uint32_t qa = smem_u32(sQ);
         const uint32_t ka = smem_u32(sK + st * TILE_BYTES);
@@ -176,12 +179,12 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       bool ok = mbar_wait(q_full, 0, abort_flag);
       if (ok) ok = issue_qk(0);
       for (int j = 0; j < n_blocks && ok; ++j) {
-        const int st = j & 1;
+        const int st = j % KV_STAGES;
         // P(j) is in shared memory, S(j) and O_blk(j-1) have been read by every softmax thread
         if (!mbar_wait(p_full, j & 1, abort_flag)) break;
         tc_fence_after_sync();
         if (j + 1 < n_blocks && !issue_qk(j + 1)) break;
-        if (!mbar_wait(&v_full[st], (j >> 1) & 1, abort_flag)) break;
+        if (!mbar_wait(&v_full[st], (j / KV_STAGES) & 1, abort_flag)) break;
         tc_fence_after_sync();
         const uint32_t pa = smem_u32(sP);
         const uint32_t va = smem_u32(sV + st * TILE_BYTES);
@@ -351,11 +354,11 @@ static int encode_qkv_map(CUtensorMap* map, const void* base, int B, int H, int 
   return encode_tmap(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, base, gd, gs, bx);
 }
 
-template <int D>
+template <int D, int KV_STAGES>
 static int launch_fa(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FaParams& p,
                      cudaStream_t s) {
-  auto kernel = flash_attn_kernel<D>;
-  constexpr size_t smem = fa_smem_bytes<D>();
+  auto kernel = flash_attn_kernel<D, KV_STAGES>;
+  constexpr size_t smem = fa_smem_bytes<D, KV_STAGES>();
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) {
@@ -396,5 +399,6 @@ extern "C" int zen_flash_attention_f16(const void* q, const void* k, const void*
   if (st == ZEN_OK) st = encode_qkv_map(&tv, v, B, H, S, D, v_sb, v_sh, v_ss, p.v_perm);
   if (st != ZEN_OK) return st;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  return D == 64 ? launch_fa<64>(tq, tk, tv, p, s) : launch_fa<128>(tq, tk, tv, p, s);
+  if (S <= FA_BKV) return D == 64 ? launch_fa<64, 1>(tq, tk, tv, p, s) : launch_fa<128, 1>(tq, tk, tv, p, s);
+  return D == 64 ? launch_fa<64, 2>(tq, tk, tv, p, s) : launch_fa<128, 2>(tq, tk, tv, p, s);
 }

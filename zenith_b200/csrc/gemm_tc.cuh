@@ -4,8 +4,8 @@
 //
 //   warp 0      : TMA producer  — 128-byte-swizzled tiles of A and B into a STAGES-deep ring
 //   warp 1      : allocates TMEM, issues tcgen05.mma (one lane), commits stage / accumulator barriers
-//   warps 2..5  : epilogue — tcgen05.ld of the accumulator (each warp its own 32-lane quadrant),
-//                 dequant / bias / activation / requant, 16-byte global stores
+//   warps 2..9  : epilogue — tcgen05.ld of the accumulator (two warps per 32-lane TMEM quadrant, taking
+//                 alternate 32-column chunks), dequant / bias / activation / requant, 16-byte stores
 //
 // TMEM holds two accumulators (2 x BN columns) so the epilogue of tile i overlaps the MMAs of
 // tile i+1.  CTAs are persistent: tile t = blockIdx.x + i * gridDim.x, M-fastest.
@@ -51,8 +51,8 @@ struct GemmKind<KIND_TF32> {
 };
 
 constexpr int GEMM_BM = 128;
-constexpr int GEMM_THREADS = 192;
-constexpr int GEMM_EPI_WARPS = 4;
+constexpr int GEMM_EPI_WARPS = 8;
+constexpr int GEMM_THREADS = 64 + 32 * GEMM_EPI_WARPS;
 
 template <int BN>
 __host__ __device__ constexpr uint32_t gemm_tmem_cols() {
@@ -72,12 +72,155 @@ __device__ __forceinline__ void issue_mma(uint32_t d, uint64_t a, uint64_t b, ui
   else mma_tf32_ss(d, a, b, idesc, acc);
 }
 
-// 16-byte stores of NV consecutive 32-bit words (dst 16-byte aligned)
+// 16-byte stores of NW consecutive 32-bit words (dst 16-byte aligned)
 template <int NW>
 __device__ __forceinline__ void store_words(void* dst, const uint32_t* w) {
   uint4* d4 = reinterpret_cast<uint4*>(dst);
 #pragma unroll
   for (int i = 0; i < NW / 4; ++i) d4[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+}
+
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float rcp_approx(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// GELU through the hardware exp2 / reciprocal units.  Same formula and same argument of the
+// exponential (bit for bit) as zen_det_gelu; differs from it by less than 1e-6 relative.
+__device__ __forceinline__ float gelu_fast(float x) {
+  const float x2 = ZEN_MUL(x, x);
+  const float w = ZEN_FMA(0.044715f, x2, 1.0f);
+  const float v = ZEN_MUL(x, w);
+  const float e = ex2_approx(ZEN_MUL(v, -2.302208198144325f));
+  return x * rcp_approx(1.0f + e);
+}
+
+// Requantisation to int8 with the exact result of  clamp(round(act(y) / out_scale))  at a fraction of
+// its cost.  The quotient is first formed with approximate arithmetic (error far below MARGIN in
+// units of one int8 step); unless it lies within MARGIN of a rounding boundary its rounding is already
+// the exact answer.  The few elements that do (about 2 in 1000) are recomputed with the
+// individually rounded IEEE operations of det_math.h, so the output is bit-identical to the CPU
+// definition everywhere.
+template <int ACT>
+__device__ __forceinline__ void requant32(const float (&y)[32], float out_scale, float inv_scale, int round_mode,
+                                          uint32_t (&packed)[8]) {
+  constexpr float MARGIN = 1e-3f;
+  int q[32];
+  uint32_t risky = 0;
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    float g = y[j];
+    if constexpr (ACT == ZEN_ACT_GELU) g = gelu_fast(g);
+    if constexpr (ACT == ZEN_ACT_RELU) g = g > 0.0f ? g : 0.0f;
+    const float t = g * inv_scale;
+    // distance to the decision boundary: a half-integer for nearest-even, an integer for truncation
+    const float tr = rintf(t);
+    const float d = round_mode == 0 ? 0.5f - fabsf(t - tr) : fabsf(t - tr);
+    if (!(d >= MARGIN) && !(fabsf(t) >= 130.0f)) risky |= 1u << j;
+    float tc = t > -128.0f ? t : -128.0f;
+    tc = tc < 127.0f ? tc : 127.0f;
+    q[j] = round_mode == 0 ? __float2int_rn(tc) : __float2int_rz(tc);
+  }
+  if (risky) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (risky & (1u << j)) q[j] = zen_det_round_clamp_i8(ZEN_DIV(zen_det_act(y[j], ACT), out_scale), round_mode);
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+    packed[j] = (uint32_t(q[4 * j]) & 0xffu) | ((uint32_t(q[4 * j + 1]) & 0xffu) << 8) |
+                ((uint32_t(q[4 * j + 2]) & 0xffu) << 16) | ((uint32_t(q[4 * j + 3]) & 0xffu) << 24);
+}
+
+// One 32-column chunk of one accumulator row: dequant / bias / activation / conversion / store.
+// OUT and ACT are compile-time so that the 32 independent element chains carry no branches and
+// the compiler can interleave them.
+template <int KIND, int OUT, int ACT>
+__device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], const float* sc, const float* bi,
+                                               const GemmParams& p, int row, int col0, bool full, float inv_scale) {
+  const int nvalid = p.N - col0;  // >= 1
+  if constexpr (OUT == ZEN_DT_S32) {
+    int32_t* o = static_cast<int32_t*>(p.out) + int64_t(row) * p.ldo + col0;
+    if (full) store_words<32>(o, r);
+    else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < nvalid) o[j] = int32_t(r[j]);
+    }
+    return;
+  } else {
+    float y[32];
+#pragma unroll
+    for (int j4 = 0; j4 < 8; ++j4) {
+      const float4 s4 = reinterpret_cast<const float4*>(sc)[j4];
+      const float4 b4 = reinterpret_cast<const float4*>(bi)[j4];
+      const float ss[4] = {s4.x, s4.y, s4.z, s4.w};
+      const float bb[4] = {b4.x, b4.y, b4.z, b4.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int j = 4 * j4 + e;
+        if constexpr (KIND == KIND_I8) y[j] = zen_det_dequant(int32_t(r[j]), p.x_scale, ss[e], bb[e]);
+        else y[j] = ZEN_ADD(__uint_as_float(r[j]), bb[e]);
+      }
+    }
+    if constexpr (OUT == ZEN_DT_S8) {
+      uint32_t w[8];
+      requant32<ACT>(y, p.out_scale, inv_scale, p.round_mode, w);
+      int8_t* o = static_cast<int8_t*>(p.out) + int64_t(row) * p.ldo + col0;
+      if (full) store_words<8>(o, w);
+      else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (j < nvalid) o[j] = int8_t((w[j >> 2] >> (8 * (j & 3))) & 0xffu);
+      }
+    } else {
+      // int8 GEMMs keep the bit-exact activation; the fp16 / TF32 GEMMs are tolerance paths and use
+      // the hardware exp2 / reciprocal form
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        if constexpr (ACT == ZEN_ACT_GELU) y[j] = (KIND == KIND_I8) ? zen_det_gelu(y[j]) : gelu_fast(y[j]);
+        if constexpr (ACT == ZEN_ACT_RELU) y[j] = y[j] > 0.0f ? y[j] : 0.0f;
+      }
+      if constexpr (OUT == ZEN_DT_F32) {
+        float* o = static_cast<float*>(p.out) + int64_t(row) * p.ldo + col0;
+        if (full) store_words<32>(o, reinterpret_cast<const uint32_t*>(y));
+        else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (j < nvalid) o[j] = y[j];
+        }
+      } else {
+        __half* o = static_cast<__half*>(p.out) + int64_t(row) * p.ldo + col0;
+        uint32_t w[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const __half2 h = __floats2half2_rn(y[2 * j], y[2 * j + 1]);
+          w[j] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+        if (full) store_words<16>(o, w);
+        else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (j < nvalid) o[j] = __ushort_as_half((unsigned short)((w[j >> 1] >> (16 * (j & 1))) & 0xffffu));
+        }
+      }
+    }
+  }
+}
+
+template <int KIND, int OUT>
+__device__ __forceinline__ void epilogue_chunk_act(const uint32_t (&r)[32], const float* sc, const float* bi,
+                                                   const GemmParams& p, int row, int col0, bool full,
+                                                   float inv_scale) {
+  if (p.act == ZEN_ACT_GELU) epilogue_chunk<KIND, OUT, ZEN_ACT_GELU>(r, sc, bi, p, row, col0, full, inv_scale);
+  else if (p.act == ZEN_ACT_RELU) epilogue_chunk<KIND, OUT, ZEN_ACT_RELU>(r, sc, bi, p, row, col0, full, inv_scale);
+  else epilogue_chunk<KIND, OUT, ZEN_ACT_NONE>(r, sc, bi, p, row, col0, full, inv_scale);
 }
 
 template <int KIND, int BN, int STAGES, bool B_MN>
@@ -213,13 +356,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
   } else {
     // ------------------------------------------------------------------ epilogue
-    const int quad = warp & 3;  // TMEM lane quadrant this warp may read
+    const int quad = warp & 3;            // TMEM lane quadrant this warp may read
+    const int half = (warp - 2) >> 2;     // which of the two warps of the quadrant: takes chunks c % 2 == half
     float* s_scale = epi_rows + (warp - 2) * 2 * BN;
     float* s_bias = s_scale + BN;
     int acc = 0;
     uint32_t acc_phase = 0;
     const bool vec_ok = (reinterpret_cast<uintptr_t>(p.out) % 16 == 0) &&
                         ((p.ldo * (p.out_dtype == ZEN_DT_S8 ? 1 : p.out_dtype == ZEN_DT_F16 ? 2 : 4)) % 16 == 0);
+    const float inv_scale = ZEN_DIV(1.0f, p.out_scale);
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
       const int m0 = (tile % p.tiles_m) * GEMM_BM;
       const int n0 = (tile / p.tiles_m) * BN;
@@ -235,7 +380,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const int row = m0 + quad * 32 + lane;
       const bool row_ok = row < p.M;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = half; c < BN / 32; c += 2) {
         uint32_t r[32];
         __syncwarp();
         tmem_ld_32x32(tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * BN + c * 32), r);
@@ -245,67 +390,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const bool full = vec_ok && (col0 + 32 <= p.N);
         const float* sc = s_scale + c * 32;
         const float* bi = s_bias + c * 32;
-        float y[32];
-        if (KIND == KIND_I8 && p.out_dtype == ZEN_DT_S32) {
-          int32_t* o = static_cast<int32_t*>(p.out) + int64_t(row) * p.ldo + col0;
-          if (full) store_words<32>(o, r);
-          else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < p.N) o[j] = int32_t(r[j]);
+        if constexpr (KIND == KIND_I8) {
+          switch (p.out_dtype) {
+            case ZEN_DT_S32: epilogue_chunk<KIND, ZEN_DT_S32, ZEN_ACT_NONE>(r, sc, bi, p, row, col0, full, inv_scale); break;
+            case ZEN_DT_F32: epilogue_chunk_act<KIND, ZEN_DT_F32>(r, sc, bi, p, row, col0, full, inv_scale); break;
+            case ZEN_DT_F16: epilogue_chunk_act<KIND, ZEN_DT_F16>(r, sc, bi, p, row, col0, full, inv_scale); break;
+            default: epilogue_chunk_act<KIND, ZEN_DT_S8>(r, sc, bi, p, row, col0, full, inv_scale); break;
           }
-          continue;
-        }
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          float v;
-          if constexpr (KIND == KIND_I8) v = zen_det_dequant(int32_t(r[j]), p.x_scale, sc[j], bi[j]);
-          else v = p.bias != nullptr ? ZEN_ADD(__uint_as_float(r[j]), bi[j]) : __uint_as_float(r[j]);
-          y[j] = zen_det_act(v, p.act);
-        }
-        if (p.out_dtype == ZEN_DT_F32) {
-          float* o = static_cast<float*>(p.out) + int64_t(row) * p.ldo + col0;
-          if (full) store_words<32>(o, reinterpret_cast<const uint32_t*>(y));
-          else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < p.N) o[j] = y[j];
-          }
-        } else if (p.out_dtype == ZEN_DT_F16) {
-          __half* o = static_cast<__half*>(p.out) + int64_t(row) * p.ldo + col0;
-          if (full) {
-            uint32_t w[16];
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              __half2 h = __floats2half2_rn(y[2 * j], y[2 * j + 1]);
-              w[j] = *reinterpret_cast<uint32_t*>(&h);
-            }
-            store_words<16>(o, w);
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < p.N) o[j] = __float2half_rn(y[j]);
-          }
-        } else {  // ZEN_DT_S8
-          int8_t* o = static_cast<int8_t*>(p.out) + int64_t(row) * p.ldo + col0;
-          if (full) {
-            uint32_t w[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              uint32_t pk = 0;
-#pragma unroll
-              for (int b = 0; b < 4; ++b) {
-                const int q = zen_det_round_clamp_i8(ZEN_DIV(y[4 * j + b], p.out_scale), p.round_mode);
-                pk |= (uint32_t(q) & 0xffu) << (8 * b);
-              }
-              w[j] = pk;
-            }
-            store_words<8>(o, w);
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < p.N) o[j] = int8_t(zen_det_round_clamp_i8(ZEN_DIV(y[j], p.out_scale), p.round_mode));
-          }
+        } else {
+          if (p.out_dtype == ZEN_DT_F32) epilogue_chunk_act<KIND, ZEN_DT_F32>(r, sc, bi, p, row, col0, full, inv_scale);
+          else epilogue_chunk_act<KIND, ZEN_DT_F16>(r, sc, bi, p, row, col0, full, inv_scale);
         }
       }
       tc_fence_before_sync();
