@@ -101,63 +101,79 @@ __device__ __forceinline__ float gelu_fast(float x) {
   return x * rcp_approx(1.0f + e);
 }
 
+constexpr int GEMM_CW = 16;  // accumulator columns per epilogue step (kept small: the step is the unrolled unit)
+
 // Requantisation to int8 with the exact result of  clamp(round(act(y) / out_scale))  at a fraction of
 // its cost.  The quotient is first formed with approximate arithmetic (error far below MARGIN in
 // units of one int8 step); unless it lies within MARGIN of a rounding boundary its rounding is already
 // the exact answer.  The few elements that do (about 2 in 1000) are recomputed with the
 // individually rounded IEEE operations of det_math.h, so the output is bit-identical to the CPU
-// definition everywhere.
+// definition everywhere.  Nearest-even rounding uses the 1.5 * 2^23 magic constant (exact rint for
+// |t| < 2^22, and the integer falls out of the mantissa), which keeps the conversion units free.
 template <int ACT>
-__device__ __forceinline__ void requant32(const float (&y)[32], float out_scale, float inv_scale, int round_mode,
-                                          uint32_t (&packed)[8]) {
+__device__ __forceinline__ void requant_chunk(const float (&y)[GEMM_CW], float out_scale, float inv_scale,
+                                              int round_mode, uint32_t (&packed)[GEMM_CW / 4]) {
   constexpr float MARGIN = 1e-3f;
-  int q[32];
+  constexpr float MAGIC = 12582912.0f;  // 1.5 * 2^23
+  int q[GEMM_CW];
   uint32_t risky = 0;
+  if (round_mode == 0) {
 #pragma unroll
-  for (int j = 0; j < 32; ++j) {
-    float g = y[j];
-    if constexpr (ACT == ZEN_ACT_GELU) g = gelu_fast(g);
-    if constexpr (ACT == ZEN_ACT_RELU) g = g > 0.0f ? g : 0.0f;
-    const float t = g * inv_scale;
-    // distance to the decision boundary: a half-integer for nearest-even, an integer for truncation
-    const float tr = rintf(t);
-    const float d = round_mode == 0 ? 0.5f - fabsf(t - tr) : fabsf(t - tr);
-    if (!(d >= MARGIN) && !(fabsf(t) >= 130.0f)) risky |= 1u << j;
-    float tc = t > -128.0f ? t : -128.0f;
-    tc = tc < 127.0f ? tc : 127.0f;
-    q[j] = round_mode == 0 ? __float2int_rn(tc) : __float2int_rz(tc);
+    for (int j = 0; j < GEMM_CW; ++j) {
+      float g = y[j];
+      if constexpr (ACT == ZEN_ACT_GELU) g = gelu_fast(g);
+      if constexpr (ACT == ZEN_ACT_RELU) g = g > 0.0f ? g : 0.0f;
+      const float t = g * inv_scale;
+      const float tc = fminf(fmaxf(t, -128.0f), 127.0f);  // NaN -> -128, as in the exact definition
+      const float m = tc + MAGIC;
+      q[j] = __float_as_int(m) - 0x4B400000;
+      const float d = 0.5f - fabsf(tc - (m - MAGIC));  // distance of tc to the nearest half-integer
+      if (d < MARGIN && fabsf(t) < 130.0f) risky |= 1u << j;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < GEMM_CW; ++j) {
+      float g = y[j];
+      if constexpr (ACT == ZEN_ACT_GELU) g = gelu_fast(g);
+      if constexpr (ACT == ZEN_ACT_RELU) g = g > 0.0f ? g : 0.0f;
+      const float t = g * inv_scale;
+      const float tc = fminf(fmaxf(t, -128.0f), 127.0f);
+      q[j] = __float2int_rz(tc);
+      if (fabsf(t - rintf(t)) < MARGIN && fabsf(t) < 130.0f) risky |= 1u << j;  // boundaries are the integers
+    }
   }
   if (risky) {
 #pragma unroll
-    for (int j = 0; j < 32; ++j)
+    for (int j = 0; j < GEMM_CW; ++j)
       if (risky & (1u << j)) q[j] = zen_det_round_clamp_i8(ZEN_DIV(zen_det_act(y[j], ACT), out_scale), round_mode);
   }
 #pragma unroll
-  for (int j = 0; j < 8; ++j)
+  for (int j = 0; j < GEMM_CW / 4; ++j)
     packed[j] = (uint32_t(q[4 * j]) & 0xffu) | ((uint32_t(q[4 * j + 1]) & 0xffu) << 8) |
                 ((uint32_t(q[4 * j + 2]) & 0xffu) << 16) | ((uint32_t(q[4 * j + 3]) & 0xffu) << 24);
 }
 
-// One 32-column chunk of one accumulator row: dequant / bias / activation / conversion / store.
-// OUT and ACT are compile-time so that the 32 independent element chains carry no branches and
-// the compiler can interleave them.
+// One GEMM_CW-column step of one accumulator row: dequant / bias / activation / conversion / store.
+// OUT and ACT are compile-time so that the independent element chains carry no branches and the
+// compiler can interleave them.
 template <int KIND, int OUT, int ACT>
-__device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], const float* sc, const float* bi,
+__device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[GEMM_CW], const float* sc, const float* bi,
                                                const GemmParams& p, int row, int col0, bool full, float inv_scale) {
+  constexpr int CW = GEMM_CW;
   const int nvalid = p.N - col0;  // >= 1
   if constexpr (OUT == ZEN_DT_S32) {
     int32_t* o = static_cast<int32_t*>(p.out) + int64_t(row) * p.ldo + col0;
-    if (full) store_words<32>(o, r);
+    if (full) store_words<CW>(o, r);
     else {
 #pragma unroll
-      for (int j = 0; j < 32; ++j)
+      for (int j = 0; j < CW; ++j)
         if (j < nvalid) o[j] = int32_t(r[j]);
     }
     return;
   } else {
-    float y[32];
+    float y[CW];
 #pragma unroll
-    for (int j4 = 0; j4 < 8; ++j4) {
+    for (int j4 = 0; j4 < CW / 4; ++j4) {
       const float4 s4 = reinterpret_cast<const float4*>(sc)[j4];
       const float4 b4 = reinterpret_cast<const float4*>(bi)[j4];
       const float ss[4] = {s4.x, s4.y, s4.z, s4.w};
@@ -170,43 +186,43 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], const fl
       }
     }
     if constexpr (OUT == ZEN_DT_S8) {
-      uint32_t w[8];
-      requant32<ACT>(y, p.out_scale, inv_scale, p.round_mode, w);
+      uint32_t w[CW / 4];
+      requant_chunk<ACT>(y, p.out_scale, inv_scale, p.round_mode, w);
       int8_t* o = static_cast<int8_t*>(p.out) + int64_t(row) * p.ldo + col0;
-      if (full) store_words<8>(o, w);
+      if (full) store_words<CW / 4>(o, w);
       else {
 #pragma unroll
-        for (int j = 0; j < 32; ++j)
+        for (int j = 0; j < CW; ++j)
           if (j < nvalid) o[j] = int8_t((w[j >> 2] >> (8 * (j & 3))) & 0xffu);
       }
     } else {
       // int8 GEMMs keep the bit-exact activation; the fp16 / TF32 GEMMs are tolerance paths and use
       // the hardware exp2 / reciprocal form
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
+      for (int j = 0; j < CW; ++j) {
         if constexpr (ACT == ZEN_ACT_GELU) y[j] = (KIND == KIND_I8) ? zen_det_gelu(y[j]) : gelu_fast(y[j]);
         if constexpr (ACT == ZEN_ACT_RELU) y[j] = y[j] > 0.0f ? y[j] : 0.0f;
       }
       if constexpr (OUT == ZEN_DT_F32) {
         float* o = static_cast<float*>(p.out) + int64_t(row) * p.ldo + col0;
-        if (full) store_words<32>(o, reinterpret_cast<const uint32_t*>(y));
+        if (full) store_words<CW>(o, reinterpret_cast<const uint32_t*>(y));
         else {
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
+          for (int j = 0; j < CW; ++j)
             if (j < nvalid) o[j] = y[j];
         }
       } else {
         __half* o = static_cast<__half*>(p.out) + int64_t(row) * p.ldo + col0;
-        uint32_t w[16];
+        uint32_t w[CW / 2];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
+        for (int j = 0; j < CW / 2; ++j) {
           const __half2 h = __floats2half2_rn(y[2 * j], y[2 * j + 1]);
           w[j] = *reinterpret_cast<const uint32_t*>(&h);
         }
-        if (full) store_words<16>(o, w);
+        if (full) store_words<CW / 2>(o, w);
         else {
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
+          for (int j = 0; j < CW; ++j)
             if (j < nvalid) o[j] = __ushort_as_half((unsigned short)((w[j >> 1] >> (16 * (j & 1))) & 0xffffu));
         }
       }
@@ -215,7 +231,7 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], const fl
 }
 
 template <int KIND, int OUT>
-__device__ __forceinline__ void epilogue_chunk_act(const uint32_t (&r)[32], const float* sc, const float* bi,
+__device__ __forceinline__ void epilogue_chunk_act(const uint32_t (&r)[GEMM_CW], const float* sc, const float* bi,
                                                    const GemmParams& p, int row, int col0, bool full,
                                                    float inv_scale) {
   if (p.act == ZEN_ACT_GELU) epilogue_chunk<KIND, OUT, ZEN_ACT_GELU>(r, sc, bi, p, row, col0, full, inv_scale);
@@ -380,16 +396,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const int row = m0 + quad * 32 + lane;
       const bool row_ok = row < p.M;
 #pragma unroll 1
-      for (int c = half; c < BN / 32; c += 2) {
-        uint32_t r[32];
+      for (int c = half; c < BN / GEMM_CW; c += 2) {
+        uint32_t r[GEMM_CW];
         __syncwarp();
-        tmem_ld_32x32(tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * BN + c * 32), r);
+        tmem_ld_32x16(tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * BN + c * GEMM_CW), r);
         tmem_wait_ld();
-        const int col0 = n0 + c * 32;
+        const int col0 = n0 + c * GEMM_CW;
         if (!row_ok || col0 >= p.N) continue;
-        const bool full = vec_ok && (col0 + 32 <= p.N);
-        const float* sc = s_scale + c * 32;
-        const float* bi = s_bias + c * 32;
+        const bool full = vec_ok && (col0 + GEMM_CW <= p.N);
+        const float* sc = s_scale + c * GEMM_CW;
+        const float* bi = s_bias + c * GEMM_CW;
         if constexpr (KIND == KIND_I8) {
           switch (p.out_dtype) {
             case ZEN_DT_S32: epilogue_chunk<KIND, ZEN_DT_S32, ZEN_ACT_NONE>(r, sc, bi, p, row, col0, full, inv_scale); break;
