@@ -40,8 +40,9 @@ struct FaParams {
 
 template <int D, int KV_STAGES>
 constexpr size_t fa_smem_bytes() {
-  // Q + KV_STAGES x (K + V) tiles (128 x D fp16 each) + P (128 x 128 fp16) + control + alignment slack
-  return size_t(1 + 2 * KV_STAGES) * FA_BQ * D * 2 + FA_BQ * FA_BKV * 2 + 256 + 1024;
+  // Q + KV_STAGES x (K + V) tiles (128 x D fp16 each) + P (128 x 128 fp16) + control + alignment slack;
+  // with a single key block P reuses the Q and K tiles, which are dead once S = Q K^T has completed
+  return size_t(1 + 2 * KV_STAGES) * FA_BQ * D * 2 + (KV_STAGES == 1 ? 0 : FA_BQ * FA_BKV * 2) + 256 + 1024;
 }
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -61,16 +62,18 @@ __device__ __forceinline__ void fa_tma_tile(uint8_t* dst, const CUtensorMap* map
 }
 
 // KV_STAGES = 2 double-buffers K and V for long sequences; KV_STAGES = 1 serves sequences of at most
-// one key block (S <= 128, the encoder's case) with a footprint small enough for two CTAs per SM, so
-// that one CTA's softmax overlaps the other's loads and MMAs.
+// one key block (S <= 128, the encoder's case): P reuses the Q / K tiles and O_blk reuses the TMEM
+// columns of S, so that four CTAs fit on an SM (one wave for 32 x 12 heads on 148 SMs) and one CTA's
+// softmax overlaps the others' loads and MMAs.
 template <int D, int KV_STAGES>
-__global__ void __launch_bounds__(FA_THREADS, (D == 64 && KV_STAGES == 1) ? 2 : 1)
+__global__ void __launch_bounds__(FA_THREADS, (D == 64 && KV_STAGES == 1) ? 4 : 1)
 flash_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                   const __grid_constant__ CUtensorMap tmap_v, const FaParams p) {
   constexpr int DC = D / 64;                 // 128-byte column chunks per row
   constexpr int TILE_BYTES = FA_BQ * D * 2;  // one Q / K / V tile
   constexpr int CHUNK_BYTES = FA_BQ * 128;   // one 64-column chunk of a tile
-  constexpr uint32_t TMEM_COLS = 256;        // S: 128 columns, O_blk: D columns
+  constexpr uint32_t TMEM_COLS = KV_STAGES == 1 ? 128 : 256;  // S: 128 columns; O_blk: D columns (aliased on S
+                                                              // when there is a single key block)
   constexpr uint32_t IDESC_QK = make_idesc(IDESC_C_F32, IDESC_F16, IDESC_F16, 0, 0, FA_BQ, FA_BKV);
   constexpr uint32_t IDESC_PV = make_idesc(IDESC_C_F32, IDESC_F16, IDESC_F16, 0, 1, FA_BQ, D);
 
@@ -79,8 +82,9 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   uint8_t* sQ = smem;
   uint8_t* sK = sQ + TILE_BYTES;              // KV_STAGES stages
   uint8_t* sV = sK + KV_STAGES * TILE_BYTES;  // KV_STAGES stages
-  uint8_t* sP = sV + KV_STAGES * TILE_BYTES;  // 2 chunks of 64 keys
-  uint8_t* ctrl = sP + FA_BQ * FA_BKV * 2;
+  uint8_t* sP = KV_STAGES == 1 ? sQ : sV + KV_STAGES * TILE_BYTES;  // 2 chunks of 64 keys
+  uint8_t* ctrl = sV + KV_STAGES * TILE_BYTES + (KV_STAGES == 1 ? 0 : FA_BQ * FA_BKV * 2);
+  static_assert(KV_STAGES != 1 || 2 * TILE_BYTES >= FA_BQ * FA_BKV * 2, "P must fit in the Q + K tiles");
   uint64_t* q_full = reinterpret_cast<uint64_t*>(ctrl);
   uint64_t* k_full = q_full + 1;    // [2]
   uint64_t* k_empty = k_full + 2;   // [2]
@@ -129,8 +133,10 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  grid_launch_dependents();
+  grid_dependency_wait();  // Q, K, V and the output buffers may belong to the previous kernel until here
   const uint32_t tmem_s = tmem_base;
-  const uint32_t tmem_o = tmem_base + 128;
+  const uint32_t tmem_o = KV_STAGES == 1 ? tmem_base : tmem_base + 128;
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
@@ -262,22 +268,43 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
 
       l_run = l_run * alpha + rowsum;
       m_run = m_new;
-      if (alpha != 1.f) {
+      if constexpr (KV_STAGES != 1) {
+        if (alpha != 1.f) {
 #pragma unroll
-        for (int i = 0; i < D; ++i) o_acc[i] *= alpha;
+          for (int i = 0; i < D; ++i) o_acc[i] *= alpha;
+        }
+        if (!mbar_wait(o_full, j & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after_sync();
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t ov[32];
+          __syncwarp();
+          tmem_ld_32x32(tmem_o + lane_sel + c * 32, ov);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] += __uint_as_float(ov[i]);
+        }
+        tc_fence_before_sync();
       }
-      if (!mbar_wait(o_full, j & 1, abort_flag)) { ok = false; break; }
-      tc_fence_after_sync();
+    }
+    if constexpr (KV_STAGES == 1) {
+      // a single key block: O is the one P V product, read straight from TMEM
+      if (ok && n_blocks > 0) {
+        if (!mbar_wait(o_full, 0, abort_flag)) ok = false;
+        tc_fence_after_sync();
+        if (ok) {
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t ov[32];
-        __syncwarp();
-        tmem_ld_32x32(tmem_o + lane_sel + c * 32, ov);
-        tmem_wait_ld();
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t ov[32];
+            __syncwarp();
+            tmem_ld_32x32(tmem_o + lane_sel + c * 32, ov);
+            tmem_wait_ld();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] += __uint_as_float(ov[i]);
+            for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] = __uint_as_float(ov[i]);
+          }
+        }
+        tc_fence_before_sync();
       }
-      tc_fence_before_sync();
     }
 
     if (ok && q < p.S) {
@@ -294,6 +321,7 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       for (int i = 0; i < D / 8; ++i)
         reinterpret_cast<uint4*>(orow)[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
       if (p.oq) {
+        const float inv_o_scale = ZEN_DIV(1.0f, p.o_scale);
         int8_t* qrow = p.oq + off;
         uint32_t qw[D / 4];
 #pragma unroll
@@ -303,7 +331,7 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
           for (int e = 0; e < 4; ++e) {
             const __half2 hh = *reinterpret_cast<const __half2*>(&w[(4 * i + e) / 2]);
             const float val = (e & 1) ? __high2float(hh) : __low2float(hh);
-            pk |= (uint32_t(zen_det_round_clamp_i8(ZEN_DIV(val, p.o_scale), 0)) & 0xffu) << (8 * e);
+            pk |= (uint32_t(quantize_exact(val, p.o_scale, inv_o_scale, 0)) & 0xffu) << (8 * e);
           }
           qw[i] = pk;
         }
@@ -368,8 +396,7 @@ static int launch_fa(const CUtensorMap& tq, const CUtensorMap& tk, const CUtenso
     attr_set = true;
   }
   dim3 grid((p.S + FA_BQ - 1) / FA_BQ, p.H, p.B);
-  kernel<<<grid, FA_THREADS, smem, s>>>(tq, tk, tv, p);
-  return cudaGetLastError() == cudaSuccess ? ZEN_OK : ZEN_ERR_LAUNCH;
+  return launch_pdl(kernel, grid, dim3(FA_THREADS), smem, s, tq, tk, tv, p);
 }
 
 }  // namespace zen

@@ -45,8 +45,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams 
   p.tiles_n = (p.N + BN - 1) / BN;
   const int tiles = p.tiles_m * p.tiles_n;
   const int grid = tiles < num_sms() ? tiles : num_sms();
-  kernel<<<grid, GEMM_THREADS, smem, stream>>>(ta, tb, p);
-  return cudaGetLastError() == cudaSuccess ? ZEN_OK : ZEN_ERR_LAUNCH;
+  return launch_pdl(kernel, dim3(grid), dim3(GEMM_THREADS), smem, stream, ta, tb, p);
 }
 
 template <int KIND>

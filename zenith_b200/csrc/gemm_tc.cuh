@@ -4,8 +4,8 @@
 //
 //   warp 0      : TMA producer  — 128-byte-swizzled tiles of A and B into a STAGES-deep ring
 //   warp 1      : allocates TMEM, issues tcgen05.mma (one lane), commits stage / accumulator barriers
-//   warps 2..9  : epilogue — tcgen05.ld of the accumulator (two warps per 32-lane TMEM quadrant, taking
-//                 alternate 32-column chunks), dequant / bias / activation / requant, 16-byte stores
+//   warps 2..17 : epilogue — tcgen05.ld of the accumulator (four warps per 32-lane TMEM quadrant, taking
+//                 16-column steps round-robin), dequant / bias / activation / requant, 16-byte stores
 //
 // TMEM holds two accumulators (2 x BN columns) so the epilogue of tile i overlaps the MMAs of
 // tile i+1.  CTAs are persistent: tile t = blockIdx.x + i * gridDim.x, M-fastest.
@@ -51,7 +51,7 @@ struct GemmKind<KIND_TF32> {
 };
 
 constexpr int GEMM_BM = 128;
-constexpr int GEMM_EPI_WARPS = 8;
+constexpr int GEMM_EPI_WARPS = 16;
 constexpr int GEMM_THREADS = 64 + 32 * GEMM_EPI_WARPS;
 
 template <int BN>
@@ -61,8 +61,8 @@ __host__ __device__ constexpr uint32_t gemm_tmem_cols() {
 
 template <int BN, int STAGES>
 __host__ __device__ constexpr size_t gemm_smem_bytes() {
-  // ring + barriers/flags (256 B) + per-epilogue-warp scale and bias rows + alignment slack
-  return size_t(STAGES) * (GEMM_BM * 128 + BN * 128) + 256 + size_t(GEMM_EPI_WARPS) * 2 * BN * 4 + 1024;
+  // ring + barriers/flags (256 B) + per-epilogue-warp scale and bias entries + alignment slack
+  return size_t(STAGES) * (GEMM_BM * 128 + BN * 128) + 256 + size_t(GEMM_EPI_WARPS) * 2 * (BN / 4 + 16) * 4 + 1024;
 }
 
 template <int KIND>
@@ -295,6 +295,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  grid_launch_dependents();
+  grid_dependency_wait();  // operands and output buffers may belong to the previous kernel until here
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -373,9 +375,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   } else {
     // ------------------------------------------------------------------ epilogue
     const int quad = warp & 3;            // TMEM lane quadrant this warp may read
-    const int half = (warp - 2) >> 2;     // which of the two warps of the quadrant: takes chunks c % 2 == half
-    float* s_scale = epi_rows + (warp - 2) * 2 * BN;
-    float* s_bias = s_scale + BN;
+    constexpr int SUBS = GEMM_EPI_WARPS / 4;
+    const int sub = (warp - 2) >> 2;      // which of the warps of this quadrant: takes steps c % SUBS == sub
+    // each warp stages the scale / bias entries of its own steps only: step c lives at (c / SUBS) * GEMM_CW
+    constexpr int COLS_PER_WARP = (BN / GEMM_CW + SUBS - 1) / SUBS * GEMM_CW;
+    float* s_scale = epi_rows + (warp - 2) * 2 * COLS_PER_WARP;
+    float* s_bias = s_scale + COLS_PER_WARP;
     int acc = 0;
     uint32_t acc_phase = 0;
     const bool vec_ok = (reinterpret_cast<uintptr_t>(p.out) % 16 == 0) &&
@@ -385,8 +390,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const int m0 = (tile % p.tiles_m) * GEMM_BM;
       const int n0 = (tile / p.tiles_m) * BN;
       __syncwarp();
-      for (int i = lane; i < BN; i += 32) {
-        const int col = n0 + i;
+      for (int i = lane; i < COLS_PER_WARP; i += 32) {
+        const int col = n0 + ((i / GEMM_CW) * SUBS + sub) * GEMM_CW + (i % GEMM_CW);
         s_scale[i] = (p.w_scale != nullptr && col < p.N) ? __ldg(p.w_scale + col) : 1.0f;
         s_bias[i] = (p.bias != nullptr && col < p.N) ? __ldg(p.bias + col) : 0.0f;
       }
@@ -395,17 +400,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       tc_fence_after_sync();
       const int row = m0 + quad * 32 + lane;
       const bool row_ok = row < p.M;
+      // This warp's steps are c = sub, sub + SUBS, ...  The loop is kept rolled: the step body (above all
+      // the GELU + requant one) is large, and unrolling it made instruction fetch the bottleneck.
+      const uint32_t tacc = tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * BN);
 #pragma unroll 1
-      for (int c = half; c < BN / GEMM_CW; c += 2) {
+      for (int c = sub, i = 0; c < BN / GEMM_CW; c += SUBS, ++i) {
         uint32_t r[GEMM_CW];
         __syncwarp();
-        tmem_ld_32x16(tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * BN + c * GEMM_CW), r);
+        tmem_ld_32x16(tacc + uint32_t(c * GEMM_CW), r);
         tmem_wait_ld();
         const int col0 = n0 + c * GEMM_CW;
         if (!row_ok || col0 >= p.N) continue;
         const bool full = vec_ok && (col0 + GEMM_CW <= p.N);
-        const float* sc = s_scale + c * GEMM_CW;
-        const float* bi = s_bias + c * GEMM_CW;
+        const float* sc = s_scale + i * GEMM_CW;
+        const float* bi = s_bias + i * GEMM_CW;
         if constexpr (KIND == KIND_I8) {
           switch (p.out_dtype) {
             case ZEN_DT_S32: epilogue_chunk<KIND, ZEN_DT_S32, ZEN_ACT_NONE>(r, sc, bi, p, row, col0, full, inv_scale); break;
@@ -418,6 +426,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           else epilogue_chunk_act<KIND, ZEN_DT_F16>(r, sc, bi, p, row, col0, full, inv_scale);
         }
       }
+      __syncwarp();
       tc_fence_before_sync();
       mbar_arrive(&tempty_bar[acc]);
       acc ^= 1;

@@ -67,13 +67,14 @@ __device__ __forceinline__ int quantize_value(float x, float scale, int zero_poi
 }
 
 template <int N>
-__device__ __forceinline__ void store_q(int8_t* p, const float (&v)[N], float scale, int round_mode) {
+__device__ __forceinline__ void store_q(int8_t* p, const float (&v)[N], float scale, float inv_scale, int round_mode) {
   uint32_t w[N / 4];
 #pragma unroll
   for (int i = 0; i < N / 4; ++i) {
     uint32_t pk = 0;
 #pragma unroll
-    for (int b = 0; b < 4; ++b) pk |= (uint32_t(quantize_value(v[4 * i + b], scale, 0, round_mode)) & 0xffu) << (8 * b);
+    for (int b = 0; b < 4; ++b)
+      pk |= (uint32_t(quantize_exact(v[4 * i + b], scale, inv_scale, round_mode)) & 0xffu) << (8 * b);
     w[i] = pk;
   }
   if constexpr (N == 8) *reinterpret_cast<uint2*>(p) = make_uint2(w[0], w[1]);
@@ -109,6 +110,8 @@ __global__ void __launch_bounds__(ROW_WARPS * 32) ln_warp_kernel(const RowParams
   constexpr int N = Vec16<T>::N;
   const int lane = threadIdx.x & 31;
   const int row = blockIdx.x * ROW_WARPS + (threadIdx.x >> 5);
+  grid_launch_dependents();
+  grid_dependency_wait();  // inputs and outputs may belong to the previous kernel until here
   if (row >= p.rows) return;
   const int H = p.hidden;
   const T* x = static_cast<const T*>(p.x);
@@ -169,6 +172,7 @@ __global__ void __launch_bounds__(ROW_WARPS * 32) ln_warp_kernel(const RowParams
     }
   }
   const float rstd = rsqrtf(warp_sum(sq) / float(H) + p.eps);
+  const float inv_q_scale = ZEN_DIV(1.0f, p.q_scale);
   const T* gamma = static_cast<const T*>(p.gamma);
   const T* beta = static_cast<const T*>(p.beta);
   T* y = static_cast<T*>(p.y) + int64_t(row) * H;
@@ -187,7 +191,7 @@ __global__ void __launch_bounds__(ROW_WARPS * 32) ln_warp_kernel(const RowParams
         // quantize the value that was stored, so that yq == quantize(y) exactly
 #pragma unroll
         for (int j = 0; j < N; ++j) o[j] = Vec16<T>::stored(o[j]);
-        store_q<N>(yq + c, o, p.q_scale, p.round_mode);
+        store_q<N>(yq + c, o, p.q_scale, inv_q_scale, p.round_mode);
       }
     }
   }
@@ -270,13 +274,13 @@ static int launch_ln(const RowParams& p, cudaStream_t s) {
   const int grid = (p.rows + ROW_WARPS - 1) / ROW_WARPS;
   if (aligned && vecs <= 8) {
     switch (vecs) {
-      case 1: ln_warp_kernel<T, 1, SRC><<<grid, ROW_WARPS * 32, 0, s>>>(p); break;
-      case 2: ln_warp_kernel<T, 2, SRC><<<grid, ROW_WARPS * 32, 0, s>>>(p); break;
-      case 3: ln_warp_kernel<T, 3, SRC><<<grid, ROW_WARPS * 32, 0, s>>>(p); break;
-      case 4: ln_warp_kernel<T, 4, SRC><<<grid, ROW_WARPS * 32, 0, s>>>(p); break;
+      case 1: return launch_pdl(ln_warp_kernel<T, 1, SRC>, dim3(grid), dim3(ROW_WARPS * 32), 0, s, p);
+      case 2: return launch_pdl(ln_warp_kernel<T, 2, SRC>, dim3(grid), dim3(ROW_WARPS * 32), 0, s, p);
+      case 3: return launch_pdl(ln_warp_kernel<T, 3, SRC>, dim3(grid), dim3(ROW_WARPS * 32), 0, s, p);
+      case 4: return launch_pdl(ln_warp_kernel<T, 4, SRC>, dim3(grid), dim3(ROW_WARPS * 32), 0, s, p);
       case 5:
-      case 6: ln_warp_kernel<T, 6, SRC><<<grid, ROW_WARPS * 32, 0, s>>>(p); break;
-      default: ln_warp_kernel<T, 8, SRC><<<grid, ROW_WARPS * 32, 0, s>>>(p); break;
+      case 6: return launch_pdl(ln_warp_kernel<T, 6, SRC>, dim3(grid), dim3(ROW_WARPS * 32), 0, s, p);
+      default: return launch_pdl(ln_warp_kernel<T, 8, SRC>, dim3(grid), dim3(ROW_WARPS * 32), 0, s, p);
     }
   } else {
     ln_block_kernel<T, SRC><<<p.rows, 256, 0, s>>>(p);

@@ -5,6 +5,8 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
+#include <utility>
 #include "../../include/zenith_b200.h"
 
 namespace zen {
@@ -56,6 +58,36 @@ inline int encode_tmap_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* 
   const uint64_t str[1] = {row_stride_bytes};
   const uint32_t box[2] = {box_inner, box_outer};
   return encode_tmap(map, dt, 2, base, dims, str, box);
+}
+
+// Launch with the programmatic-stream-serialization attribute (see grid_dependency_wait()).  Only for
+// kernels that execute grid_dependency_wait() before touching global data.  ZEN_DISABLE_PDL=1 in the
+// environment falls back to ordinary stream order.
+inline bool pdl_enabled() {
+  static bool on = []() {
+    const char* e = getenv("ZEN_DISABLE_PDL");
+    return !(e && e[0] == '1');
+  }();
+  return on;
+}
+
+template <typename... KArgs, typename... Args>
+inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  if (cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...) != cudaSuccess) {
+    cudaGetLastError();
+    return ZEN_ERR_LAUNCH;
+  }
+  return ZEN_OK;
 }
 
 inline int num_sms() {

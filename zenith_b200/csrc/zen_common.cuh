@@ -11,6 +11,7 @@
 #include <cuda_fp16.h>
 #include <stdint.h>
 #include "../../include/zenith_b200.h"
+#include "det_math.h"
 
 namespace zen {
 
@@ -65,6 +66,15 @@ __device__ __forceinline__ bool elect_one() {
       : "=r"(pred));
   return pred != 0;
 }
+
+// ---------------------------------------------------------------------------
+// programmatic dependent launch: a kernel launched with launch_pdl() may begin (block scheduling,
+// barrier / TMEM set-up) while its predecessor in the stream is still running.  grid_dependency_wait()
+// returns once the predecessor has completed and its writes are visible; nothing that reads or
+// writes global data shared with the predecessor may precede it.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // ---------------------------------------------------------------------------
 // mbarrier
@@ -236,6 +246,24 @@ __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16])
         "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr)
       : "memory");
+}
+
+// ---------------------------------------------------------------------------
+// exact int8 quantisation at low cost
+// ---------------------------------------------------------------------------
+// clamp(round(x / scale), -128, 127), bit-identical to the division-based definition of det_math.h.
+// Nearest-even: the quotient is formed with a reciprocal multiply (inv_scale = 1 / scale, off by at
+// most 2 ulp, i.e. < 2e-5 of an int8 step) and rounded with the 1.5 * 2^23 constant; only when it
+// lies within 1e-3 of a half-integer is the true division evaluated.  Truncation always divides.
+__device__ __forceinline__ int quantize_exact(float x, float scale, float inv_scale, int round_mode) {
+  if (round_mode != 0) return zen_det_round_clamp_i8(ZEN_DIV(x, scale), round_mode);
+  const float t = x * inv_scale;
+  const float tc = fminf(fmaxf(t, -128.0f), 127.0f);  // NaN -> -128, as in the definition
+  const float m = tc + 12582912.0f;
+  int q = __float_as_int(m) - 0x4B400000;
+  const float d = 0.5f - fabsf(tc - (m - 12582912.0f));
+  if (d < 1e-3f && fabsf(t) < 130.0f) q = zen_det_round_clamp_i8(ZEN_DIV(x, scale), 0);
+  return q;
 }
 
 // ---------------------------------------------------------------------------
