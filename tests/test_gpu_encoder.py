@@ -101,3 +101,10 @@ def test_int8_encoder_gemms_bit_exact_and_output_tracks_oracle(cuda, params):
     enc.capture(*ids.shape)
     enc.set_inputs(*tdev(ids, lens, cuda))
     assert torch.equal(enc.replay(), eager)
+    # concurrent micro-batches (sequences are independent): bit-identical, eager and replayed
+    for n in (2, 3):
+        enc_m = Int8Encoder(CFG, params, scales, cuda, micro_batches=n)
+        assert torch.equal(enc_m.forward(*tdev(ids, lens, cuda)), eager)
+        enc_m.capture(*ids.shape)
+        enc_m.set_inputs(*tdev(ids, lens, cuda))
+        assert torch.equal(enc_m.replay(), eager)

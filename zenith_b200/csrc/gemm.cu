@@ -30,7 +30,8 @@ static int pick_bn(int M, int N, const int* allowed, int n_allowed) {
 }
 
 template <int KIND, int BN, int STAGES, bool B_MN>
-static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams p, cudaStream_t stream) {
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, GemmParams p,
+                       cudaStream_t stream) {
   auto kernel = gemm_tc_kernel<KIND, BN, STAGES, B_MN>;
   constexpr size_t smem = gemm_smem_bytes<BN, STAGES>();
   static bool attr_set = false;  // per instantiation; setting twice is harmless
@@ -45,7 +46,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams 
   p.tiles_n = (p.N + BN - 1) / BN;
   const int tiles = p.tiles_m * p.tiles_n;
   const int grid = tiles < num_sms() ? tiles : num_sms();
-  return launch_pdl(kernel, dim3(grid), dim3(GEMM_THREADS), smem, stream, ta, tb, p);
+  return launch_pdl(kernel, dim3(grid), dim3(GEMM_THREADS), smem, stream, ta, tb, tc, p);
 }
 
 template <int KIND>
@@ -67,7 +68,20 @@ static int run_gemm(const void* A, int64_t lda, const void* B, int64_t ldb, Gemm
   else st = encode_tmap_2d(&tb, tmap_dtype<KIND>(), B, uint64_t(p.N), uint64_t(p.K), uint64_t(ldb) * ELEM, BK, BK);
   if (st != ZEN_OK) return st;
   p.num_k_blocks = (p.K + BK - 1) / BK;
-  return launch_gemm<KIND, BN, STAGES, B_MN>(ta, tb, p, stream);
+  // fp16 / int8 outputs with 16-byte aligned rows leave through shared memory and TMA stores of
+  // 32-row x 64-column blocks; anything else is stored by the epilogue threads directly
+  CUtensorMap tc = ta;
+  p.staged_store = 0;
+  const int oelem = p.out_dtype == ZEN_DT_S8 ? 1 : p.out_dtype == ZEN_DT_F16 ? 2 : 4;
+  if ((p.out_dtype == ZEN_DT_F16 || p.out_dtype == ZEN_DT_S8) && reinterpret_cast<uintptr_t>(p.out) % 16 == 0 &&
+      (p.ldo * oelem) % 16 == 0) {
+    st = encode_tmap_2d(&tc, p.out_dtype == ZEN_DT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8,
+                        p.out, uint64_t(p.N), uint64_t(p.M), uint64_t(p.ldo) * oelem, 64, 32,
+                        p.out_dtype == ZEN_DT_F16 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B);
+    if (st != ZEN_OK) return st;
+    p.staged_store = 1;
+  }
+  return launch_gemm<KIND, BN, STAGES, B_MN>(ta, tb, tc, p, stream);
 }
 
 // out[c, r] = in[r, c] for a row-major [rows, cols] fp32 matrix, 32 x 32 tiles through shared memory.
@@ -139,10 +153,10 @@ int zen_linear_i8(const int8_t* xq, int64_t ldx, const int8_t* wq, int64_t ldw, 
   static const int allowed[] = {64, 128, 192, 256};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (pick_bn(M, N, allowed, 4)) {
-    case 64: return run_gemm<KIND_I8, 64, 8, false>(xq, ldx, wq, ldw, p, s);
-    case 128: return run_gemm<KIND_I8, 128, 6, false>(xq, ldx, wq, ldw, p, s);
-    case 192: return run_gemm<KIND_I8, 192, 5, false>(xq, ldx, wq, ldw, p, s);
-    default: return run_gemm<KIND_I8, 256, 4, false>(xq, ldx, wq, ldw, p, s);
+    case 64: return run_gemm<KIND_I8, 64, 7, false>(xq, ldx, wq, ldw, p, s);
+    case 128: return run_gemm<KIND_I8, 128, 5, false>(xq, ldx, wq, ldw, p, s);
+    case 192: return run_gemm<KIND_I8, 192, 4, false>(xq, ldx, wq, ldw, p, s);
+    default: return run_gemm<KIND_I8, 256, 3, false>(xq, ldx, wq, ldw, p, s);
   }
 }
 
@@ -159,10 +173,10 @@ int zen_linear_f16(const void* x, int64_t ldx, const void* w, int64_t ldw, int M
   static const int allowed[] = {64, 128, 192, 256};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (pick_bn(M, N, allowed, 4)) {
-    case 64: return run_gemm<KIND_F16, 64, 8, false>(x, ldx, w, ldw, p, s);
-    case 128: return run_gemm<KIND_F16, 128, 6, false>(x, ldx, w, ldw, p, s);
-    case 192: return run_gemm<KIND_F16, 192, 5, false>(x, ldx, w, ldw, p, s);
-    default: return run_gemm<KIND_F16, 256, 4, false>(x, ldx, w, ldw, p, s);
+    case 64: return run_gemm<KIND_F16, 64, 7, false>(x, ldx, w, ldw, p, s);
+    case 128: return run_gemm<KIND_F16, 128, 5, false>(x, ldx, w, ldw, p, s);
+    case 192: return run_gemm<KIND_F16, 192, 4, false>(x, ldx, w, ldw, p, s);
+    default: return run_gemm<KIND_F16, 256, 3, false>(x, ldx, w, ldw, p, s);
   }
 }
 
@@ -178,9 +192,9 @@ int zen_linear_f32(const float* x, int64_t ldx, const float* w, int64_t ldw, int
   static const int allowed[] = {64, 128, 256};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (pick_bn(M, N, allowed, 3)) {
-    case 64: return run_gemm<KIND_TF32, 64, 8, false>(x, ldx, w, ldw, p, s);
-    case 128: return run_gemm<KIND_TF32, 128, 6, false>(x, ldx, w, ldw, p, s);
-    default: return run_gemm<KIND_TF32, 256, 4, false>(x, ldx, w, ldw, p, s);
+    case 64: return run_gemm<KIND_TF32, 64, 7, false>(x, ldx, w, ldw, p, s);
+    case 128: return run_gemm<KIND_TF32, 128, 5, false>(x, ldx, w, ldw, p, s);
+    default: return run_gemm<KIND_TF32, 256, 3, false>(x, ldx, w, ldw, p, s);
   }
 }
 
@@ -194,9 +208,9 @@ int zen_wmma_matmul_f16(const void* A, const void* B, float* C, int M, int N, in
   static const int allowed[] = {64, 128, 256};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (pick_bn(M, N, allowed, 3)) {
-    case 64: return run_gemm<KIND_F16, 64, 8, true>(A, K, B, N, p, s);
-    case 128: return run_gemm<KIND_F16, 128, 6, true>(A, K, B, N, p, s);
-    default: return run_gemm<KIND_F16, 256, 4, true>(A, K, B, N, p, s);
+    case 64: return run_gemm<KIND_F16, 64, 7, true>(A, K, B, N, p, s);
+    case 128: return run_gemm<KIND_F16, 128, 5, true>(A, K, B, N, p, s);
+    default: return run_gemm<KIND_F16, 256, 3, true>(A, K, B, N, p, s);
   }
 }
 

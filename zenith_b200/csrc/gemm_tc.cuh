@@ -4,8 +4,11 @@
 //
 //   warp 0      : TMA producer  — 128-byte-swizzled tiles of A and B into a STAGES-deep ring
 //   warp 1      : allocates TMEM, issues tcgen05.mma (one lane), commits stage / accumulator barriers
-//   warps 2..17 : epilogue — tcgen05.ld of the accumulator (four warps per 32-lane TMEM quadrant, taking
-//                 16-column steps round-robin), dequant / bias / activation / requant, 16-byte stores
+//   warps 2..17 : epilogue — four warps per 32-lane TMEM quadrant, each owning one 64-column slab of the
+//                 tile: tcgen05.ld in 16-column steps, dequant / bias / activation / requant, then the
+//                 32 x 64 block is staged in swizzled shared memory and written by one TMA store
+//                 (full 128-byte lines; edges clipped by the tensor map).  fp32 / int32 outputs and
+//                 unaligned outputs use per-thread 16-byte global stores instead.
 //
 // TMEM holds two accumulators (2 x BN columns) so the epilogue of tile i overlaps the MMAs of
 // tile i+1.  CTAs are persistent: tile t = blockIdx.x + i * gridDim.x, M-fastest.
@@ -33,6 +36,7 @@ struct GemmParams {
   float out_scale;
   const float* w_scale;
   const float* bias;
+  int staged_store;  // 1: fp16 / int8 output leaves through shared memory and TMA stores
 };
 
 template <int KIND>
@@ -61,8 +65,10 @@ __host__ __device__ constexpr uint32_t gemm_tmem_cols() {
 
 template <int BN, int STAGES>
 __host__ __device__ constexpr size_t gemm_smem_bytes() {
-  // ring + barriers/flags (256 B) + per-epilogue-warp scale and bias entries + alignment slack
-  return size_t(STAGES) * (GEMM_BM * 128 + BN * 128) + 256 + size_t(GEMM_EPI_WARPS) * 2 * (BN / 4 + 16) * 4 + 1024;
+  // ring + output staging (4 KB per active epilogue warp) + barriers/flags (256 B) + per-epilogue-warp
+  // scale and bias entries + alignment slack
+  return size_t(STAGES) * (GEMM_BM * 128 + BN * 128) + size_t((BN + 63) / 64) * 4 * 4096 + 256 +
+         size_t(GEMM_EPI_WARPS) * 2 * 64 * 4 + 1024;
 }
 
 template <int KIND>
@@ -156,9 +162,13 @@ __device__ __forceinline__ void requant_chunk(const float (&y)[GEMM_CW], float o
 // One GEMM_CW-column step of one accumulator row: dequant / bias / activation / conversion / store.
 // OUT and ACT are compile-time so that the independent element chains carry no branches and the
 // compiler can interleave them.
+// `stage` != nullptr: this lane's row of the warp's staging block (fp16: 128-byte rows, 128B swizzle;
+// int8: 64-byte rows, 64B swizzle — the layouts the output tensor map expects); `istep` is the
+// position of the step inside the 64-column slab.
 template <int KIND, int OUT, int ACT>
 __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[GEMM_CW], const float* sc, const float* bi,
-                                               const GemmParams& p, int row, int col0, bool full, float inv_scale) {
+                                               const GemmParams& p, int row, int col0, bool full, float inv_scale,
+                                               uint8_t* stage, int lane, int istep) {
   constexpr int CW = GEMM_CW;
   const int nvalid = p.N - col0;  // >= 1
   if constexpr (OUT == ZEN_DT_S32) {
@@ -188,6 +198,10 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[GEMM_CW], con
     if constexpr (OUT == ZEN_DT_S8) {
       uint32_t w[CW / 4];
       requant_chunk<ACT>(y, p.out_scale, inv_scale, p.round_mode, w);
+      if (stage != nullptr) {
+        *reinterpret_cast<uint4*>(stage + lane * 64 + ((istep ^ ((lane >> 1) & 3)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        return;
+      }
       int8_t* o = static_cast<int8_t*>(p.out) + int64_t(row) * p.ldo + col0;
       if (full) store_words<CW / 4>(o, w);
       else {
@@ -219,6 +233,12 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[GEMM_CW], con
           const __half2 h = __floats2half2_rn(y[2 * j], y[2 * j + 1]);
           w[j] = *reinterpret_cast<const uint32_t*>(&h);
         }
+        if (stage != nullptr) {
+          uint8_t* srow = stage + lane * 128;
+          *reinterpret_cast<uint4*>(srow + (((2 * istep) ^ (lane & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+          *reinterpret_cast<uint4*>(srow + (((2 * istep + 1) ^ (lane & 7)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
+          return;
+        }
         if (full) store_words<CW / 2>(o, w);
         else {
 #pragma unroll
@@ -232,17 +252,20 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[GEMM_CW], con
 
 template <int KIND, int OUT>
 __device__ __forceinline__ void epilogue_chunk_act(const uint32_t (&r)[GEMM_CW], const float* sc, const float* bi,
-                                                   const GemmParams& p, int row, int col0, bool full,
-                                                   float inv_scale) {
-  if (p.act == ZEN_ACT_GELU) epilogue_chunk<KIND, OUT, ZEN_ACT_GELU>(r, sc, bi, p, row, col0, full, inv_scale);
-  else if (p.act == ZEN_ACT_RELU) epilogue_chunk<KIND, OUT, ZEN_ACT_RELU>(r, sc, bi, p, row, col0, full, inv_scale);
-  else epilogue_chunk<KIND, OUT, ZEN_ACT_NONE>(r, sc, bi, p, row, col0, full, inv_scale);
+                                                   const GemmParams& p, int row, int col0, bool full, float inv_scale,
+                                                   uint8_t* stage, int lane, int istep) {
+  if (p.act == ZEN_ACT_GELU)
+    epilogue_chunk<KIND, OUT, ZEN_ACT_GELU>(r, sc, bi, p, row, col0, full, inv_scale, stage, lane, istep);
+  else if (p.act == ZEN_ACT_RELU)
+    epilogue_chunk<KIND, OUT, ZEN_ACT_RELU>(r, sc, bi, p, row, col0, full, inv_scale, stage, lane, istep);
+  else
+    epilogue_chunk<KIND, OUT, ZEN_ACT_NONE>(r, sc, bi, p, row, col0, full, inv_scale, stage, lane, istep);
 }
 
 template <int KIND, int BN, int STAGES, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-               const GemmParams p) {
+               const __grid_constant__ CUtensorMap tmap_c, const GemmParams p) {
   constexpr int ELEM = GemmKind<KIND>::ELEM;
   constexpr int BK = 128 / ELEM;  // elements per 128-byte swizzle row == K extent of one stage
   constexpr int UK = 32 / ELEM;   // K extent of one tcgen05.mma
@@ -259,7 +282,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  uint8_t* ctrl = smem + size_t(STAGES) * STAGE_BYTES;
+  constexpr int SLABS = (BN + 63) / 64;  // 64-column slabs of the tile, one per epilogue warp of a quadrant
+  uint8_t* out_stage = smem + size_t(STAGES) * STAGE_BYTES;  // [SLABS][4 quadrants][4 KB], 1024-byte aligned
+  uint8_t* ctrl = out_stage + size_t(SLABS) * 4 * 4096;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(ctrl);
   uint64_t* empty_bar = full_bar + STAGES;
   uint64_t* tfull_bar = empty_bar + STAGES;
@@ -276,6 +301,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
+    if (p.staged_store) tma_prefetch_desc(&tmap_c);
     for (int i = 0; i < STAGES; ++i) {
       mbar_init(&full_bar[i], 1);
       mbar_init(&empty_bar[i], 1);
@@ -374,63 +400,93 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
   } else {
     // ------------------------------------------------------------------ epilogue
-    const int quad = warp & 3;            // TMEM lane quadrant this warp may read
-    constexpr int SUBS = GEMM_EPI_WARPS / 4;
-    const int sub = (warp - 2) >> 2;      // which of the warps of this quadrant: takes steps c % SUBS == sub
-    // each warp stages the scale / bias entries of its own steps only: step c lives at (c / SUBS) * GEMM_CW
-    constexpr int COLS_PER_WARP = (BN / GEMM_CW + SUBS - 1) / SUBS * GEMM_CW;
-    float* s_scale = epi_rows + (warp - 2) * 2 * COLS_PER_WARP;
-    float* s_bias = s_scale + COLS_PER_WARP;
-    int acc = 0;
-    uint32_t acc_phase = 0;
-    const bool vec_ok = (reinterpret_cast<uintptr_t>(p.out) % 16 == 0) &&
-                        ((p.ldo * (p.out_dtype == ZEN_DT_S8 ? 1 : p.out_dtype == ZEN_DT_F16 ? 2 : 4)) % 16 == 0);
-    const float inv_scale = ZEN_DIV(1.0f, p.out_scale);
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-      const int m0 = (tile % p.tiles_m) * GEMM_BM;
-      const int n0 = (tile / p.tiles_m) * BN;
-      __syncwarp();
-      for (int i = lane; i < COLS_PER_WARP; i += 32) {
-        const int col = n0 + ((i / GEMM_CW) * SUBS + sub) * GEMM_CW + (i % GEMM_CW);
-        s_scale[i] = (p.w_scale != nullptr && col < p.N) ? __ldg(p.w_scale + col) : 1.0f;
-        s_bias[i] = (p.bias != nullptr && col < p.N) ? __ldg(p.bias + col) : 0.0f;
-      }
-      __syncwarp();
-      if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag)) break;
-      tc_fence_after_sync();
-      const int row = m0 + quad * 32 + lane;
-      const bool row_ok = row < p.M;
-      // This warp's steps are c = sub, sub + SUBS, ...  The loop is kept rolled: the step body (above all
-      // the GELU + requant one) is large, and unrolling it made instruction fetch the bottleneck.
-      const uint32_t tacc = tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * BN);
-#pragma unroll 1
-      for (int c = sub, i = 0; c < BN / GEMM_CW; c += SUBS, ++i) {
-        uint32_t r[GEMM_CW];
+    const int quad = warp & 3;        // TMEM lane quadrant this warp may read: rows quad*32 .. +31 of the tile
+    const int sub = (warp - 2) >> 2;  // 64-column slab of the tile owned by this warp
+    constexpr int STEPS = 64 / GEMM_CW;
+    if (sub * 64 < BN) {
+      float* s_scale = epi_rows + (warp - 2) * 2 * 64;
+      float* s_bias = s_scale + 64;
+      const int slab_cols = (BN - sub * 64) < 64 ? (BN - sub * 64) : 64;
+      const int elem = p.out_dtype == ZEN_DT_S8 ? 1 : p.out_dtype == ZEN_DT_F16 ? 2 : 4;
+      const bool vec_ok = (reinterpret_cast<uintptr_t>(p.out) % 16 == 0) && ((p.ldo * elem) % 16 == 0);
+      const bool staged = p.staged_store != 0;
+      uint8_t* stage = staged ? out_stage + size_t(sub * 4 + quad) * 4096 : nullptr;
+      const float inv_scale = ZEN_DIV(1.0f, p.out_scale);
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+        const int m0 = (tile % p.tiles_m) * GEMM_BM;
+        const int n0 = (tile / p.tiles_m) * BN + sub * 64;
         __syncwarp();
-        tmem_ld_32x16(tacc + uint32_t(c * GEMM_CW), r);
-        tmem_wait_ld();
-        const int col0 = n0 + c * GEMM_CW;
-        if (!row_ok || col0 >= p.N) continue;
-        const bool full = vec_ok && (col0 + GEMM_CW <= p.N);
-        const float* sc = s_scale + i * GEMM_CW;
-        const float* bi = s_bias + i * GEMM_CW;
-        if constexpr (KIND == KIND_I8) {
-          switch (p.out_dtype) {
-            case ZEN_DT_S32: epilogue_chunk<KIND, ZEN_DT_S32, ZEN_ACT_NONE>(r, sc, bi, p, row, col0, full, inv_scale); break;
-            case ZEN_DT_F32: epilogue_chunk_act<KIND, ZEN_DT_F32>(r, sc, bi, p, row, col0, full, inv_scale); break;
-            case ZEN_DT_F16: epilogue_chunk_act<KIND, ZEN_DT_F16>(r, sc, bi, p, row, col0, full, inv_scale); break;
-            default: epilogue_chunk_act<KIND, ZEN_DT_S8>(r, sc, bi, p, row, col0, full, inv_scale); break;
-          }
-        } else {
-          if (p.out_dtype == ZEN_DT_F32) epilogue_chunk_act<KIND, ZEN_DT_F32>(r, sc, bi, p, row, col0, full, inv_scale);
-          else epilogue_chunk_act<KIND, ZEN_DT_F16>(r, sc, bi, p, row, col0, full, inv_scale);
+        for (int i = lane; i < 64; i += 32) {
+          const int col = n0 + i;
+          s_scale[i] = (p.w_scale != nullptr && col < p.N) ? __ldg(p.w_scale + col) : 1.0f;
+          s_bias[i] = (p.bias != nullptr && col < p.N) ? __ldg(p.bias + col) : 0.0f;
         }
+        if (staged) {
+          if (lane == 0) tma_store_wait_read();  // the previous tile's store has finished reading the block
+        }
+        __syncwarp();
+        if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag)) break;
+        tc_fence_after_sync();
+        const int row = m0 + quad * 32 + lane;
+        const bool row_ok = row < p.M;
+        const uint32_t tacc = tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * BN + sub * 64);
+        // The loop is kept rolled: the step body (above all the GELU + requant one) is large, and
+        // unrolling it made instruction fetch the bottleneck.
+#pragma unroll 1
+        for (int i = 0; i < STEPS; ++i) {
+          if (i * GEMM_CW >= slab_cols) break;
+          uint32_t r[GEMM_CW];
+          __syncwarp();
+          tmem_ld_32x16(tacc + uint32_t(i * GEMM_CW), r);
+          tmem_wait_ld();
+          const int col0 = n0 + i * GEMM_CW;
+          if (!staged && (!row_ok || col0 >= p.N)) continue;
+          const bool full = vec_ok && (col0 + GEMM_CW <= p.N);
+          const float* sc = s_scale + i * GEMM_CW;
+          const float* bi = s_bias + i * GEMM_CW;
+          if constexpr (KIND == KIND_I8) {
+            switch (p.out_dtype) {
+              case ZEN_DT_S32:
+                epilogue_chunk<KIND, ZEN_DT_S32, ZEN_ACT_NONE>(r, sc, bi, p, row, col0, full, inv_scale, stage, lane, i);
+                break;
+              case ZEN_DT_F32: epilogue_chunk_act<KIND, ZEN_DT_F32>(r, sc, bi, p, row, col0, full, inv_scale, stage, lane, i); break;
+              case ZEN_DT_F16: epilogue_chunk_act<KIND, ZEN_DT_F16>(r, sc, bi, p, row, col0, full, inv_scale, stage, lane, i); break;
+              default: epilogue_chunk_act<KIND, ZEN_DT_S8>(r, sc, bi, p, row, col0, full, inv_scale, stage, lane, i); break;
+            }
+          } else {
+            if (p.out_dtype == ZEN_DT_F32)
+              epilogue_chunk_act<KIND, ZEN_DT_F32>(r, sc, bi, p, row, col0, full, inv_scale, stage, lane, i);
+            else
+              epilogue_chunk_act<KIND, ZEN_DT_F16>(r, sc, bi, p, row, col0, full, inv_scale, stage, lane, i);
+          }
+        }
+        __syncwarp();
+        tc_fence_before_sync();
+        mbar_arrive(&tempty_bar[acc]);  // the accumulator is free as soon as it has been read
+        if (staged) {
+          fence_proxy_async_smem();  // this lane's writes to the block -> visible to the TMA engine
+          __syncwarp();
+          if (lane == 0 && n0 < p.N && m0 + quad * 32 < p.M) {
+            tma_store_2d(&tmap_c, stage, n0, m0 + quad * 32);
+            tma_store_commit();
+          }
+        }
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
       }
-      __syncwarp();
-      tc_fence_before_sync();
-      mbar_arrive(&tempty_bar[acc]);
-      acc ^= 1;
-      if (acc == 0) acc_phase ^= 1u;
+      if (staged && lane == 0) tma_store_wait_all();
+    } else {
+      // no slab for this warp at this tile width: it still owes its arrivals on the accumulator barriers
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+        if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag)) break;
+        mbar_arrive(&tempty_bar[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
     }
   }
 

@@ -29,7 +29,8 @@ inline EncodeTiledFn encode_tiled_fn() {
 // Rank-`rank` tiled map with 128-byte swizzle; dims/strides innermost first, strides in bytes
 // for dims 1..rank-1.  Out-of-bounds elements read as zero.
 inline int encode_tmap(CUtensorMap* map, CUtensorMapDataType dt, int rank, const void* base, const uint64_t* dims,
-                       const uint64_t* strides_bytes, const uint32_t* box) {
+                       const uint64_t* strides_bytes, const uint32_t* box,
+                       CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return ZEN_ERR_DRIVER;
   cuuint64_t gdim[5];
@@ -47,17 +48,18 @@ inline int encode_tmap(CUtensorMap* map, CUtensorMapDataType dt, int rank, const
   }
   if (reinterpret_cast<uintptr_t>(base) % 16) return ZEN_ERR_UNSUPPORTED;
   CUresult r = fn(map, dt, static_cast<cuuint32_t>(rank), const_cast<void*>(base), gdim, gstr, bx, es,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? ZEN_OK : ZEN_ERR_DRIVER;
 }
 
 inline int encode_tmap_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* base, uint64_t inner, uint64_t outer,
-                          uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer) {
+                          uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer,
+                          CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
   const uint64_t dims[2] = {inner, outer};
   const uint64_t str[1] = {row_stride_bytes};
   const uint32_t box[2] = {box_inner, box_outer};
-  return encode_tmap(map, dt, 2, base, dims, str, box);
+  return encode_tmap(map, dt, 2, base, dims, str, box, swizzle);
 }
 
 // Launch with the programmatic-stream-serialization attribute (see grid_dependency_wait()).  Only for

@@ -78,6 +78,11 @@ def init_params(cfg: EncoderConfig, seed: int = 1234, random_affine: bool = Fals
     return p
 
 
+def _row_ptr(t: torch.Tensor, row0: int) -> int:
+    """Device address of row ``row0`` of a contiguous 1-D / 2-D tensor."""
+    return t.data_ptr() + row0 * (t.stride(0) if t.dim() > 1 else 1) * t.element_size()
+
+
 def _dev(a, dtype, device):
     return torch.from_numpy(np.ascontiguousarray(a)).to(device=device, dtype=dtype)
 
@@ -85,10 +90,11 @@ def _dev(a, dtype, device):
 class _EncoderBase:
     """Shared plumbing: embedding tables, per-shape buffers, the launch list, CUDA-graph capture."""
 
-    def __init__(self, cfg: EncoderConfig, params: dict, device):
+    def __init__(self, cfg: EncoderConfig, params: dict, device, micro_batches: int = 1):
         if cfg.head_dim not in (64, 128):
             raise RuntimeError("head_dim must be 64 or 128")
         self.cfg = cfg
+        self.micro_batches = max(1, int(micro_batches))
         self.device = torch.device(device)
         d = self.device
         self.word = _dev(params["word"], torch.float16, d)
@@ -112,19 +118,45 @@ class _EncoderBase:
         d = self.device
         self.ids = torch.zeros(B * S, dtype=torch.int32, device=d)
         self.kv_lens = torch.full((B,), S, dtype=torch.int32, device=d)
-        self._launches = []
-        self._build(B, S)
+        self._alloc(B, S)
+        # Sequences are independent through the whole encoder, so the batch may be cut into micro-batches
+        # whose launch sequences run side by side (separate streams / graph branches): the fill and
+        # drain latency of one micro-batch's kernels then hides behind the other's work.  Every
+        # micro-batch works on its own row range of the same buffers; results do not change.
+        n = min(self.micro_batches, B)
+        bounds = [(i * B // n, (i + 1) * B // n) for i in range(n)]
+        self._micro = []
+        for b0, b1 in bounds:
+            self._launches = []
+            self._build(b0, b1 - b0, S)
+            self._micro.append(self._launches)
+        self._launches = [l for m in self._micro for l in m]
         self.launches_per_forward = len(self._launches)
+        self._streams = [torch.cuda.Stream(device=d) for _ in range(len(self._micro) - 1)]
 
     def _add(self, fn: str, *args) -> None:
         self._launches.append((getattr(_capi.lib(), fn), fn, args))
 
-    def _run(self) -> None:
-        stream = torch.cuda.current_stream().cuda_stream
-        for f, name, args in self._launches:
+    @staticmethod
+    def _issue(launches, stream) -> None:
+        for f, name, args in launches:
             st = f(*args, stream)
             if st != 0:
                 _capi.check(name, st)
+
+    def _run(self) -> None:
+        main = torch.cuda.current_stream()
+        if len(self._micro) == 1:
+            self._issue(self._micro[0], main.cuda_stream)
+        else:
+            for s in self._streams:
+                s.wait_stream(main)
+            self._issue(self._micro[0], main.cuda_stream)
+            for s, launches in zip(self._streams, self._micro[1:]):
+                with torch.cuda.stream(s):
+                    self._issue(launches, s.cuda_stream)
+            for s in self._streams:
+                main.wait_stream(s)
         ops.launch_count += len(self._launches)
 
     # -- public ------------------------------------------------------------------------------
@@ -169,8 +201,8 @@ class _EncoderBase:
 class Fp16Encoder(_EncoderBase):
     """fp16 weights and activations, fp32 accumulation and statistics."""
 
-    def __init__(self, cfg: EncoderConfig, params: dict, device="cuda:0"):
-        super().__init__(cfg, params, device)
+    def __init__(self, cfg: EncoderConfig, params: dict, device="cuda:0", micro_batches: int = 1):
+        super().__init__(cfg, params, device, micro_batches)
         d = self.device
         self.layers = []
         for lp in params["layers"]:
@@ -180,9 +212,9 @@ class Fp16Encoder(_EncoderBase):
             self.layers.append(L)
         self.taps: dict | None = None  # filled by forward_with_taps
 
-    def _build(self, B: int, S: int) -> None:
+    def _alloc(self, B: int, S: int) -> None:
         cfg, d = self.cfg, self.device
-        T, H, F, nh, hd = B * S, cfg.hidden, cfg.ffn, cfg.heads, cfg.head_dim
+        T, H, F = B * S, cfg.hidden, cfg.ffn
         f16 = dict(dtype=torch.float16, device=d)
         self.x = [torch.empty((T, H), **f16) for _ in range(2)]
         self.qkv = torch.empty((T, 3 * H), **f16)
@@ -191,37 +223,46 @@ class Fp16Encoder(_EncoderBase):
         self.h1 = torch.empty((T, H), **f16)
         self.g = torch.empty((T, F), **f16)
         self.o = torch.empty((T, H), **f16)
-        self._add("zen_embed_layernorm_f16", self.ids.data_ptr(), None, self.word.data_ptr(), self.pos.data_ptr(),
-                  self.type.data_ptr(), self.emb_g.data_ptr(), self.emb_b.data_ptr(), self.x[0].data_ptr(), None, 1.0,
+        self.out = self.x[len(self.layers) & 1]
+
+    def _build(self, b0: int, B: int, S: int) -> None:
+        """Launch list for sequences [b0, b0 + B) of the batch (rows b0*S .. of every buffer)."""
+        cfg = self.cfg
+        T, H, F, nh, hd = B * S, cfg.hidden, cfg.ffn, cfg.heads, cfg.head_dim
+        r0 = b0 * S
+        P = lambda t: _row_ptr(t, r0)
+        self._add("zen_embed_layernorm_f16", P(self.ids), None, self.word.data_ptr(), self.pos.data_ptr(),
+                  self.type.data_ptr(), self.emb_g.data_ptr(), self.emb_b.data_ptr(), P(self.x[0]), None, 1.0,
                   ROUND_NEAREST_EVEN, T, S, H, cfg.vocab, cfg.eps)
         qs = (S * 3 * H, hd, 3 * H)
         os_ = (S * H, hd, H)
+        kv = self.kv_lens.data_ptr() + 4 * b0
         cur = 0
         for L in self.layers:
             x, xn = self.x[cur], self.x[cur ^ 1]
-            self._add("zen_linear_f16", x.data_ptr(), H, L["wqkv"].data_ptr(), H, T, 3 * H, H, L["bqkv"].data_ptr(),
-                      ACT_NONE, DT_F16, self.qkv.data_ptr(), 3 * H)
-            self._add("zen_flash_attention_f16", self.qkv.data_ptr(), self.qkv.data_ptr() + 2 * H,
-                      self.qkv.data_ptr() + 4 * H, self.ctx.data_ptr(), None, 1.0, B, nh, S, hd, *qs, *qs, *qs, *os_,
-                      self.kv_lens.data_ptr(), 0, 1.0 / math.sqrt(hd))
-            self._add("zen_linear_f16", self.ctx.data_ptr(), H, L["wo"].data_ptr(), H, T, H, H, L["bo"].data_ptr(),
-                      ACT_NONE, DT_F16, self.ao.data_ptr(), H)
-            self._add("zen_add_layernorm_f16", self.ao.data_ptr(), x.data_ptr(), L["ln1_g"].data_ptr(),
-                      L["ln1_b"].data_ptr(), self.h1.data_ptr(), None, 1.0, ROUND_NEAREST_EVEN, T, H, cfg.eps)
-            self._add("zen_linear_f16", self.h1.data_ptr(), H, L["w1"].data_ptr(), H, T, F, H, L["b1"].data_ptr(),
-                      ACT_GELU, DT_F16, self.g.data_ptr(), F)
-            self._add("zen_linear_f16", self.g.data_ptr(), F, L["w2"].data_ptr(), F, T, H, F, L["b2"].data_ptr(),
-                      ACT_NONE, DT_F16, self.o.data_ptr(), H)
-            self._add("zen_add_layernorm_f16", self.o.data_ptr(), self.h1.data_ptr(), L["ln2_g"].data_ptr(),
-                      L["ln2_b"].data_ptr(), xn.data_ptr(), None, 1.0, ROUND_NEAREST_EVEN, T, H, cfg.eps)
+            self._add("zen_linear_f16", P(x), H, L["wqkv"].data_ptr(), H, T, 3 * H, H, L["bqkv"].data_ptr(),
+                      ACT_NONE, DT_F16, P(self.qkv), 3 * H)
+            self._add("zen_flash_attention_f16", P(self.qkv), P(self.qkv) + 2 * H, P(self.qkv) + 4 * H, P(self.ctx), None,
+                      1.0, B, nh, S, hd, *qs, *qs, *qs, *os_, kv, 0, 1.0 / math.sqrt(hd))
+            self._add("zen_linear_f16", P(self.ctx), H, L["wo"].data_ptr(), H, T, H, H, L["bo"].data_ptr(),
+                      ACT_NONE, DT_F16, P(self.ao), H)
+            self._add("zen_add_layernorm_f16", P(self.ao), P(x), L["ln1_g"].data_ptr(), L["ln1_b"].data_ptr(),
+                      P(self.h1), None, 1.0, ROUND_NEAREST_EVEN, T, H, cfg.eps)
+            self._add("zen_linear_f16", P(self.h1), H, L["w1"].data_ptr(), H, T, F, H, L["b1"].data_ptr(),
+                      ACT_GELU, DT_F16, P(self.g), F)
+            self._add("zen_linear_f16", P(self.g), F, L["w2"].data_ptr(), F, T, H, F, L["b2"].data_ptr(),
+                      ACT_NONE, DT_F16, P(self.o), H)
+            self._add("zen_add_layernorm_f16", P(self.o), P(self.h1), L["ln2_g"].data_ptr(), L["ln2_b"].data_ptr(),
+                      P(xn), None, 1.0, ROUND_NEAREST_EVEN, T, H, cfg.eps)
             cur ^= 1
-        self.out = self.x[cur]
 
     def forward_with_taps(self, ids, kv_lens=None) -> dict:
         """One pass that also returns, per layer, (min, max) of the four tensors that feed a GEMM in the
         W8A8 dataflow: layer input ``x``, attention output ``ctx``, post-LN ``h1`` and GELU output
         ``gelu``.  Cold path used by calibration: runs layer by layer and reads back 8 floats per layer."""
         self.set_inputs(ids, kv_lens)
+        if len(self._micro) != 1:
+            raise RuntimeError("forward_with_taps needs micro_batches == 1")
         stream = torch.cuda.current_stream().cuda_stream
         taps = {p: [] for p in ACT_POINTS}
         per_layer = 7
@@ -251,8 +292,8 @@ class Int8Scales:
 class Int8Encoder(_EncoderBase):
     """W8A8 encoder: int8 GEMM operands, int32 accumulation, fp16 residual stream / LayerNorm / softmax."""
 
-    def __init__(self, cfg: EncoderConfig, params: dict, scales: Int8Scales, device="cuda:0"):
-        super().__init__(cfg, params, device)
+    def __init__(self, cfg: EncoderConfig, params: dict, scales: Int8Scales, device="cuda:0", micro_batches: int = 1):
+        super().__init__(cfg, params, device, micro_batches)
         d = self.device
         self.act_scales = scales.act
         self.layers = []
@@ -265,9 +306,9 @@ class Int8Encoder(_EncoderBase):
             L.update({k: _dev(lp[k], torch.float16, d) for k in ("ln1_g", "ln1_b", "ln2_g", "ln2_b")})
             self.layers.append(L)
 
-    def _build(self, B: int, S: int) -> None:
+    def _alloc(self, B: int, S: int) -> None:
         cfg, d = self.cfg, self.device
-        T, H, F, nh, hd = B * S, cfg.hidden, cfg.ffn, cfg.heads, cfg.head_dim
+        T, H, F = B * S, cfg.hidden, cfg.ffn
         f16 = dict(dtype=torch.float16, device=d)
         s8 = dict(dtype=torch.int8, device=d)
         self.x = [torch.empty((T, H), **f16) for _ in range(2)]
@@ -280,47 +321,51 @@ class Int8Encoder(_EncoderBase):
         self.h1q = torch.empty((T, H), **s8)
         self.gq = torch.empty((T, F), **s8)
         self.o = torch.empty((T, H), **f16)
+        self.out = self.x[len(self.layers) & 1]
+
+    def _build(self, b0: int, B: int, S: int) -> None:
+        """Launch list for sequences [b0, b0 + B) of the batch (rows b0*S .. of every buffer)."""
+        cfg = self.cfg
+        T, H, F, nh, hd = B * S, cfg.hidden, cfg.ffn, cfg.heads, cfg.head_dim
+        r0 = b0 * S
+        P = lambda t: _row_ptr(t, r0)
         sc = self.act_scales
-        self._add("zen_embed_layernorm_f16", self.ids.data_ptr(), None, self.word.data_ptr(), self.pos.data_ptr(),
-                  self.type.data_ptr(), self.emb_g.data_ptr(), self.emb_b.data_ptr(), self.x[0].data_ptr(),
-                  self.xq[0].data_ptr(), sc[0]["x"], ROUND_NEAREST_EVEN, T, S, H, cfg.vocab, cfg.eps)
+        self._add("zen_embed_layernorm_f16", P(self.ids), None, self.word.data_ptr(), self.pos.data_ptr(),
+                  self.type.data_ptr(), self.emb_g.data_ptr(), self.emb_b.data_ptr(), P(self.x[0]), P(self.xq[0]),
+                  sc[0]["x"], ROUND_NEAREST_EVEN, T, S, H, cfg.vocab, cfg.eps)
         qs = (S * 3 * H, hd, 3 * H)
         os_ = (S * H, hd, H)
+        kv = self.kv_lens.data_ptr() + 4 * b0
         cur = 0
         n_layers = len(self.layers)
         for li, L in enumerate(self.layers):
             a = sc[li]
             x, xq, xn, xqn = self.x[cur], self.xq[cur], self.x[cur ^ 1], self.xq[cur ^ 1]
             last = li == n_layers - 1
-            self._add("zen_linear_i8", xq.data_ptr(), H, L["wqkv"].data_ptr(), H, T, 3 * H, H, a["x"],
-                      L["wqkv_s"].data_ptr(), L["bqkv"].data_ptr(), ACT_NONE, DT_F16, 1.0, ROUND_NEAREST_EVEN,
-                      self.qkv.data_ptr(), 3 * H)
-            self._add("zen_flash_attention_f16", self.qkv.data_ptr(), self.qkv.data_ptr() + 2 * H,
-                      self.qkv.data_ptr() + 4 * H, self.ctx.data_ptr(), self.ctxq.data_ptr(), a["ctx"], B, nh, S, hd,
-                      *qs, *qs, *qs, *os_, self.kv_lens.data_ptr(), 0, 1.0 / math.sqrt(hd))
-            self._add("zen_linear_i8", self.ctxq.data_ptr(), H, L["wo"].data_ptr(), H, T, H, H, a["ctx"],
-                      L["wo_s"].data_ptr(), L["bo"].data_ptr(), ACT_NONE, DT_F16, 1.0, ROUND_NEAREST_EVEN,
-                      self.ao.data_ptr(), H)
-            self._add("zen_add_layernorm_f16", self.ao.data_ptr(), x.data_ptr(), L["ln1_g"].data_ptr(),
-                      L["ln1_b"].data_ptr(), self.h1.data_ptr(), self.h1q.data_ptr(), a["h1"], ROUND_NEAREST_EVEN, T, H,
+            self._add("zen_linear_i8", P(xq), H, L["wqkv"].data_ptr(), H, T, 3 * H, H, a["x"], L["wqkv_s"].data_ptr(),
+                      L["bqkv"].data_ptr(), ACT_NONE, DT_F16, 1.0, ROUND_NEAREST_EVEN, P(self.qkv), 3 * H)
+            self._add("zen_flash_attention_f16", P(self.qkv), P(self.qkv) + 2 * H, P(self.qkv) + 4 * H, P(self.ctx),
+                      P(self.ctxq), a["ctx"], B, nh, S, hd, *qs, *qs, *qs, *os_, kv, 0, 1.0 / math.sqrt(hd))
+            self._add("zen_linear_i8", P(self.ctxq), H, L["wo"].data_ptr(), H, T, H, H, a["ctx"], L["wo_s"].data_ptr(),
+                      L["bo"].data_ptr(), ACT_NONE, DT_F16, 1.0, ROUND_NEAREST_EVEN, P(self.ao), H)
+            self._add("zen_add_layernorm_f16", P(self.ao), P(x), L["ln1_g"].data_ptr(), L["ln1_b"].data_ptr(),
+                      P(self.h1), P(self.h1q), a["h1"], ROUND_NEAREST_EVEN, T, H, cfg.eps)
+            self._add("zen_linear_i8", P(self.h1q), H, L["w1"].data_ptr(), H, T, F, H, a["h1"], L["w1_s"].data_ptr(),
+                      L["b1"].data_ptr(), ACT_GELU, DT_S8, a["gelu"], ROUND_NEAREST_EVEN, P(self.gq), F)
+            self._add("zen_linear_i8", P(self.gq), F, L["w2"].data_ptr(), F, T, H, F, a["gelu"], L["w2_s"].data_ptr(),
+                      L["b2"].data_ptr(), ACT_NONE, DT_F16, 1.0, ROUND_NEAREST_EVEN, P(self.o), H)
+            self._add("zen_add_layernorm_f16", P(self.o), P(self.h1), L["ln2_g"].data_ptr(), L["ln2_b"].data_ptr(),
+                      P(xn), None if last else P(xqn), 1.0 if last else sc[li + 1]["x"], ROUND_NEAREST_EVEN, T, H,
                       cfg.eps)
-            self._add("zen_linear_i8", self.h1q.data_ptr(), H, L["w1"].data_ptr(), H, T, F, H, a["h1"],
-                      L["w1_s"].data_ptr(), L["b1"].data_ptr(), ACT_GELU, DT_S8, a["gelu"], ROUND_NEAREST_EVEN,
-                      self.gq.data_ptr(), F)
-            self._add("zen_linear_i8", self.gq.data_ptr(), F, L["w2"].data_ptr(), F, T, H, F, a["gelu"],
-                      L["w2_s"].data_ptr(), L["b2"].data_ptr(), ACT_NONE, DT_F16, 1.0, ROUND_NEAREST_EVEN,
-                      self.o.data_ptr(), H)
-            self._add("zen_add_layernorm_f16", self.o.data_ptr(), self.h1.data_ptr(), L["ln2_g"].data_ptr(),
-                      L["ln2_b"].data_ptr(), xn.data_ptr(), None if last else xqn.data_ptr(),
-                      1.0 if last else sc[li + 1]["x"], ROUND_NEAREST_EVEN, T, H, cfg.eps)
             cur ^= 1
-        self.out = self.x[cur]
 
     def forward_layerwise(self, ids, kv_lens=None):
         """Generator for tests: runs the pass one layer at a time and yields ``(layer, buffers)`` after
         each layer, where ``buffers`` are the live device tensors of that layer (inputs and outputs of
         every kernel), so that each kernel can be checked in isolation on the inputs it really saw."""
         self.set_inputs(ids, kv_lens)
+        if len(self._micro) != 1:
+            raise RuntimeError("forward_layerwise needs micro_batches == 1")
         stream = torch.cuda.current_stream().cuda_stream
         f, name, args = self._launches[0]
         _capi.check(name, f(*args, stream))
