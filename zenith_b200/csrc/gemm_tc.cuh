@@ -110,49 +110,44 @@ __device__ __forceinline__ float gelu_fast(float x) {
 constexpr int GEMM_CW = 16;  // accumulator columns per epilogue step (kept small: the step is the unrolled unit)
 
 // Requantisation to int8 with the exact result of  clamp(round(act(y) / out_scale))  at a fraction of
-// its cost.  The quotient is first formed with approximate arithmetic (error far below MARGIN in
-// units of one int8 step); unless it lies within MARGIN of a rounding boundary its rounding is already
-// the exact answer.  The few elements that do (about 2 in 1000) are recomputed with the
-// individually rounded IEEE operations of det_math.h, so the output is bit-identical to the CPU
-// definition everywhere.  Nearest-even rounding uses the 1.5 * 2^23 magic constant (exact rint for
-// |t| < 2^22, and the integer falls out of the mantissa), which keeps the conversion units free.
+// its cost.  y is exact; the quotient t is formed with approximate arithmetic (hardware exp2 /
+// reciprocal, reciprocal multiply): relative error below 1e-6, i.e. below 1e-6 |t| of an int8 step.
+// Unless t lies within 4e-6 |t| + 2e-6 of a rounding boundary its rounding is already the exact
+// answer; the rare elements that do are recomputed with the individually rounded IEEE operations of
+// det_math.h, so the output is bit-identical to the CPU definition everywhere.  Nearest-even rounding uses the 1.5 * 2^23 constant (exact rint for
+// |t| < 2^22, the integer falls out of the mantissa), which keeps the conversion units free.
 template <int ACT>
-__device__ __forceinline__ void requant_chunk(const float (&y)[GEMM_CW], float out_scale, float inv_scale,
-                                              int round_mode, uint32_t (&packed)[GEMM_CW / 4]) {
-  constexpr float MARGIN = 1e-3f;
+__device__ __forceinline__ uint32_t requant_fast(const float (&yfast)[GEMM_CW], float inv_scale, int round_mode,
+                                                 int (&q)[GEMM_CW]) {
   constexpr float MAGIC = 12582912.0f;  // 1.5 * 2^23
-  int q[GEMM_CW];
   uint32_t risky = 0;
   if (round_mode == 0) {
 #pragma unroll
     for (int j = 0; j < GEMM_CW; ++j) {
-      float g = y[j];
+      float g = yfast[j];
       if constexpr (ACT == ZEN_ACT_GELU) g = gelu_fast(g);
-      if constexpr (ACT == ZEN_ACT_RELU) g = g > 0.0f ? g : 0.0f;
-      const float t = g * inv_scale;
-      const float tc = fminf(fmaxf(t, -128.0f), 127.0f);  // NaN -> -128, as in the exact definition
+      if constexpr (ACT == ZEN_ACT_RELU) g = fmaxf(g, 0.0f);
+      const float tc = fminf(fmaxf(g * inv_scale, -128.0f), 127.0f);  // NaN -> -128, as in the exact definition
       const float m = tc + MAGIC;
       q[j] = __float_as_int(m) - 0x4B400000;
-      const float d = 0.5f - fabsf(tc - (m - MAGIC));  // distance of tc to the nearest half-integer
-      if (d < MARGIN && fabsf(t) < 130.0f) risky |= 1u << j;
+      // |tc - rint(tc)| close to 0.5 <=> close to a rounding boundary (a clamped value has distance 0)
+      if (fabsf(tc - (m - MAGIC)) > fmaf(fabsf(tc), -4e-6f, 0.5f - 2e-6f)) risky |= 1u << j;
     }
   } else {
 #pragma unroll
     for (int j = 0; j < GEMM_CW; ++j) {
-      float g = y[j];
+      float g = yfast[j];
       if constexpr (ACT == ZEN_ACT_GELU) g = gelu_fast(g);
-      if constexpr (ACT == ZEN_ACT_RELU) g = g > 0.0f ? g : 0.0f;
+      if constexpr (ACT == ZEN_ACT_RELU) g = fmaxf(g, 0.0f);
       const float t = g * inv_scale;
-      const float tc = fminf(fmaxf(t, -128.0f), 127.0f);
-      q[j] = __float2int_rz(tc);
-      if (fabsf(t - rintf(t)) < MARGIN && fabsf(t) < 130.0f) risky |= 1u << j;  // boundaries are the integers
+      q[j] = __float2int_rz(fminf(fmaxf(t, -128.0f), 127.0f));
+      if (fabsf(t - rintf(t)) < 1e-3f && fabsf(t) < 130.0f) risky |= 1u << j;  // boundaries are the integers
     }
   }
-  if (risky) {
-#pragma unroll
-    for (int j = 0; j < GEMM_CW; ++j)
-      if (risky & (1u << j)) q[j] = zen_det_round_clamp_i8(ZEN_DIV(zen_det_act(y[j], ACT), out_scale), round_mode);
-  }
+  return risky;
+}
+
+__device__ __forceinline__ void pack_q(const int (&q)[GEMM_CW], uint32_t (&packed)[GEMM_CW / 4]) {
 #pragma unroll
   for (int j = 0; j < GEMM_CW / 4; ++j)
     packed[j] = (uint32_t(q[4 * j]) & 0xffu) | ((uint32_t(q[4 * j + 1]) & 0xffu) << 8) |
@@ -197,7 +192,15 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[GEMM_CW], con
     }
     if constexpr (OUT == ZEN_DT_S8) {
       uint32_t w[CW / 4];
-      requant_chunk<ACT>(y, p.out_scale, inv_scale, p.round_mode, w);
+      int q[CW];
+      const uint32_t risky = requant_fast<ACT>(y, inv_scale, p.round_mode, q);
+      if (risky) {
+#pragma unroll
+        for (int j = 0; j < CW; ++j)
+          if (risky & (1u << j))
+            q[j] = zen_det_round_clamp_i8(ZEN_DIV(zen_det_act(y[j], ACT), p.out_scale), p.round_mode);
+      }
+      pack_q(q, w);
       if (stage != nullptr) {
         *reinterpret_cast<uint4*>(stage + lane * 64 + ((istep ^ ((lane >> 1) & 3)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
         return;
