@@ -106,6 +106,22 @@ size_t zen_matmul_f32_workspace_bytes(int N, int K);
 int zen_matmul_f32(const float* A, const float* B, float* C, int M, int N, int K, void* workspace,
                    size_t workspace_bytes, void* stream);
 
+/* The same product as zen_matmul_f32 for callers that have no way to provide a workspace.  It has no
+ * counterpart in the reference.  Who needs it: code that runs where device memory cannot be obtained —
+ * inside a stream capture (cudaMalloc is not allowed there), in a serving loop that must not hit the
+ * allocator's implicit device synchronisation, or behind a dispatcher that hands a kernel nothing but
+ * its inputs and outputs.  The transposed copy of B goes to a fixed array that lives in the library
+ * image on every GPU that loads it (ZEN_MATMUL_STATIC_MAX_ELEMS floats = 4 MiB per device, held until
+ * the process exits); N * K may not exceed that count (ZEN_ERR_TOO_LARGE otherwise).  Nothing is
+ * allocated or freed, here or in anything this calls.
+ * The first call on each device looks the array's address up (cudaGetSymbolAddress, with that device
+ * current); make that first call outside any stream capture.  All calls on a device share the one
+ * array: two calls whose kernels may overlap on the GPU (different streams without an ordering
+ * between them) race on it and must be serialised by the caller.  The array keeps the previous call's
+ * contents; this entry point overwrites every element it later reads, so no clearing is needed. */
+#define ZEN_MATMUL_STATIC_MAX_ELEMS (1 << 20)
+int zen_matmul_f32_static(const float* A, const float* B, float* C, int M, int N, int K, void* stream);
+
 /* Elementwise.  n = element count.
  * gelu: core/src/cuda_kernels.cu:115-126,559-562 (gelu_f32), core/src/fp16_kernels.cu:128-147.
  * relu: core/src/cuda_kernels.cu relu_f32 (zenith_cuda.relu). */

@@ -30,6 +30,7 @@ SIGNATURES = {
     "zen_wmma_matmul_f16": [_p, _p, _p, _i, _i, _i, _p],
     "zen_matmul_f32_workspace_bytes": [_i, _i],
     "zen_matmul_f32": [_p, _p, _p, _i, _i, _i, _p, C.c_size_t, _p],
+    "zen_matmul_f32_static": [_p, _p, _p, _i, _i, _i, _p],
     "zen_gelu_f32": [_p, _p, _i64, _p],
     "zen_gelu_f16": [_p, _p, _i64, _p],
     "zen_relu_f32": [_p, _p, _i64, _p],

@@ -1,6 +1,7 @@
 // Host side of the tcgen05 GEMMs: tile selection, tensor maps, launches, C ABI.
 #include "gemm_tc.cuh"
 #include "tma_host.cuh"
+#include <mutex>
 
 namespace zen {
 
@@ -228,6 +229,51 @@ int zen_matmul_f32(const float* A, const float* B, float* C, int M, int N, int K
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   float* Bt = static_cast<float*>(workspace);
   int st = launch_transpose_f32(B, Bt, K, N, s);
+  if (st != ZEN_OK) return st;
+  return zen_linear_f32(A, K, Bt, K, M, N, K, nullptr, ZEN_ACT_NONE, C, N, stream);
+}
+
+// ------------------------------------------------------------------------------------------------
+// zen_matmul_f32 without a caller workspace
+// ------------------------------------------------------------------------------------------------
+// Scratch for the transposed B operand, resident in every device that loads this library for as long
+// as the process lives.  In host code the NAME below is only a stand-in for the symbol: it is not a
+// device address and must never be handed to a kernel.  The address valid on a given device is
+// obtained once per device with cudaGetSymbolAddress (scratch_for_current_device) and that pointer is
+// what the kernels receive.
+static __device__ __align__(256) float g_matmul_static_scratch[ZEN_MATMUL_STATIC_MAX_ELEMS];
+
+static int scratch_for_current_device(float** out) {
+  constexpr int kMaxDevices = 64;
+  static std::mutex mu;
+  static float* per_device[kMaxDevices] = {};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    cudaGetLastError();
+    return ZEN_ERR_LAUNCH;
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  if (per_device[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_matmul_static_scratch) != cudaSuccess || p == nullptr) {
+      cudaGetLastError();
+      return ZEN_ERR_LAUNCH;
+    }
+    per_device[dev] = static_cast<float*>(p);
+  }
+  *out = per_device[dev];
+  return ZEN_OK;
+}
+
+int zen_matmul_f32_static(const float* A, const float* B, float* C, int M, int N, int K, void* stream) {
+  if (!A || !B || !C || M <= 0 || N <= 0 || K <= 0) return ZEN_ERR_INVALID_ARG;
+  if (K % 4) return ZEN_ERR_UNSUPPORTED;
+  if (size_t(N) * size_t(K) > size_t(ZEN_MATMUL_STATIC_MAX_ELEMS)) return ZEN_ERR_TOO_LARGE;
+  float* Bt = nullptr;
+  int st = scratch_for_current_device(&Bt);
+  if (st != ZEN_OK) return st;
+  // every element of Bt that the GEMM reads is written by the transpose first: nothing needs clearing
+  st = launch_transpose_f32(B, Bt, K, N, static_cast<cudaStream_t>(stream));
   if (st != ZEN_OK) return st;
   return zen_linear_f32(A, K, Bt, K, M, N, K, nullptr, ZEN_ACT_NONE, C, N, stream);
 }
