@@ -145,7 +145,7 @@ def run_reference_arm(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    sample = 8
+    sample = 4
     r = cpu_executor(sample, max(1, args.steps), max(1, min(args.warmup, 2)))
     line = {
         "impl": "reference", "metric": METRIC, "value": r["seq_per_s"], "unit": "sequences/s", "n_gpus": args.gpus,
@@ -310,7 +310,11 @@ def run_ours(args) -> None:
             "bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TOP/s", "frac": achieved / int8_peak,
             "peak_source": f"2 x {peaks['source']} bf16 GEMM burst ({peaks['bf16_tflops']} TFLOP/s): int8 issues at "
                            "twice the bf16 rate; nominal dense int8 is 4500 TOP/s",
-            "frac_of_nominal": achieved / 4500.0, "traffic": None, "per_shape": g["per_shape"]}
+            "frac_of_nominal": achieved / 4500.0,
+            # DRAM bytes of the same four launches from profiles/gemm_i8_bert_base_layer_shapes.md (ncu): reads
+            # only and equal to the operand bytes; the outputs are still in L2 when each kernel ends
+            "traffic": 29.46e6, "traffic_unit": "bytes per layer (4 launches)",
+            "algorithmic_bytes": 73.1e6, "per_shape": g["per_shape"]}
         gemm_ms_per_step = 12 * g["us_per_layer"] / 1e3
         line["roofline"]["gemm_share_of_step"] = gemm_ms_per_step / (total_ms / K)
         try:
