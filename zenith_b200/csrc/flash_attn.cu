@@ -396,7 +396,7 @@ static int launch_fa(const CUtensorMap& tq, const CUtensorMap& tk, const CUtenso
     attr_set = true;
   }
   dim3 grid((p.S + FA_BQ - 1) / FA_BQ, p.H, p.B);
-  return launch_pdl(kernel, grid, dim3(FA_THREADS), smem, s, tq, tk, tv, p);
+  return launch_pdl(PDL_ATTENTION, kernel, grid, dim3(FA_THREADS), smem, s, tq, tk, tv, p);
 }
 
 }  // namespace zen

@@ -47,7 +47,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
   p.tiles_n = (p.N + BN - 1) / BN;
   const int tiles = p.tiles_m * p.tiles_n;
   const int grid = tiles < num_sms() ? tiles : num_sms();
-  return launch_pdl(kernel, dim3(grid), dim3(GEMM_THREADS), smem, stream, ta, tb, tc, p);
+  return launch_pdl(PDL_GEMM, kernel, dim3(grid), dim3(GEMM_THREADS), smem, stream, ta, tb, tc, p);
 }
 
 template <int KIND>

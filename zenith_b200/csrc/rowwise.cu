@@ -274,13 +274,13 @@ static int launch_ln(const RowParams& p, cudaStream_t s) {
   const int grid = (p.rows + ROW_WARPS - 1) / ROW_WARPS;
   if (aligned && vecs <= 8) {
     switch (vecs) {
-      case 1: return launch_pdl(ln_warp_kernel<T, 1, SRC>, dim3(grid), dim3(ROW_WARPS * 32), 0, s, p);
-      case 2: return launch_pdl(ln_warp_kernel<T, 2, SRC>, dim3(grid), dim3(ROW_WARPS * 32), 0, s, p);
-      case 3: return launch_pdl(ln_warp_kernel<T, 3, SRC>, dim3(grid), dim3(ROW_WARPS * 32), 0, s, p);
-      case 4: return launch_pdl(ln_warp_kernel<T, 4, SRC>, dim3(grid), dim3(ROW_WARPS * 32), 0, s, p);
+      case 1: return launch_pdl(PDL_ROW, ln_warp_kernel<T, 1, SRC>, dim3(grid), dim3(ROW_WARPS * 32), 0, s, p);
+      case 2: return launch_pdl(PDL_ROW, ln_warp_kernel<T, 2, SRC>, dim3(grid), dim3(ROW_WARPS * 32), 0, s, p);
+      case 3: return launch_pdl(PDL_ROW, ln_warp_kernel<T, 3, SRC>, dim3(grid), dim3(ROW_WARPS * 32), 0, s, p);
+      case 4: return launch_pdl(PDL_ROW, ln_warp_kernel<T, 4, SRC>, dim3(grid), dim3(ROW_WARPS * 32), 0, s, p);
       case 5:
-      case 6: return launch_pdl(ln_warp_kernel<T, 6, SRC>, dim3(grid), dim3(ROW_WARPS * 32), 0, s, p);
-      default: return launch_pdl(ln_warp_kernel<T, 8, SRC>, dim3(grid), dim3(ROW_WARPS * 32), 0, s, p);
+      case 6: return launch_pdl(PDL_ROW, ln_warp_kernel<T, 6, SRC>, dim3(grid), dim3(ROW_WARPS * 32), 0, s, p);
+      default: return launch_pdl(PDL_ROW, ln_warp_kernel<T, 8, SRC>, dim3(grid), dim3(ROW_WARPS * 32), 0, s, p);
     }
   } else {
     ln_block_kernel<T, SRC><<<p.rows, 256, 0, s>>>(p);
