@@ -5,10 +5,12 @@ extern "C" {
 int zen_tu_status_gemm(int* out, int clear);
 int zen_tu_status_rowwise(int* out, int clear);
 int zen_tu_status_flash_attn(int* out, int clear);
+int zen_tu_status_gemm_ln(int* out, int clear);
 }
 
 typedef int (*TuStatusFn)(int*, int);
-static const TuStatusFn kTuStatus[] = {zen_tu_status_gemm, zen_tu_status_rowwise, zen_tu_status_flash_attn};
+static const TuStatusFn kTuStatus[] = {zen_tu_status_gemm, zen_tu_status_rowwise, zen_tu_status_flash_attn,
+                                        zen_tu_status_gemm_ln};
 
 static int fold_status(int* out, int clear) {
   if (cudaDeviceSynchronize() != cudaSuccess) {

@@ -37,7 +37,11 @@ def _time(fn, iters, flush):
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["gemm_i8", "gemm_f16", "add_ln", "attention"])
+    ap.add_argument("case", choices=["gemm_i8", "gemm_f16", "add_ln", "attention", "encoder"])
+    ap.add_argument("--config", choices=["base", "large"], default="base")
+    ap.add_argument("--dtype", choices=["int8", "fp16"], default="int8")
+    ap.add_argument("--batch", type=int, default=32)
+    ap.add_argument("--seq", type=int, default=128)
     ap.add_argument("--m", type=int, default=4096)
     ap.add_argument("--n", type=int, default=2304)
     ap.add_argument("--k", type=int, default=768)
@@ -85,6 +89,34 @@ def main() -> None:
         med, best = _time(lambda: ops.add_layernorm(x, r, g, be, 1e-12, out_scale=0.03), a.iters, flush)
         nbytes = a.rows * a.hidden * 7  # 2 fp16 reads, 1 fp16 write, 1 int8 write
         out.update(rows=a.rows, hidden=a.hidden, us=med, us_min=best, gbs=nbytes / med / 1e3)
+    elif a.case == "encoder":
+        import numpy as np
+
+        from .calibrate import calibrate
+        from .encoder import BERT_BASE, BERT_LARGE, Fp16Encoder, Int8Encoder, init_params
+
+        cfg = BERT_BASE if a.config == "base" else BERT_LARGE
+        params = init_params(cfg, 1234)
+        rng = np.random.default_rng(0)
+
+        def batch():
+            ids = torch.from_numpy(rng.integers(0, cfg.vocab, (a.batch, a.seq)).astype(np.int32)).to(dev)
+            lens = torch.from_numpy((a.seq - rng.integers(0, 33, a.batch)).astype(np.int32)).to(dev)
+            return ids, lens
+
+        if a.dtype == "int8":
+            enc = Int8Encoder(cfg, params, calibrate(cfg, params, [batch() for _ in range(4)], dev), dev)
+        else:
+            enc = Fp16Encoder(cfg, params, dev)
+        enc.capture(a.batch, a.seq)
+        enc.set_inputs(*batch())
+        med, best = _time(enc.replay, a.iters, flush)
+        T = a.batch * a.seq
+        gemm_ops = 2.0 * T * (4 * cfg.hidden**2 + 2 * cfg.hidden * cfg.ffn) * cfg.layers
+        attn_flops = 4.0 * a.batch * cfg.heads * a.seq * a.seq * cfg.head_dim * cfg.layers
+        out.update(config=a.config, dtype=a.dtype, batch=a.batch, seq=a.seq, us=med, us_min=best,
+                   seq_per_s=a.batch / med * 1e6, gemm_tops=gemm_ops / med / 1e6, attn_tflops=attn_flops / med / 1e6,
+                   launches=enc.launches_per_forward)
     else:
         q = torch.randn(a.b, a.h, a.s, a.d, device=dev, dtype=torch.float16)
         k = torch.randn_like(q)

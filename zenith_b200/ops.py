@@ -95,6 +95,34 @@ def linear_int8(xq, wq, x_scale: float, w_scale=None, bias=None, *, act="none", 
     return out
 
 
+def linear_int8_add_layernorm(xq, wq, x_scale: float, w_scale, bias, residual, gamma, beta, eps: float, *,
+                              out_scale: float | None = None, round="nearest_even"):
+    """``LayerNorm(dequant(xq @ wq.T) + bias + residual) * gamma + beta`` in one kernel (hidden size 768).
+
+    Returns fp16 ``y`` and, with ``out_scale``, also the int8 copy ``quantize(y, out_scale)``.
+    """
+    _require(xq, "xq", torch.int8, 2)
+    _require(wq, "wq", torch.int8, 2)
+    _require(residual, "residual", torch.float16, 2)
+    _require(gamma, "gamma", torch.float16, 1)
+    _require(beta, "beta", torch.float16, 1)
+    M, K = xq.shape
+    N = wq.shape[0]
+    if wq.shape[1] != K or tuple(residual.shape) != (M, N):
+        raise RuntimeError("shape mismatch")
+    if w_scale is not None:
+        _require(w_scale, "w_scale", torch.float32, 1)
+    if bias is not None:
+        _require(bias, "bias", torch.float32, 1)
+    y = torch.empty((M, N), dtype=torch.float16, device=xq.device)
+    yq = torch.empty((M, N), dtype=torch.int8, device=xq.device) if out_scale is not None else None
+    if M:
+        _call("zen_linear_i8_add_layernorm", xq.data_ptr(), K, wq.data_ptr(), K, M, N, K, float(x_scale), _ptr(w_scale),
+              _ptr(bias), residual.data_ptr(), N, gamma.data_ptr(), beta.data_ptr(), float(eps), y.data_ptr(), _ptr(yq),
+              float(out_scale or 1.0), _ROUND[round], _stream())
+    return y if yq is None else (y, yq)
+
+
 def linear_fp16(x, w, bias=None, *, act="none", out_dtype=torch.float16, out=None):
     """``act(x @ w.T + bias)`` with fp16 operands, fp32 accumulation (core/src/fp16_kernels.cu:92-122)."""
     _require(x, "x", torch.float16, 2)
