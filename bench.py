@@ -11,7 +11,7 @@ over 30522 words, the last 0..32 positions of each row masked).  Ranks are indep
 (weak scaling, global batch 32 * N); for N > 1 each step ends with the NCCL all_gather of the hidden
 states.  Rank 0 prints ONE JSON line.
 
-`value`      sequences/s with token ids already in HBM (CUDA-graph replay of the 85 launches).
+`value`      sequences/s with token ids already in HBM (CUDA-graph replay of the 61 launches).
 `e2e`        the same through the public driver with HOST buffers: pinned ids / lengths copied to the
              device and the fp16 hidden states copied back inside the timed region, every step.
 `roofline`   the int8 tcgen05 GEMM (4 shapes x 12 layers per step), timed alone with CUDA events.

@@ -62,9 +62,11 @@ def _f16(a):
     return a.astype(np.float16).astype(np.float32)
 
 
-def encoder_int8(cfg, params, scales, ids, kv_lens=None, trace=None):
+def encoder_int8(cfg, params, scales, ids, kv_lens=None, trace=None, fused_layernorm=False):
     """Pinned W8A8 dataflow; returns fp16 hidden states [B*S, H].  ``trace`` (list) receives a dict of
-    every intermediate per layer."""
+    every intermediate per layer.  ``fused_layernorm``: the attention-output and FFN2 projections feed the
+    residual add in fp32 (no fp16 rounding in between), as the fused GEMM + LayerNorm kernel does."""
+    proj = "f32" if fused_layernorm else "f16"
     B, S = ids.shape
     nh, hd, H = cfg.heads, cfg.head_dim, cfg.hidden
     x = _f16(embed(cfg, params, ids, np.float16))
@@ -77,11 +79,11 @@ def encoder_int8(cfg, params, scales, ids, kv_lens=None, trace=None):
         q, k, v = (_split_heads(qkv[:, i * H:(i + 1) * H], B, S, nh, hd) for i in range(3))
         ctx = _f16(_merge_heads(O.attention(q, k, v, kv_lens), B, S, nh, hd))
         ctxq = O.quantize(ctx, a["ctx"])
-        ao = O.linear_int8(ctxq, wq["wo"][0], a["ctx"], wq["wo"][1], lp["bo"], "none", "f16").astype(np.float32)
+        ao = O.linear_int8(ctxq, wq["wo"][0], a["ctx"], wq["wo"][1], lp["bo"], "none", proj).astype(np.float32)
         h1 = _f16(O.add_layernorm(ao, x, ln["ln1_g"], ln["ln1_b"], cfg.eps))
         h1q = O.quantize(h1, a["h1"])
         gq = O.linear_int8(h1q, wq["w1"][0], a["h1"], wq["w1"][1], lp["b1"], "gelu", "s8", a["gelu"])
-        o = O.linear_int8(gq, wq["w2"][0], a["gelu"], wq["w2"][1], lp["b2"], "none", "f16").astype(np.float32)
+        o = O.linear_int8(gq, wq["w2"][0], a["gelu"], wq["w2"][1], lp["b2"], "none", proj).astype(np.float32)
         x_next = _f16(O.add_layernorm(o, h1, ln["ln2_g"], ln["ln2_b"], cfg.eps))
         xq_next = O.quantize(x_next, scales.act[li + 1]["x"]) if li + 1 < n_layers else None
         if trace is not None:

@@ -69,7 +69,7 @@ def test_device_calibration_matches_oracle_calibration(cuda, params):
 def test_int8_encoder_gemms_bit_exact_and_output_tracks_oracle(cuda, params):
     batches = [batch(100 + i) for i in range(4)]
     scales = ER.calibrate_on_oracle(CFG, params, batches, quantize_weights, activation_scales_from_ranges, Int8Scales)
-    enc = Int8Encoder(CFG, params, scales, cuda)
+    enc = Int8Encoder(CFG, params, scales, cuda, fuse_layernorm=False)
     ids, lens = batch(2)
     np_ = lambda t: t.cpu().numpy()
     for li, buf in enc.forward_layerwise(*tdev(ids, lens, cuda)):
@@ -103,8 +103,43 @@ def test_int8_encoder_gemms_bit_exact_and_output_tracks_oracle(cuda, params):
     assert torch.equal(enc.replay(), eager)
     # concurrent micro-batches (sequences are independent): bit-identical, eager and replayed
     for n in (2, 3):
-        enc_m = Int8Encoder(CFG, params, scales, cuda, micro_batches=n)
+        enc_m = Int8Encoder(CFG, params, scales, cuda, micro_batches=n, fuse_layernorm=False)
         assert torch.equal(enc_m.forward(*tdev(ids, lens, cuda)), eager)
         enc_m.capture(*ids.shape)
         enc_m.set_inputs(*tdev(ids, lens, cuda))
         assert torch.equal(enc_m.replay(), eager)
+
+
+def test_int8_encoder_with_fused_layernorm_kernels(cuda):
+    """hidden 768: attention-output and FFN2 run as GEMM + residual + LayerNorm kernels (5 launches / layer)."""
+    cfg = EncoderConfig(layers=2, hidden=768, heads=12, ffn=1024, vocab=2000, max_pos=128)
+    params = init_params(cfg, 11, random_affine=True)
+    mk = lambda s: (rng(s).integers(0, cfg.vocab, (2, 96)), np.array([96, 70], np.int32))
+    scales = ER.calibrate_on_oracle(cfg, params, [mk(s) for s in range(3)], quantize_weights,
+                                    activation_scales_from_ranges, Int8Scales)
+    ids, lens = mk(50)
+    enc = Int8Encoder(cfg, params, scales, cuda)
+    assert enc.fuse_layernorm and enc.launches_per_layer == 5
+    np_ = lambda t: t.cpu().numpy()
+    for li, buf in enc.forward_layerwise(*tdev(ids, lens, cuda)):
+        a, wq, lp = scales.act[li], scales.weights[li], params["layers"][li]
+        f16 = lambda k: lp[k].astype(np.float16).astype(np.float32)
+        # the fused kernel on the device's own inputs: LayerNorm(dequant(ctx_q . Wo) + bo + x)
+        t = O.linear_int8(np_(buf["ctxq"]), wq["wo"][0], a["ctx"], wq["wo"][1], lp["bo"], "none", "f32") + np_(buf["x"].float())
+        want = O.layernorm(t, f16("ln1_g"), f16("ln1_b"), cfg.eps)
+        assert np.max(np.abs(np_(buf["h1"].float()) - want)) < 1e-2
+        assert np.array_equal(np_(buf["h1q"]), O.quantize(np_(buf["h1"].float()), a["h1"]))
+        want = O.linear_int8(np_(buf["h1q"]), wq["w1"][0], a["h1"], wq["w1"][1], lp["b1"], "gelu", "s8", a["gelu"])
+        assert np.array_equal(np_(buf["gq"]), want)
+        t = O.linear_int8(np_(buf["gq"]), wq["w2"][0], a["gelu"], wq["w2"][1], lp["b2"], "none", "f32") + np_(buf["h1"].float())
+        want = O.layernorm(t, f16("ln2_g"), f16("ln2_b"), cfg.eps)
+        assert np.max(np.abs(np_(buf["x_next"].float()) - want)) < 1e-2
+    got = np_(enc.out.float())
+    want8 = ER.encoder_int8(cfg, params, scales, ids, lens, fused_layernorm=True).astype(np.float32)
+    assert np.mean(np.abs(got - want8)) < 5e-3 and np.max(np.abs(got - want8)) < 0.1
+    unfused = Int8Encoder(cfg, params, scales, cuda, fuse_layernorm=False).forward(*tdev(ids, lens, cuda)).float()
+    assert (unfused - enc.out.float()).abs().mean().item() < 5e-3
+    eager = enc.out.clone()
+    enc.capture(*ids.shape)
+    enc.set_inputs(*tdev(ids, lens, cuda))
+    assert torch.equal(enc.replay(), eager)

@@ -106,7 +106,7 @@ template <int BN, int STAGES>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_i8_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                   const __grid_constant__ CUtensorMap tmap_y, const __grid_constant__ CUtensorMap tmap_q,
-                  const GemmLnParams p) {
+                  const __grid_constant__ CUtensorMap tmap_r, const GemmLnParams p) {
   constexpr int BK = 128, UK = 32;
   constexpr int A_BYTES = GEMM_BM * 128;
   constexpr int B_BYTES = BN * 128;
@@ -131,7 +131,8 @@ gemm_i8_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   uint64_t* tempty_bar = tfull_bar + 2;
   uint64_t* stats_bar = tempty_bar + 2;  // [2] cluster-wide: the four partials of every row have arrived
   uint64_t* slab_bar = stats_bar + 2;    // CTA-local: the SLABS partials of every row are in pstats
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(slab_bar + 1);
+  uint64_t* res_bar = slab_bar + 1;      // [SLABS * 4] per warp: its 32 x 64 residual block has landed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(res_bar + SLABS * 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* epi_rows = reinterpret_cast<float*>(ctrl + 256);
 
@@ -148,6 +149,7 @@ gemm_i8_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     tma_prefetch_desc(&tmap_b);
     tma_prefetch_desc(&tmap_y);
     tma_prefetch_desc(&tmap_q);
+    tma_prefetch_desc(&tmap_r);
     for (int i = 0; i < STAGES; ++i) {
       mbar_init(&full_bar[i], 1);
       mbar_init(&empty_bar[i], 1);
@@ -158,6 +160,7 @@ gemm_i8_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       mbar_init(&stats_bar[i], LN_CLUSTER * 128);  // one arrival per row from each CTA of the cluster
     }
     mbar_init(slab_bar, EPI_ACTIVE);
+    for (int i = 0; i < SLABS * 4; ++i) mbar_init(&res_bar[i], 1);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -266,13 +269,17 @@ gemm_i8_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       bool ok = true;
       for (int mt = cluster_id; mt < p.tiles_m; mt += num_clusters, ++it) {
         const int m0 = mt * GEMM_BM;
-        const int row = m0 + r;
-        const bool row_ok = row < p.M;
         const int par = it & 1;
-        const __half* res_row = p.residual + int64_t(row_ok ? row : 0) * p.ldr + n0;
-        if (lane == 0) tma_store_wait_read();  // the previous tile's stores have finished reading the blocks
+        // The 32 x 64 residual block of this warp is fetched by TMA into the fp16 staging block (same
+        // swizzled layout as the output block that later overwrites it in place, row by row).
+        if (lane == 0) {
+          tma_store_wait_read();  // the previous tile's stores have finished reading the blocks
+          mbar_arrive_expect_tx(&res_bar[ew], 4096);
+          tma_load_2d(sty, &tmap_r, &res_bar[ew], n0, m0 + quad * 32);
+        }
         __syncwarp();
         if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(&res_bar[ew], uint32_t(it) & 1u, abort_flag)) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t tacc = tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * BN + sub * 64);
 
@@ -283,11 +290,9 @@ gemm_i8_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           uint32_t a[GEMM_CW];
           __syncwarp();
           tmem_ld_32x16(tacc + uint32_t(i * GEMM_CW), a);
-          uint4 rr[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
-          if (row_ok) {
-            rr[0] = *reinterpret_cast<const uint4*>(res_row + i * GEMM_CW);
-            rr[1] = *reinterpret_cast<const uint4*>(res_row + i * GEMM_CW + 8);
-          }
+          uint4 rr[2];
+          rr[0] = *reinterpret_cast<const uint4*>(sty + lane * 128 + (((2 * i) ^ (lane & 7)) << 4));
+          rr[1] = *reinterpret_cast<const uint4*>(sty + lane * 128 + (((2 * i + 1) ^ (lane & 7)) << 4));
           tmem_wait_ld();
           const __half2* rh = reinterpret_cast<const __half2*>(rr);
           float y[GEMM_CW];
@@ -354,11 +359,9 @@ gemm_i8_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           uint32_t a[GEMM_CW];
           __syncwarp();
           tmem_ld_32x16(tacc + uint32_t(i * GEMM_CW), a);
-          uint4 rr[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
-          if (row_ok) {
-            rr[0] = *reinterpret_cast<const uint4*>(res_row + i * GEMM_CW);
-            rr[1] = *reinterpret_cast<const uint4*>(res_row + i * GEMM_CW + 8);
-          }
+          uint4 rr[2];
+          rr[0] = *reinterpret_cast<const uint4*>(sty + lane * 128 + (((2 * i) ^ (lane & 7)) << 4));
+          rr[1] = *reinterpret_cast<const uint4*>(sty + lane * 128 + (((2 * i + 1) ^ (lane & 7)) << 4));
           tmem_wait_ld();
           const __half2* rh = reinterpret_cast<const __half2*>(rr);
           uint32_t w[GEMM_CW / 2];
@@ -380,15 +383,16 @@ gemm_i8_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           *reinterpret_cast<uint4*>(srow + (((2 * i) ^ (lane & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
           *reinterpret_cast<uint4*>(srow + (((2 * i + 1) ^ (lane & 7)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
           if (p.emit_q) {
-            uint32_t qw[GEMM_CW / 4];
+            // branch-free fast rounding of all 16 values, exact recomputation only for the flagged ones
+            int q[GEMM_CW];
+            uint32_t risky = requant_fast<ZEN_ACT_NONE>(of, inv_q, p.round_mode, q);
+            if (risky) {
 #pragma unroll
-            for (int j4 = 0; j4 < GEMM_CW / 4; ++j4) {
-              uint32_t pk = 0;
-#pragma unroll
-              for (int e = 0; e < 4; ++e)
-                pk |= (uint32_t(quantize_exact(of[4 * j4 + e], p.out_scale, inv_q, p.round_mode)) & 0xffu) << (8 * e);
-              qw[j4] = pk;
+              for (int j = 0; j < GEMM_CW; ++j)
+                if (risky & (1u << j)) q[j] = zen_det_round_clamp_i8(ZEN_DIV(of[j], p.out_scale), p.round_mode);
             }
+            uint32_t qw[GEMM_CW / 4];
+            pack_q(q, qw);
             *reinterpret_cast<uint4*>(stq + lane * 64 + ((i ^ ((lane >> 1) & 3)) << 4)) = make_uint4(qw[0], qw[1], qw[2], qw[3]);
           }
         }
@@ -428,7 +432,7 @@ gemm_i8_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 
 template <int BN, int STAGES>
 static int launch_gemm_ln(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& ty, const CUtensorMap& tq,
-                          const GemmLnParams& p, cudaStream_t stream) {
+                          const CUtensorMap& tr, const GemmLnParams& p, cudaStream_t stream) {
   auto kernel = gemm_i8_ln_kernel<BN, STAGES>;
   constexpr size_t smem = gemm_ln_smem_bytes<BN, STAGES>();
   static bool attr_set = false;
@@ -455,7 +459,7 @@ static int launch_gemm_ln(const CUtensorMap& ta, const CUtensorMap& tb, const CU
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = (pdl_mask() & PDL_GEMM) ? 2 : 1;
-  if (cudaLaunchKernelEx(&cfg, kernel, ta, tb, ty, tq, p) != cudaSuccess) {
+  if (cudaLaunchKernelEx(&cfg, kernel, ta, tb, ty, tq, tr, p) != cudaSuccess) {
     cudaGetLastError();
     return ZEN_ERR_LAUNCH;
   }
@@ -491,7 +495,7 @@ extern "C" int zen_linear_i8_add_layernorm(const int8_t* xq, int64_t ldx, const 
   p.residual = static_cast<const __half*>(residual); p.ldr = ldr;
   p.gamma = static_cast<const __half*>(gamma); p.beta = static_cast<const __half*>(beta);
   p.emit_q = yq ? 1 : 0;
-  CUtensorMap ta, tb, ty, tq;
+  CUtensorMap ta, tb, ty, tq, tr;
   int st = encode_tmap_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, xq, uint64_t(K), uint64_t(M), uint64_t(ldx), 128, GEMM_BM);
   if (st == ZEN_OK) st = encode_tmap_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, wq, uint64_t(K), uint64_t(N), uint64_t(ldw), 128, BN);
   if (st == ZEN_OK)
@@ -501,6 +505,9 @@ extern "C" int zen_linear_i8_add_layernorm(const int8_t* xq, int64_t ldx, const 
   if (st == ZEN_OK && yq)
     st = encode_tmap_2d(&tq, CU_TENSOR_MAP_DATA_TYPE_UINT8, yq, uint64_t(N), uint64_t(M), uint64_t(N), 64, 32,
                         CU_TENSOR_MAP_SWIZZLE_64B);
+  if (st == ZEN_OK)
+    st = encode_tmap_2d(&tr, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, residual, uint64_t(N), uint64_t(M), uint64_t(ldr) * 2, 64, 32,
+                        CU_TENSOR_MAP_SWIZZLE_128B);
   if (st != ZEN_OK) return st;
-  return launch_gemm_ln<BN, STAGES>(ta, tb, ty, tq, p, static_cast<cudaStream_t>(stream));
+  return launch_gemm_ln<BN, STAGES>(ta, tb, ty, tq, tr, p, static_cast<cudaStream_t>(stream));
 }

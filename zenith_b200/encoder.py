@@ -14,6 +14,9 @@ activation scale at each of the four GEMM inputs):
     int8 copy at s_ctx)--> ctx_q --out GEMM (dequant+bias -> fp16)--> +x, LayerNorm (fp16 + int8 copy
     at s_h1) --> h1_q --FFN1 GEMM (dequant+bias+GELU+requant at s_gelu)--> g_q --FFN2 GEMM (dequant+
     bias -> fp16)--> +h1, LayerNorm (fp16 + int8 copy at the next layer's s_x).
+
+With hidden size 768 the two "GEMM, +residual, LayerNorm" pairs each run as ONE kernel
+(``zen_linear_i8_add_layernorm``): 5 launches per layer.
 """
 from __future__ import annotations
 
@@ -292,8 +295,16 @@ class Int8Scales:
 class Int8Encoder(_EncoderBase):
     """W8A8 encoder: int8 GEMM operands, int32 accumulation, fp16 residual stream / LayerNorm / softmax."""
 
-    def __init__(self, cfg: EncoderConfig, params: dict, scales: Int8Scales, device="cuda:0", micro_batches: int = 1):
+    def __init__(self, cfg: EncoderConfig, params: dict, scales: Int8Scales, device="cuda:0", micro_batches: int = 1,
+                 fuse_layernorm: bool | None = None):
+        """``fuse_layernorm``: run attention-output and FFN2 as one GEMM + residual + LayerNorm kernel each
+        (5 launches per layer instead of 7).  Default: on when the hidden size allows it (768).  In the
+        fused form the projection output is not rounded to fp16 before the residual add."""
         super().__init__(cfg, params, device, micro_batches)
+        self.fuse_layernorm = (cfg.hidden == 768) if fuse_layernorm is None else bool(fuse_layernorm)
+        if self.fuse_layernorm and cfg.hidden != 768:
+            raise RuntimeError("the fused GEMM + LayerNorm kernel needs hidden == 768")
+        self.launches_per_layer = 5 if self.fuse_layernorm else 7
         d = self.device
         self.act_scales = scales.act
         self.layers = []
@@ -346,17 +357,30 @@ class Int8Encoder(_EncoderBase):
                       L["bqkv"].data_ptr(), ACT_NONE, DT_F16, 1.0, ROUND_NEAREST_EVEN, P(self.qkv), 3 * H)
             self._add("zen_flash_attention_f16", P(self.qkv), P(self.qkv) + 2 * H, P(self.qkv) + 4 * H, P(self.ctx),
                       P(self.ctxq), a["ctx"], B, nh, S, hd, *qs, *qs, *qs, *os_, kv, 0, 1.0 / math.sqrt(hd))
-            self._add("zen_linear_i8", P(self.ctxq), H, L["wo"].data_ptr(), H, T, H, H, a["ctx"], L["wo_s"].data_ptr(),
-                      L["bo"].data_ptr(), ACT_NONE, DT_F16, 1.0, ROUND_NEAREST_EVEN, P(self.ao), H)
-            self._add("zen_add_layernorm_f16", P(self.ao), P(x), L["ln1_g"].data_ptr(), L["ln1_b"].data_ptr(),
-                      P(self.h1), P(self.h1q), a["h1"], ROUND_NEAREST_EVEN, T, H, cfg.eps)
+            if self.fuse_layernorm:
+                self._add("zen_linear_i8_add_layernorm", P(self.ctxq), H, L["wo"].data_ptr(), H, T, H, H, a["ctx"],
+                          L["wo_s"].data_ptr(), L["bo"].data_ptr(), P(x), H, L["ln1_g"].data_ptr(), L["ln1_b"].data_ptr(),
+                          cfg.eps, P(self.h1), P(self.h1q), a["h1"], ROUND_NEAREST_EVEN)
+            else:
+                self._add("zen_linear_i8", P(self.ctxq), H, L["wo"].data_ptr(), H, T, H, H, a["ctx"],
+                          L["wo_s"].data_ptr(), L["bo"].data_ptr(), ACT_NONE, DT_F16, 1.0, ROUND_NEAREST_EVEN,
+                          P(self.ao), H)
+                self._add("zen_add_layernorm_f16", P(self.ao), P(x), L["ln1_g"].data_ptr(), L["ln1_b"].data_ptr(),
+                          P(self.h1), P(self.h1q), a["h1"], ROUND_NEAREST_EVEN, T, H, cfg.eps)
             self._add("zen_linear_i8", P(self.h1q), H, L["w1"].data_ptr(), H, T, F, H, a["h1"], L["w1_s"].data_ptr(),
                       L["b1"].data_ptr(), ACT_GELU, DT_S8, a["gelu"], ROUND_NEAREST_EVEN, P(self.gq), F)
-            self._add("zen_linear_i8", P(self.gq), F, L["w2"].data_ptr(), F, T, H, F, a["gelu"], L["w2_s"].data_ptr(),
-                      L["b2"].data_ptr(), ACT_NONE, DT_F16, 1.0, ROUND_NEAREST_EVEN, P(self.o), H)
-            self._add("zen_add_layernorm_f16", P(self.o), P(self.h1), L["ln2_g"].data_ptr(), L["ln2_b"].data_ptr(),
-                      P(xn), None if last else P(xqn), 1.0 if last else sc[li + 1]["x"], ROUND_NEAREST_EVEN, T, H,
-                      cfg.eps)
+            if self.fuse_layernorm:
+                self._add("zen_linear_i8_add_layernorm", P(self.gq), F, L["w2"].data_ptr(), F, T, H, F, a["gelu"],
+                          L["w2_s"].data_ptr(), L["b2"].data_ptr(), P(self.h1), H, L["ln2_g"].data_ptr(),
+                          L["ln2_b"].data_ptr(), cfg.eps, P(xn), None if last else P(xqn),
+                          1.0 if last else sc[li + 1]["x"], ROUND_NEAREST_EVEN)
+            else:
+                self._add("zen_linear_i8", P(self.gq), F, L["w2"].data_ptr(), F, T, H, F, a["gelu"],
+                          L["w2_s"].data_ptr(), L["b2"].data_ptr(), ACT_NONE, DT_F16, 1.0, ROUND_NEAREST_EVEN,
+                          P(self.o), H)
+                self._add("zen_add_layernorm_f16", P(self.o), P(self.h1), L["ln2_g"].data_ptr(), L["ln2_b"].data_ptr(),
+                          P(xn), None if last else P(xqn), 1.0 if last else sc[li + 1]["x"], ROUND_NEAREST_EVEN, T, H,
+                          cfg.eps)
             cur ^= 1
 
     def forward_layerwise(self, ids, kv_lens=None):
@@ -371,7 +395,8 @@ class Int8Encoder(_EncoderBase):
         _capi.check(name, f(*args, stream))
         cur = 0
         for li in range(len(self.layers)):
-            for f, name, args in self._launches[1 + li * 7: 1 + (li + 1) * 7]:
+            n = self.launches_per_layer
+            for f, name, args in self._launches[1 + li * n: 1 + (li + 1) * n]:
                 _capi.check(name, f(*args, stream))
             torch.cuda.synchronize()
             yield li, {"x": self.x[cur], "xq": self.xq[cur], "qkv": self.qkv, "ctx": self.ctx, "ctxq": self.ctxq,
