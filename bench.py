@@ -164,20 +164,32 @@ def run_reference_arm(args) -> None:
 # GPU arm
 # ------------------------------------------------------------------------------------------------
 def time_gemm_shapes(torch, ops, dev, flush) -> dict:
-    """Each of the four int8 GEMM shapes of one layer, timed alone with CUDA events (L2 flushed before
-    every launch), with the epilogue it has in the encoder."""
+    """The four int8 GEMM launches of one encoder layer, each timed alone with CUDA events (L2 flushed before
+    every launch), with the epilogue it has in the encoder: QKV (-> fp16), attention-out (+ residual +
+    LayerNorm, cluster kernel), FFN1 (+ GELU + requant), FFN2 (+ residual + LayerNorm)."""
     T, H, F = BATCH * SEQ, 768, 3072
-    shapes = [("qkv", T, 3 * H, H, dict(out_dtype=torch.float16)), ("attn_out", T, H, H, dict(out_dtype=torch.float16)),
-              ("ffn1_gelu_requant", T, F, H, dict(act="gelu", out_dtype=torch.int8, out_scale=0.05)),
-              ("ffn2", T, H, F, dict(out_dtype=torch.float16))]
-    per_shape, tot_ops, tot_us = {}, 0.0, 0.0
-    for name, M, N, K, kw in shapes:
-        x = torch.randint(-128, 128, (M, K), dtype=torch.int8, device=dev)
+
+    def plain(N, K, **kw):
+        x = torch.randint(-128, 128, (T, K), dtype=torch.int8, device=dev)
         w = torch.randint(-128, 128, (N, K), dtype=torch.int8, device=dev)
-        ws = torch.rand(N, device=dev) * 1e-3
-        b = torch.randn(N, device=dev)
-        out = torch.empty((M, N), dtype=kw["out_dtype"], device=dev)
-        fn = lambda: ops.linear_int8(x, w, 0.02, ws, b, out=out, **kw)
+        ws, b = torch.rand(N, device=dev) * 1e-3, torch.randn(N, device=dev)
+        out = torch.empty((T, N), dtype=kw["out_dtype"], device=dev)
+        return lambda: ops.linear_int8(x, w, 0.02, ws, b, out=out, **kw)
+
+    def with_ln(K):
+        x = torch.randint(-128, 128, (T, K), dtype=torch.int8, device=dev)
+        w = torch.randint(-128, 128, (H, K), dtype=torch.int8, device=dev)
+        ws, b = torch.rand(H, device=dev) * 1e-3, torch.randn(H, device=dev)
+        res = torch.randn(T, H, device=dev, dtype=torch.float16)
+        g, be = torch.ones(H, device=dev, dtype=torch.float16), torch.zeros(H, device=dev, dtype=torch.float16)
+        return lambda: ops.linear_int8_add_layernorm(x, w, 0.02, ws, b, res, g, be, 1e-12, out_scale=0.03)
+
+    shapes = [("qkv", 3 * H, H, plain(3 * H, H, out_dtype=torch.float16)),
+              ("attn_out_add_layernorm", H, H, with_ln(H)),
+              ("ffn1_gelu_requant", F, H, plain(F, H, act="gelu", out_dtype=torch.int8, out_scale=0.05)),
+              ("ffn2_add_layernorm", H, F, with_ln(F))]
+    per_shape, tot_ops, tot_us = {}, 0.0, 0.0
+    for name, N, K, fn in shapes:
         for _ in range(3):
             fn()
         us = []
@@ -190,8 +202,8 @@ def time_gemm_shapes(torch, ops, dev, flush) -> dict:
             e.synchronize()
             us.append(s.elapsed_time(e) * 1e3)
         t = statistics.median(us)
-        per_shape[name] = {"us": round(t, 2), "tops": round(2.0 * M * N * K / t / 1e6, 1)}
-        tot_ops += 2.0 * M * N * K
+        per_shape[name] = {"us": round(t, 2), "tops": round(2.0 * T * N * K / t / 1e6, 1)}
+        tot_ops += 2.0 * T * N * K
         tot_us += t
     return {"per_shape": per_shape, "ops_per_layer": tot_ops, "us_per_layer": tot_us}
 
@@ -306,17 +318,16 @@ def run_ours(args) -> None:
         int8_peak = 2.0 * peaks["bf16_tflops"]
         achieved = g["ops_per_layer"] / g["us_per_layer"] / 1e6
         line["roofline"] = {
-            "kernel": "gemm_tc_kernel<int8> (QKV, attention-out, FFN1+GELU+requant, FFN2 of one layer)",
+            "kernel": "int8 tcgen05 GEMM family of one layer: gemm_tc_kernel (QKV, FFN1+GELU+requant) and "
+                      "gemm_i8_ln_kernel (attention-out / FFN2 + residual + LayerNorm)",
             "bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TOP/s", "frac": achieved / int8_peak,
             "peak_source": f"2 x {peaks['source']} bf16 GEMM burst ({peaks['bf16_tflops']} TFLOP/s): int8 issues at "
                            "twice the bf16 rate; nominal dense int8 is 4500 TOP/s",
             "frac_of_nominal": achieved / 4500.0,
             # DRAM bytes of the same four launches from profiles/gemm_i8_bert_base_layer_shapes.md (ncu): reads
-            # only and equal to the operand bytes; the outputs are still in L2 when each kernel ends
-            "traffic": 29.46e6, "traffic_unit": "bytes per layer (4 launches)",
-            "algorithmic_bytes": 73.1e6, "per_shape": g["per_shape"]}
-        gemm_ms_per_step = 12 * g["us_per_layer"] / 1e3
-        line["roofline"]["gemm_share_of_step"] = gemm_ms_per_step / (total_ms / K)
+            # only and equal to the operand (+ residual) bytes; the outputs are still in L2 when each kernel ends
+            "traffic": 42.0e6, "traffic_unit": "bytes per layer (4 launches)",
+            "algorithmic_bytes": 92.1e6, "per_shape": g["per_shape"]}
         try:
             r = cpu_executor(8, 3, 1)
             line["cpu_baseline"] = {"value": r["seq_per_s"], "unit": "sequences/s", "cores": r["cores"], "kind": "port",

@@ -37,7 +37,7 @@ def _time(fn, iters, flush):
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["gemm_i8", "gemm_f16", "add_ln", "attention", "encoder"])
+    ap.add_argument("case", choices=["gemm_i8", "gemm_i8_ln", "gemm_f16", "add_ln", "attention", "encoder"])
     ap.add_argument("--config", choices=["base", "large"], default="base")
     ap.add_argument("--dtype", choices=["int8", "fp16"], default="int8")
     ap.add_argument("--batch", type=int, default=32)
@@ -73,6 +73,18 @@ def main() -> None:
         med, best = _time(lambda: ops.linear_int8(x, w, 0.02, ws, b, out=y, **kw), a.iters, flush)
         out.update(m=a.m, n=a.n, k=a.k, epilogue=a.epilogue, tile_n=a.tile_n, us=med, us_min=best,
                    tops=2.0 * a.m * a.n * a.k / med / 1e6)
+    elif a.case == "gemm_i8_ln":
+        n = 768
+        x = torch.randint(-128, 128, (a.m, a.k), dtype=torch.int8, device=dev)
+        w = torch.randint(-128, 128, (n, a.k), dtype=torch.int8, device=dev)
+        ws = torch.rand(n, device=dev) * 1e-3
+        b = torch.randn(n, device=dev)
+        res = torch.randn(a.m, n, device=dev, dtype=torch.float16)
+        g = torch.ones(n, device=dev, dtype=torch.float16)
+        be = torch.zeros_like(g)
+        med, best = _time(lambda: ops.linear_int8_add_layernorm(x, w, 0.02, ws, b, res, g, be, 1e-12, out_scale=0.03),
+                          a.iters, flush)
+        out.update(m=a.m, n=n, k=a.k, us=med, us_min=best, tops=2.0 * a.m * n * a.k / med / 1e6)
     elif a.case == "gemm_f16":
         x = torch.randn(a.m, a.k, device=dev, dtype=torch.float16)
         w = torch.randn(a.n, a.k, device=dev, dtype=torch.float16)
