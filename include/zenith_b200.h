@@ -79,8 +79,8 @@ int zen_linear_i8(const int8_t* xq, int64_t ldx, const int8_t* wq, int64_t ldw, 
  *   t = (float(acc) * x_scale) * w_scale[n] + bias[n] + residual[m,n];   y = LayerNorm_n(t) * gamma + beta
  * y is written as fp16 [M,N] (contiguous) and, if yq != NULL, also as int8 clamp(round(y / out_scale)) of
  * the fp16 value.  residual fp16 [M,N] (row stride ldr), gamma / beta fp16 [N].  Statistics in fp32 over
- * the un-rounded t (pairwise-combined mean / M2).  N must be 768 (four 192-column CTAs of a cluster share
- * a row through distributed shared memory); other widths: zen_linear_i8 followed by zen_add_layernorm_f16.
+ * the un-rounded t (pairwise-combined mean / M2).  N must be 768 or 1024 (four CTAs of a cluster, 192 or 256
+ * columns each, share a row through distributed shared memory); other widths: zen_linear_i8 followed by zen_add_layernorm_f16.
  * Replaces the sequence linear -> fused_add_layernorm of the reference's encoder drivers
  * (benchmarks/bert_hybrid.py:121-145; core/src/fused_kernels.cu:145-221). */
 int zen_linear_i8_add_layernorm(const int8_t* xq, int64_t ldx, const int8_t* wq, int64_t ldw, int M, int N, int K,

@@ -17,9 +17,9 @@ def dev(a, cuda):
     return torch.from_numpy(np.ascontiguousarray(a)).to(cuda)
 
 
-@pytest.mark.parametrize("M,K", [(128, 768), (300, 768), (4096, 768), (1000, 3072), (4096, 3072), (1, 128)])
-def test_linear_add_layernorm(cuda, M, K):
-    N = 768
+@pytest.mark.parametrize("M,K,N", [(128, 768, 768), (300, 768, 768), (4096, 768, 768), (1000, 3072, 768),
+                                   (4096, 3072, 768), (1, 128, 768), (700, 1024, 1024), (512, 4096, 1024)])
+def test_linear_add_layernorm(cuda, M, K, N):
     x = rng(M).integers(-128, 128, (M, K), dtype=np.int8)
     w = rng(K).integers(-128, 128, (N, K), dtype=np.int8)
     ws = ((rng(1).random(N) + 0.5) * 2e-4).astype(np.float32)

@@ -480,12 +480,12 @@ extern "C" int zen_linear_i8_add_layernorm(const int8_t* xq, int64_t ldx, const 
   if (!xq || !wq || !residual || !gamma || !beta || !y || M <= 0 || N <= 0 || K <= 0) return ZEN_ERR_INVALID_ARG;
   if (round_mode != ZEN_ROUND_NEAREST_EVEN && round_mode != ZEN_ROUND_TRUNC) return ZEN_ERR_INVALID_ARG;
   if (yq && !(out_scale > 0.0f)) return ZEN_ERR_INVALID_ARG;
-  if (N != 768) return ZEN_ERR_UNSUPPORTED;  // four CTAs x 192 columns hold one row
+  if (N != 768 && N != 1024) return ZEN_ERR_UNSUPPORTED;  // four CTAs x 192 (or 256) columns hold one row
   if (K % 16 || ldx % 16 || ldw % 16 || ldx < K || ldw < K || ldr % 8 || ldr < N) return ZEN_ERR_UNSUPPORTED;
   if (reinterpret_cast<uintptr_t>(y) % 16 || reinterpret_cast<uintptr_t>(yq) % 16 ||
       reinterpret_cast<uintptr_t>(residual) % 16)
     return ZEN_ERR_UNSUPPORTED;
-  constexpr int BN = 192, STAGES = 3;
+  const int BN = N / LN_CLUSTER;
   GemmLnParams p{};
   p.M = M; p.N = N; p.K = K;
   p.tiles_m = (M + GEMM_BM - 1) / GEMM_BM;
@@ -509,5 +509,6 @@ extern "C" int zen_linear_i8_add_layernorm(const int8_t* xq, int64_t ldx, const 
     st = encode_tmap_2d(&tr, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, residual, uint64_t(N), uint64_t(M), uint64_t(ldr) * 2, 64, 32,
                         CU_TENSOR_MAP_SWIZZLE_128B);
   if (st != ZEN_OK) return st;
-  return launch_gemm_ln<BN, STAGES>(ta, tb, ty, tq, tr, p, static_cast<cudaStream_t>(stream));
+  if (BN == 192) return launch_gemm_ln<192, 3>(ta, tb, ty, tq, tr, p, static_cast<cudaStream_t>(stream));
+  return launch_gemm_ln<256, 2>(ta, tb, ty, tq, tr, p, static_cast<cudaStream_t>(stream));
 }

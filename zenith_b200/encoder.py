@@ -298,12 +298,13 @@ class Int8Encoder(_EncoderBase):
     def __init__(self, cfg: EncoderConfig, params: dict, scales: Int8Scales, device="cuda:0", micro_batches: int = 1,
                  fuse_layernorm: bool | None = None):
         """``fuse_layernorm``: run attention-output and FFN2 as one GEMM + residual + LayerNorm kernel each
-        (5 launches per layer instead of 7).  Default: on when the hidden size allows it (768).  In the
+        (5 launches per layer instead of 7).  Possible for hidden 768 and 1024; on by default for 768 only (at
+        BERT-large's 12k-token shards the separate kernels measured faster: 8.98 vs 10.26 ms per pass).  In the
         fused form the projection output is not rounded to fp16 before the residual add."""
         super().__init__(cfg, params, device, micro_batches)
         self.fuse_layernorm = (cfg.hidden == 768) if fuse_layernorm is None else bool(fuse_layernorm)
-        if self.fuse_layernorm and cfg.hidden != 768:
-            raise RuntimeError("the fused GEMM + LayerNorm kernel needs hidden == 768")
+        if self.fuse_layernorm and cfg.hidden not in (768, 1024):
+            raise RuntimeError("the fused GEMM + LayerNorm kernel needs hidden == 768 or 1024")
         self.launches_per_layer = 5 if self.fuse_layernorm else 7
         d = self.device
         self.act_scales = scales.act

@@ -74,7 +74,7 @@ def main() -> None:
         out.update(m=a.m, n=a.n, k=a.k, epilogue=a.epilogue, tile_n=a.tile_n, us=med, us_min=best,
                    tops=2.0 * a.m * a.n * a.k / med / 1e6)
     elif a.case == "gemm_i8_ln":
-        n = 768
+        n = a.n if a.n in (768, 1024) else 768
         x = torch.randint(-128, 128, (a.m, a.k), dtype=torch.int8, device=dev)
         w = torch.randint(-128, 128, (n, a.k), dtype=torch.int8, device=dev)
         ws = torch.rand(n, device=dev) * 1e-3
