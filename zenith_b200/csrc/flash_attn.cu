@@ -61,6 +61,10 @@ __device__ __forceinline__ void fa_tma_tile(uint8_t* dst, const CUtensorMap* map
   tma_load_4d(dst, map, bar, c[0], c[1], c[2], c[3]);
 }
 
+}  // namespace zen
+#include "flash_attn_pipe.cuh"
+namespace zen {
+
 // KV_STAGES = 2 double-buffers K and V for long sequences; KV_STAGES = 1 serves sequences of at most
 // one key block (S <= 128, the encoder's case): P reuses the Q / K tiles and O_blk reuses the TMEM
 // columns of S, so that four CTAs fit on an SM (one wave for 32 x 12 heads on 148 SMs) and one CTA's
@@ -399,6 +403,23 @@ static int launch_fa(const CUtensorMap& tq, const CUtensorMap& tk, const CUtenso
   return launch_pdl(PDL_ATTENTION, kernel, grid, dim3(FA_THREADS), smem, s, tq, tk, tv, p);
 }
 
+template <int D, int KV_STAGES>
+static int launch_fa_pipe(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FaParams& p,
+                          cudaStream_t s) {
+  auto kernel = flash_attn_pipe_kernel<D, KV_STAGES>;
+  constexpr size_t smem = fap_smem_bytes<D, KV_STAGES>();
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) {
+      cudaGetLastError();
+      return ZEN_ERR_LAUNCH;
+    }
+    attr_set = true;
+  }
+  dim3 grid((p.S + 255) / 256, p.H, p.B);
+  return launch_pdl(PDL_ATTENTION, kernel, grid, dim3(FAP_THREADS), smem, s, tq, tk, tv, p);
+}
+
 }  // namespace zen
 
 using namespace zen;
@@ -427,5 +448,10 @@ extern "C" int zen_flash_attention_f16(const void* q, const void* k, const void*
   if (st != ZEN_OK) return st;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (S <= FA_BKV) return D == 64 ? launch_fa<64, 1>(tq, tk, tv, p, s) : launch_fa<128, 1>(tq, tk, tv, p, s);
-  return D == 64 ? launch_fa<64, 2>(tq, tk, tv, p, s) : launch_fa<128, 2>(tq, tk, tv, p, s);
+  static const bool simple = []() {
+    const char* e = getenv("ZEN_ATTENTION_SIMPLE");  // 1: the one-tile-per-CTA kernel also for long sequences
+    return e && e[0] == '1';
+  }();
+  if (simple) return D == 64 ? launch_fa<64, 2>(tq, tk, tv, p, s) : launch_fa<128, 2>(tq, tk, tv, p, s);
+  return D == 64 ? launch_fa_pipe<64, 2>(tq, tk, tv, p, s) : launch_fa_pipe<128, 1>(tq, tk, tv, p, s);
 }

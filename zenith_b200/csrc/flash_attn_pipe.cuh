@@ -1,0 +1,342 @@
+// Flash-attention forward for sequences longer than one key block: two 128-query tiles per CTA.
+//
+//   warp 0      : TMA producer — both Q tiles once, then K and V tiles of 128 keys (ring of KV_STAGES)
+//   warp 1      : TMEM owner and tcgen05.mma issuer for both tiles
+//   warps 2..5  : softmax group A (query rows 0..127 of the CTA), one thread per row
+//   warps 6..9  : softmax group B (query rows 128..255)
+//
+// K and V are loaded once for 256 queries, and while one group runs its softmax the tensor core
+// works for the other (S = Q K^T of the next block, O += P V of the current one).  O accumulates in
+// TMEM across key blocks (tcgen05.mma with the accumulate flag); the running maximum used for
+// scaling is only moved, and O rescaled in TMEM by tcgen05.ld / st, when the row maximum has grown
+// by more than 2^8 since the last move, so that the rescale is rare after the first blocks and P
+// stays below 256 in fp16.  TMEM: S_A, S_B (128 columns each), O_A, O_B (D columns each).
+#pragma once
+#include "zen_common.cuh"
+
+namespace zen {
+
+constexpr int FAP_THREADS = 320;
+
+template <int D, int KV_STAGES>
+constexpr size_t fap_smem_bytes() {
+  // 2 Q tiles + KV_STAGES x (K + V) tiles (128 x D fp16 each) + 2 P tiles (128 x 128 fp16) + control + slack
+  return size_t(2 + 2 * KV_STAGES) * 128 * D * 2 + 2 * 128 * 128 * 2 + 256 + 1024;
+}
+
+template <int D, int KV_STAGES>
+__global__ void __launch_bounds__(FAP_THREADS, 1)
+flash_attn_pipe_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                       const __grid_constant__ CUtensorMap tmap_v, const FaParams p) {
+  constexpr int DC = D / 64;
+  constexpr int TILE_BYTES = 128 * D * 2;
+  constexpr int CHUNK_BYTES = 128 * 128;
+  constexpr int P_BYTES = 128 * 128 * 2;
+  constexpr uint32_t TMEM_COLS = 512;
+  constexpr uint32_t IDESC_QK = make_idesc(IDESC_C_F32, IDESC_F16, IDESC_F16, 0, 0, 128, 128);
+  constexpr uint32_t IDESC_PV = make_idesc(IDESC_C_F32, IDESC_F16, IDESC_F16, 0, 1, 128, D);
+  constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint8_t* sQ = smem;                              // [2][TILE]
+  uint8_t* sK = sQ + 2 * TILE_BYTES;               // [KV_STAGES][TILE]
+  uint8_t* sV = sK + KV_STAGES * TILE_BYTES;       // [KV_STAGES][TILE]
+  uint8_t* sP = sV + KV_STAGES * TILE_BYTES;       // [2][P]
+  uint8_t* ctrl = sP + 2 * P_BYTES;
+  uint64_t* q_full = reinterpret_cast<uint64_t*>(ctrl);
+  uint64_t* k_full = q_full + 1;                   // [KV_STAGES]
+  uint64_t* k_empty = k_full + KV_STAGES;
+  uint64_t* v_full = k_empty + KV_STAGES;
+  uint64_t* v_empty = v_full + KV_STAGES;
+  uint64_t* s_full = v_empty + KV_STAGES;          // [2] per group
+  uint64_t* p_full = s_full + 2;                   // [2]
+  uint64_t* o_full = p_full + 2;                   // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int q0 = blockIdx.x * 256;
+  const int h = blockIdx.y;
+  const int b = blockIdx.z;
+
+  int kv_len = p.kv_lens ? p.kv_lens[b] : p.S;
+  kv_len = kv_len < 0 ? 0 : (kv_len > p.S ? p.S : kv_len);
+  // key blocks needed by each group (group B has no rows if the sequence ends before its tile)
+  int nblk[2];
+#pragma unroll
+  for (int g = 0; g < 2; ++g) {
+    int end = kv_len;
+    if (p.causal && q0 + g * 128 + 128 < end) end = q0 + g * 128 + 128;
+    nblk[g] = (q0 + g * 128 < p.S) ? (end + 127) / 128 : 0;
+  }
+  const int n_blocks = nblk[0] > nblk[1] ? nblk[0] : nblk[1];
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmap_q);
+    tma_prefetch_desc(&tmap_k);
+    tma_prefetch_desc(&tmap_v);
+    mbar_init(q_full, 1);
+    for (int i = 0; i < KV_STAGES; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&v_empty[i], 1);
+    }
+    for (int g = 0; g < 2; ++g) {
+      mbar_init(&s_full[g], 1);
+      mbar_init(&p_full[g], 128);
+      mbar_init(&o_full[g], 1);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  grid_launch_dependents();
+  grid_dependency_wait();
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0 && n_blocks > 0) {
+      bool ok = true;
+      mbar_arrive_expect_tx(q_full, 2 * TILE_BYTES);
+#pragma unroll
+      for (int g = 0; g < 2; ++g)
+#pragma unroll
+        for (int dc = 0; dc < DC; ++dc)
+          fa_tma_tile(sQ + g * TILE_BYTES + dc * CHUNK_BYTES, &tmap_q, q_full, p.q_perm, dc * 64, q0 + g * 128, h, b);
+      for (int j = 0; j < n_blocks && ok; ++j) {
+        const int st = j % KV_STAGES;
+        const uint32_t ph = (j / KV_STAGES) & 1;
+        if (!mbar_wait(&k_empty[st], ph ^ 1u, abort_flag)) { ok = false; break; }
+        mbar_arrive_expect_tx(&k_full[st], TILE_BYTES);
+#pragma unroll
+        for (int dc = 0; dc < DC; ++dc)
+          fa_tma_tile(sK + st * TILE_BYTES + dc * CHUNK_BYTES, &tmap_k, &k_full[st], p.k_perm, dc * 64, j * 128, h, b);
+        if (!mbar_wait(&v_empty[st], ph ^ 1u, abort_flag)) { ok = false; break; }
+        mbar_arrive_expect_tx(&v_full[st], TILE_BYTES);
+#pragma unroll
+        for (int dc = 0; dc < DC; ++dc)
+          fa_tma_tile(sV + st * TILE_BYTES + dc * CHUNK_BYTES, &tmap_v, &v_full[st], p.v_perm, dc * 64, j * 128, h, b);
+      }
+      if (!ok) {
+        for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0 && n_blocks > 0) {
+      auto issue_qk = [&](int g, int j) {
+        const uint32_t qa = smem_u32(sQ + g * TILE_BYTES);
+        const uint32_t ka = smem_u32(sK + (j % KV_STAGES) * TILE_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t off = (ks / 4) * CHUNK_BYTES + (ks % 4) * 32;
+          mma_f16_ss(tmem_base + uint32_t(g * 128), make_smem_desc_sw128(qa + off, 1024, 16),
+                     make_smem_desc_sw128(ka + off, 1024, 16), IDESC_QK, ks != 0 ? 1u : 0u);
+        }
+        tc_commit(&s_full[g]);
+      };
+      auto issue_pv = [&](int g, int j) {
+        const uint32_t pa = smem_u32(sP + g * P_BYTES);
+        const uint32_t va = smem_u32(sV + (j % KV_STAGES) * TILE_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          mma_f16_ss(tmem_base + uint32_t(256 + g * D),
+                     make_smem_desc_sw128(pa + (ks / 4) * CHUNK_BYTES + (ks % 4) * 32, 1024, 16),
+                     make_smem_desc_sw128(va + ks * (16 * 128), 1024, CHUNK_BYTES), IDESC_PV, (j | ks) != 0 ? 1u : 0u);
+        tc_commit(&o_full[g]);
+      };
+      bool ok = mbar_wait(q_full, 0, abort_flag);
+      if (ok) ok = mbar_wait(&k_full[0], 0, abort_flag);
+      if (ok) {
+        tc_fence_after_sync();
+        if (nblk[0] > 0) issue_qk(0, 0);
+        if (nblk[1] > 0) issue_qk(1, 0);
+        tc_commit(&k_empty[0]);
+      }
+      for (int j = 0; j < n_blocks && ok; ++j) {
+        const int st = j % KV_STAGES;
+        const bool next = j + 1 < n_blocks;
+        bool k_next_ready = false;
+#pragma unroll
+        for (int g = 0; g < 2; ++g) {
+          if (j < nblk[g]) {
+            // P_g(j) is in shared memory; S_g(j) has been read; O_g has been rescaled if it had to be
+            if (!mbar_wait(&p_full[g], j & 1, abort_flag)) { ok = false; break; }
+            if (g == 0 || nblk[0] <= j) {
+              if (!mbar_wait(&v_full[st], (j / KV_STAGES) & 1, abort_flag)) { ok = false; break; }
+            }
+            tc_fence_after_sync();
+            issue_pv(g, j);
+          }
+          if (next && j + 1 < nblk[g]) {
+            if (!k_next_ready) {
+              if (!mbar_wait(&k_full[(j + 1) % KV_STAGES], ((j + 1) / KV_STAGES) & 1, abort_flag)) { ok = false; break; }
+              tc_fence_after_sync();
+              k_next_ready = true;
+            }
+            issue_qk(g, j + 1);
+          }
+        }
+        if (!ok) break;
+        tc_commit(&v_empty[st]);                                  // V(j) consumed by both groups' P V
+        if (next) tc_commit(&k_empty[(j + 1) % KV_STAGES]);       // K(j+1) consumed by both groups' Q K^T
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- softmax groups
+    const int g = (warp - 2) >> 2;
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;
+    const int q = q0 + g * 128 + r;
+    const uint32_t lane_sel = uint32_t(quad * 32) << 16;
+    const uint32_t tmem_s = tmem_base + uint32_t(g * 128);
+    const uint32_t tmem_o = tmem_base + uint32_t(256 + g * D);
+    uint8_t* myP = sP + g * P_BYTES;
+    const int nb = nblk[g];
+    float m_ref = -INFINITY;  // the maximum the stored probabilities and O are scaled with (log2 units)
+    float l_run = 0.f;
+    bool ok = true;
+
+    for (int j = 0; j < nb && ok; ++j) {
+      if (!mbar_wait(&s_full[g], j & 1, abort_flag)) { ok = false; break; }
+      tc_fence_after_sync();
+      const int key0 = j * 128;
+      int lim = kv_len - key0;
+      if (p.causal && q + 1 - key0 < lim) lim = q + 1 - key0;
+      // pass 1: row maximum of this block
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t sv[32];
+        __syncwarp();
+        tmem_ld_32x32(tmem_s + lane_sel + c * 32, sv);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (c * 32 + i < lim) mx = fmaxf(mx, __uint_as_float(sv[i]));
+      }
+      const float m_blk = mx * p.scale_log2;
+      // move the reference maximum only when this row has outgrown it by more than the threshold
+      const bool grow = m_blk > m_ref + RESCALE_THRESHOLD || (m_ref == -INFINITY && m_blk != -INFINITY);
+      const float m_new = grow ? m_blk : m_ref;
+      const float alpha = (grow && m_ref != -INFINITY) ? fast_exp2(m_ref - m_new) : 1.0f;
+      const float m_use = m_new == -INFINITY ? 0.f : m_new;
+      if (j > 0) {
+        // P V of the previous block has completed: P may be overwritten, O may be rescaled
+        if (!mbar_wait(&o_full[g], (j - 1) & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after_sync();
+        if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+#pragma unroll 1
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t ov[32];
+            __syncwarp();
+            tmem_ld_32x32(tmem_o + lane_sel + c * 32, ov);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+            tmem_st_32x32(tmem_o + lane_sel + c * 32, ov);
+          }
+          tmem_wait_st();
+          l_run *= alpha;
+        }
+      }
+      m_ref = m_new;
+      // pass 2: probabilities -> shared memory (fp16, swizzled K-major), row sum
+      float rowsum = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t sv[32];
+        __syncwarp();
+        tmem_ld_32x32(tmem_s + lane_sel + c * 32, sv);
+        tmem_wait_ld();
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float a = (c * 32 + 2 * i < lim) ? fast_exp2(__uint_as_float(sv[2 * i]) * p.scale_log2 - m_use) : 0.f;
+          const float bq = (c * 32 + 2 * i + 1 < lim) ? fast_exp2(__uint_as_float(sv[2 * i + 1]) * p.scale_log2 - m_use) : 0.f;
+          rowsum += a + bq;
+          const __half2 hh = __floats2half2_rn(a, bq);
+          pk[i] = *reinterpret_cast<const uint32_t*>(&hh);
+        }
+        uint8_t* prow = myP + (c >> 1) * CHUNK_BYTES + r * 128;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int unit = ((c & 1) * 4 + u) ^ (r & 7);
+          *reinterpret_cast<uint4*>(prow + unit * 16) = make_uint4(pk[4 * u], pk[4 * u + 1], pk[4 * u + 2], pk[4 * u + 3]);
+        }
+      }
+      l_run += rowsum;
+      tc_fence_before_sync();
+      fence_proxy_async_smem();
+      mbar_arrive(&p_full[g]);
+    }
+
+    if (ok && nb > 0) {
+      if (!mbar_wait(&o_full[g], (nb - 1) & 1, abort_flag)) ok = false;
+      tc_fence_after_sync();
+    }
+    if (ok) {
+      // every lane takes part in the TMEM loads; only rows inside the sequence are stored
+      const bool row_ok = q < p.S;
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      const int64_t off = int64_t(b) * p.o_sb + int64_t(h) * p.o_sh + int64_t(q) * p.o_ss;
+      __half* orow = static_cast<__half*>(p.o) + off;
+      const float inv_o_scale = p.oq ? ZEN_DIV(1.0f, p.o_scale) : 1.0f;
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t ov[32];
+        __syncwarp();
+        if (nb > 0) {
+          tmem_ld_32x32(tmem_o + lane_sel + c * 32, ov);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) ov[i] = 0;
+        }
+        uint32_t w[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const __half2 hh = __floats2half2_rn(__uint_as_float(ov[2 * i]) * inv, __uint_as_float(ov[2 * i + 1]) * inv);
+          w[i] = *reinterpret_cast<const uint32_t*>(&hh);
+        }
+        if (!row_ok) continue;
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          reinterpret_cast<uint4*>(orow + c * 32)[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+        if (p.oq) {
+          uint32_t qw[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            uint32_t pkq = 0;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const __half2 hh = *reinterpret_cast<const __half2*>(&w[(4 * i + e) / 2]);
+              const float val = (e & 1) ? __high2float(hh) : __low2float(hh);
+              pkq |= (uint32_t(quantize_exact(val, p.o_scale, inv_o_scale, 0)) & 0xffu) << (8 * e);
+            }
+            qw[i] = pkq;
+          }
+          int8_t* qrow = p.oq + off + c * 32;
+          reinterpret_cast<uint4*>(qrow)[0] = make_uint4(qw[0], qw[1], qw[2], qw[3]);
+          reinterpret_cast<uint4*>(qrow)[1] = make_uint4(qw[4], qw[5], qw[6], qw[7]);
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+}  // namespace zen
