@@ -213,18 +213,26 @@ flash_attn_pipe_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       const int key0 = j * 128;
       int lim = kv_len - key0;
       if (p.causal && q + 1 - key0 < lim) lim = q + 1 - key0;
-      // pass 1: row maximum of this block
-      float mx = -INFINITY;
+      // pass 1: row maximum of this block (four independent chains; no predicates when the block is
+      // entirely valid for this row)
+      const bool full_blk = lim >= 128;
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         uint32_t sv[32];
         __syncwarp();
         tmem_ld_32x32(tmem_s + lane_sel + c * 32, sv);
         tmem_wait_ld();
+        if (full_blk) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (c * 32 + i < lim) mx = fmaxf(mx, __uint_as_float(sv[i]));
+          for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (c * 32 + i < lim) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[i]));
+        }
       }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       const float m_blk = mx * p.scale_log2;
       // move the reference maximum only when this row has outgrown it by more than the threshold
       const bool grow = m_blk > m_ref + RESCALE_THRESHOLD || (m_ref == -INFINITY && m_blk != -INFINITY);
@@ -252,7 +260,8 @@ flash_attn_pipe_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       }
       m_ref = m_new;
       // pass 2: probabilities -> shared memory (fp16, swizzled K-major), row sum
-      float rowsum = 0.f;
+      float rs4[4] = {0.f, 0.f, 0.f, 0.f};
+      const float neg_m = -m_use;
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         uint32_t sv[32];
@@ -260,13 +269,25 @@ flash_attn_pipe_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         tmem_ld_32x32(tmem_s + lane_sel + c * 32, sv);
         tmem_wait_ld();
         uint32_t pk[16];
+        if (full_blk) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float a = (c * 32 + 2 * i < lim) ? fast_exp2(__uint_as_float(sv[2 * i]) * p.scale_log2 - m_use) : 0.f;
-          const float bq = (c * 32 + 2 * i + 1 < lim) ? fast_exp2(__uint_as_float(sv[2 * i + 1]) * p.scale_log2 - m_use) : 0.f;
-          rowsum += a + bq;
-          const __half2 hh = __floats2half2_rn(a, bq);
-          pk[i] = *reinterpret_cast<const uint32_t*>(&hh);
+          for (int i = 0; i < 16; ++i) {
+            const float a = fast_exp2(fmaf(__uint_as_float(sv[2 * i]), p.scale_log2, neg_m));
+            const float bq = fast_exp2(fmaf(__uint_as_float(sv[2 * i + 1]), p.scale_log2, neg_m));
+            rs4[i & 3] += a + bq;
+            const __half2 hh = __floats2half2_rn(a, bq);
+            pk[i] = *reinterpret_cast<const uint32_t*>(&hh);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float a = (c * 32 + 2 * i < lim) ? fast_exp2(fmaf(__uint_as_float(sv[2 * i]), p.scale_log2, neg_m)) : 0.f;
+            const float bq =
+                (c * 32 + 2 * i + 1 < lim) ? fast_exp2(fmaf(__uint_as_float(sv[2 * i + 1]), p.scale_log2, neg_m)) : 0.f;
+            rs4[i & 3] += a + bq;
+            const __half2 hh = __floats2half2_rn(a, bq);
+            pk[i] = *reinterpret_cast<const uint32_t*>(&hh);
+          }
         }
         uint8_t* prow = myP + (c >> 1) * CHUNK_BYTES + r * 128;
 #pragma unroll
@@ -275,6 +296,7 @@ flash_attn_pipe_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
           *reinterpret_cast<uint4*>(prow + unit * 16) = make_uint4(pk[4 * u], pk[4 * u + 1], pk[4 * u + 2], pk[4 * u + 3]);
         }
       }
+      const float rowsum = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
       l_run += rowsum;
       tc_fence_before_sync();
       fence_proxy_async_smem();
