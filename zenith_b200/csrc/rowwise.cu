@@ -68,15 +68,23 @@ __device__ __forceinline__ int quantize_value(float x, float scale, int zero_poi
 
 template <int N>
 __device__ __forceinline__ void store_q(int8_t* p, const float (&v)[N], float scale, float inv_scale, int round_mode) {
+  int q[N];
+  if (round_mode == 0) {
+    const uint32_t risky = quantize_fast_rn<N>(v, inv_scale, q);
+    if (risky) {
+#pragma unroll
+      for (int j = 0; j < N; ++j)
+        if (risky & (1u << j)) q[j] = zen_det_round_clamp_i8(ZEN_DIV(v[j], scale), 0);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < N; ++j) q[j] = zen_det_round_clamp_i8(ZEN_DIV(v[j], scale), round_mode);
+  }
   uint32_t w[N / 4];
 #pragma unroll
-  for (int i = 0; i < N / 4; ++i) {
-    uint32_t pk = 0;
-#pragma unroll
-    for (int b = 0; b < 4; ++b)
-      pk |= (uint32_t(quantize_exact(v[4 * i + b], scale, inv_scale, round_mode)) & 0xffu) << (8 * b);
-    w[i] = pk;
-  }
+  for (int i = 0; i < N / 4; ++i)
+    w[i] = (uint32_t(q[4 * i]) & 0xffu) | ((uint32_t(q[4 * i + 1]) & 0xffu) << 8) |
+           ((uint32_t(q[4 * i + 2]) & 0xffu) << 16) | ((uint32_t(q[4 * i + 3]) & 0xffu) << 24);
   if constexpr (N == 8) *reinterpret_cast<uint2*>(p) = make_uint2(w[0], w[1]);
   else *reinterpret_cast<uint32_t*>(p) = w[0];
 }

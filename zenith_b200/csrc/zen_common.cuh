@@ -293,6 +293,22 @@ __device__ __forceinline__ int quantize_exact(float x, float scale, float inv_sc
   return q;
 }
 
+// Branch-free nearest-even form of quantize_exact for N values at once: q[] receives the fast
+// roundings, the returned mask flags the values that lie too close to a rounding boundary and
+// must be recomputed with the true division (a few per thousand).
+template <int N>
+__device__ __forceinline__ uint32_t quantize_fast_rn(const float (&x)[N], float inv_scale, int (&q)[N]) {
+  uint32_t risky = 0;
+#pragma unroll
+  for (int j = 0; j < N; ++j) {
+    const float tc = fminf(fmaxf(x[j] * inv_scale, -128.0f), 127.0f);
+    const float m = tc + 12582912.0f;
+    q[j] = __float_as_int(m) - 0x4B400000;
+    if (fabsf(tc - (m - 12582912.0f)) > 0.5f - 1e-3f) risky |= 1u << j;
+  }
+  return risky;
+}
+
 // ---------------------------------------------------------------------------
 // descriptors
 // ---------------------------------------------------------------------------
