@@ -2,7 +2,7 @@
 
 * ``oracle/_build/libzen_oracle.so``  from ``oracle/zen_oracle.c`` (gcc, -ffp-contract=off).
 * ``oracle/_ref/libzenith_ref_cpu.so`` from the REFERENCE's own ``core/src/cpu_kernels.cpp``, compiled
-  where it lies under the mounted reference tree (``ZENITH_REFERENCE`` or ``/root/reference``) with
+  where it lies under the mounted reference tree (environment variable ``ZENITH_REFERENCE``) with
   ``g++ -O3 -mavx2 -mfma -std=c++20`` plus a C-linkage shim.  Skipped when the tree is absent: a
   prebuilt ``_ref`` library is then used as it is.
 

@@ -391,14 +391,7 @@ static int launch_fa(const CUtensorMap& tq, const CUtensorMap& tk, const CUtenso
                      cudaStream_t s) {
   auto kernel = flash_attn_kernel<D, KV_STAGES>;
   constexpr size_t smem = fa_smem_bytes<D, KV_STAGES>();
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) {
-      cudaGetLastError();
-      return ZEN_ERR_LAUNCH;
-    }
-    attr_set = true;
-  }
+  if (int st = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), smem); st != ZEN_OK) return st;
   dim3 grid((p.S + FA_BQ - 1) / FA_BQ, p.H, p.B);
   return launch_pdl(PDL_ATTENTION, kernel, grid, dim3(FA_THREADS), smem, s, tq, tk, tv, p);
 }
@@ -408,14 +401,7 @@ static int launch_fa_pipe(const CUtensorMap& tq, const CUtensorMap& tk, const CU
                           cudaStream_t s) {
   auto kernel = flash_attn_pipe_kernel<D, KV_STAGES>;
   constexpr size_t smem = fap_smem_bytes<D, KV_STAGES>();
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) {
-      cudaGetLastError();
-      return ZEN_ERR_LAUNCH;
-    }
-    attr_set = true;
-  }
+  if (int st = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), smem); st != ZEN_OK) return st;
   dim3 grid((p.S + 255) / 256, p.H, p.B);
   return launch_pdl(PDL_ATTENTION, kernel, grid, dim3(FAP_THREADS), smem, s, tq, tk, tv, p);
 }

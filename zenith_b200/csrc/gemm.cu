@@ -35,14 +35,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
                        cudaStream_t stream) {
   auto kernel = gemm_tc_kernel<KIND, BN, STAGES, B_MN>;
   constexpr size_t smem = gemm_smem_bytes<BN, STAGES>();
-  static bool attr_set = false;  // per instantiation; setting twice is harmless
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) {
-      cudaGetLastError();
-      return ZEN_ERR_LAUNCH;
-    }
-    attr_set = true;
-  }
+  if (int st = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), smem); st != ZEN_OK) return st;
   p.tiles_m = (p.M + GEMM_BM - 1) / GEMM_BM;
   p.tiles_n = (p.N + BN - 1) / BN;
   const int tiles = p.tiles_m * p.tiles_n;

@@ -435,14 +435,7 @@ static int launch_gemm_ln(const CUtensorMap& ta, const CUtensorMap& tb, const CU
                           const CUtensorMap& tr, const GemmLnParams& p, cudaStream_t stream) {
   auto kernel = gemm_i8_ln_kernel<BN, STAGES>;
   constexpr size_t smem = gemm_ln_smem_bytes<BN, STAGES>();
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) {
-      cudaGetLastError();
-      return ZEN_ERR_LAUNCH;
-    }
-    attr_set = true;
-  }
+  if (int st = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), smem); st != ZEN_OK) return st;
   int clusters = num_sms() / LN_CLUSTER;
   if (clusters > p.tiles_m) clusters = p.tiles_m;
   cudaLaunchConfig_t cfg = {};

@@ -7,6 +7,8 @@
 #include <stdint.h>
 #include <stdlib.h>
 #include <utility>
+#include <mutex>
+#include <set>
 #include "../../include/zenith_b200.h"
 
 namespace zen {
@@ -96,14 +98,33 @@ inline int launch_pdl(int family, void (*kernel)(KArgs...), dim3 grid, dim3 bloc
   return ZEN_OK;
 }
 
+// Opt a kernel in to more than 48 KB of dynamic shared memory, once per (kernel, device).
+inline int ensure_dynamic_smem(const void* kernel, size_t smem) {
+  static std::mutex mu;
+  static std::set<std::pair<const void*, int>> done;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) {
+    cudaGetLastError();
+    return ZEN_ERR_LAUNCH;
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  if (done.count({kernel, dev})) return ZEN_OK;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) {
+    cudaGetLastError();
+    return ZEN_ERR_LAUNCH;
+  }
+  done.insert({kernel, dev});
+  return ZEN_OK;
+}
+
 inline int num_sms() {
-  static int n = []() {
-    int dev = 0, v = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
-    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) return 148;
-    return v;
-  }();
-  return n;
+  static int cached[64] = {};
+  int dev = 0, v = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] > 0) return cached[dev];
+  if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) return 148;
+  cached[dev] = v;
+  return v;
 }
 
 }  // namespace zen
