@@ -10,7 +10,8 @@
 // pairwise (Chan) update, which is as robust as the two-pass form of the stand-alone kernel.
 //
 // Main loop, warp roles, TMEM double buffering and the TMA-store epilogue are those of
-// gemm_tc.cuh; the epilogue reads each accumulator twice (statistics pass, normalise pass).
+// gemm_tc.cuh; the epilogue makes two passes over tensor memory: the first replaces each accumulator
+// by y (fp32) and reduces the statistics, the second normalises.
 #include "gemm_tc.cuh"
 #include "tma_host.cuh"
 
@@ -255,7 +256,8 @@ gemm_i8_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       for (int i = lane; i < 64; i += 32) {
         const int col = n0 + i;
         const bool in = col < p.N;
-        s_scale[i] = (p.w_scale != nullptr && in) ? __ldg(p.w_scale + col) : 1.0f;
+        // LayerNorm is a tolerance path: the two dequantisation scales are folded into one factor
+        s_scale[i] = p.x_scale * ((p.w_scale != nullptr && in) ? __ldg(p.w_scale + col) : 1.0f);
         s_bias[i] = (p.bias != nullptr && in) ? __ldg(p.bias + col) : 0.0f;
         s_gamma[i] = in ? __half2float(p.gamma[col]) : 0.0f;
         s_beta[i] = in ? __half2float(p.beta[col]) : 0.0f;
@@ -283,8 +285,9 @@ gemm_i8_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         tc_fence_after_sync();
         const uint32_t tacc = tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * BN + sub * 64);
 
-        // ---- pass A: statistics of this thread's 64 values of its row
-        float cnt = 0.f, mean = 0.f, m2 = 0.f;
+        // ---- pass A: y = dequant + bias + residual for this thread's 64 values of its row, written
+        //      back over the accumulator (fp32 bits) for pass B, and their (mean, M2)
+        float mean = 0.f, m2 = 0.f;
 #pragma unroll 1
         for (int i = 0; i < STEPS; ++i) {
           uint32_t a[GEMM_CW];
@@ -293,17 +296,27 @@ gemm_i8_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           uint4 rr[2];
           rr[0] = *reinterpret_cast<const uint4*>(sty + lane * 128 + (((2 * i) ^ (lane & 7)) << 4));
           rr[1] = *reinterpret_cast<const uint4*>(sty + lane * 128 + (((2 * i + 1) ^ (lane & 7)) << 4));
+          float cs[GEMM_CW], bs[GEMM_CW];
+#pragma unroll
+          for (int j4 = 0; j4 < GEMM_CW / 4; ++j4) {
+            *reinterpret_cast<float4*>(cs + 4 * j4) = reinterpret_cast<const float4*>(s_scale + i * GEMM_CW)[j4];
+            *reinterpret_cast<float4*>(bs + 4 * j4) = reinterpret_cast<const float4*>(s_bias + i * GEMM_CW)[j4];
+          }
           tmem_wait_ld();
           const __half2* rh = reinterpret_cast<const __half2*>(rr);
           float y[GEMM_CW];
           float s = 0.f;
 #pragma unroll
-          for (int j = 0; j < GEMM_CW; ++j) {
+          for (int j = 0; j < GEMM_CW; j += 2) {
             const float2 rf = __half22float2(rh[j >> 1]);
-            y[j] = zen_det_dequant(int32_t(a[j]), p.x_scale, s_scale[i * GEMM_CW + j], s_bias[i * GEMM_CW + j]) +
-                   ((j & 1) ? rf.y : rf.x);
-            s += y[j];
+            y[j] = fmaf(float(int32_t(a[j])), cs[j], bs[j]) + rf.x;
+            y[j + 1] = fmaf(float(int32_t(a[j + 1])), cs[j + 1], bs[j + 1]) + rf.y;
+            s += y[j] + y[j + 1];
           }
+          uint32_t yb[GEMM_CW];
+#pragma unroll
+          for (int j = 0; j < GEMM_CW; ++j) yb[j] = __float_as_uint(y[j]);
+          tmem_st_32x16(tacc + uint32_t(i * GEMM_CW), yb);
           const float mu = s * (1.0f / GEMM_CW);
           float q2 = 0.f;
 #pragma unroll
@@ -312,13 +325,17 @@ gemm_i8_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             q2 = fmaf(d, d, q2);
           }
           if (i == 0) {
-            cnt = GEMM_CW;
             mean = mu;
             m2 = q2;
           } else {
-            chan_merge(cnt, mean, m2, float(GEMM_CW), mu, q2);
+            // pairwise update with n_a = 16 i, n_b = 16: n_b / n = 1 / (i + 1)
+            const float f = i == 1 ? 0.5f : i == 2 ? (1.0f / 3.0f) : i == 3 ? 0.25f : 1.0f / float(i + 1);
+            const float delta = mu - mean;
+            mean = fmaf(delta, f, mean);
+            m2 = m2 + q2 + delta * delta * (float(GEMM_CW * i) * f);
           }
         }
+        tmem_wait_st();
         pstats[sub * 128 + r] = make_float2(mean, m2);
         mbar_arrive(slab_bar);
         if (sub == 0) {
@@ -353,27 +370,25 @@ gemm_i8_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         }
         const float rstd = rsqrtf(q2 * inv_n + p.eps);
 
-        // ---- pass B: normalise, stage fp16 (+ int8), TMA stores
+        // ---- pass B: normalise y (read back from tensor memory), stage fp16 (+ int8), TMA stores
 #pragma unroll 1
         for (int i = 0; i < STEPS; ++i) {
-          uint32_t a[GEMM_CW];
+          uint32_t yb[GEMM_CW];
           __syncwarp();
-          tmem_ld_32x16(tacc + uint32_t(i * GEMM_CW), a);
-          uint4 rr[2];
-          rr[0] = *reinterpret_cast<const uint4*>(sty + lane * 128 + (((2 * i) ^ (lane & 7)) << 4));
-          rr[1] = *reinterpret_cast<const uint4*>(sty + lane * 128 + (((2 * i + 1) ^ (lane & 7)) << 4));
+          tmem_ld_32x16(tacc + uint32_t(i * GEMM_CW), yb);
+          float gs[GEMM_CW], bs[GEMM_CW];
+#pragma unroll
+          for (int j4 = 0; j4 < GEMM_CW / 4; ++j4) {
+            *reinterpret_cast<float4*>(gs + 4 * j4) = reinterpret_cast<const float4*>(s_gamma + i * GEMM_CW)[j4];
+            *reinterpret_cast<float4*>(bs + 4 * j4) = reinterpret_cast<const float4*>(s_beta + i * GEMM_CW)[j4];
+          }
           tmem_wait_ld();
-          const __half2* rh = reinterpret_cast<const __half2*>(rr);
           uint32_t w[GEMM_CW / 2];
           float of[GEMM_CW];
 #pragma unroll
           for (int j = 0; j < GEMM_CW; j += 2) {
-            const float2 rf = __half22float2(rh[j >> 1]);
-            const float y0 = zen_det_dequant(int32_t(a[j]), p.x_scale, s_scale[i * GEMM_CW + j], s_bias[i * GEMM_CW + j]) + rf.x;
-            const float y1 = zen_det_dequant(int32_t(a[j + 1]), p.x_scale, s_scale[i * GEMM_CW + j + 1],
-                                             s_bias[i * GEMM_CW + j + 1]) + rf.y;
-            const float o0 = (y0 - mu) * rstd * s_gamma[i * GEMM_CW + j] + s_beta[i * GEMM_CW + j];
-            const float o1 = (y1 - mu) * rstd * s_gamma[i * GEMM_CW + j + 1] + s_beta[i * GEMM_CW + j + 1];
+            const float o0 = fmaf((__uint_as_float(yb[j]) - mu) * rstd, gs[j], bs[j]);
+            const float o1 = fmaf((__uint_as_float(yb[j + 1]) - mu) * rstd, gs[j + 1], bs[j + 1]);
             const __half2 h = __floats2half2_rn(o0, o1);
             w[j >> 1] = *reinterpret_cast<const uint32_t*>(&h);
             of[j] = __low2float(h);  // the int8 copy quantizes the value that was stored

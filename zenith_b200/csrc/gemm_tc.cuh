@@ -253,6 +253,100 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[GEMM_CW], con
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// int8 accumulators -> int8 outputs, nearest-even: the FFN1 epilogue, which is bound by instruction
+// issue and by the conversion / special-function unit, not by memory.  Differences from the generic
+// step: (1) the s32 -> f32 conversion goes through the 1.5 * 2^23 constant on the integer and FP32
+// pipes (exact for |acc| < 2^22; anything larger is caught by `span` and takes the exact path), which
+// leaves the conversion unit to the exponential and the reciprocal; (2) the exact recomputation is a
+// rolled out-of-line loop over the flagged columns that reads the accumulators again from tensor
+// memory, so the straight-line step body stays small.  Returns the mask of this lane's elements that
+// must be recomputed.
+// ---------------------------------------------------------------------------------------------
+template <int ACT>
+__device__ __forceinline__ uint32_t requant_i8_step(const uint32_t (&r)[GEMM_CW], const float* sc, const float* bi,
+                                                float x_scale, float inv_scale, uint32_t (&w)[GEMM_CW / 4]) {
+  constexpr float MAGIC = 12582912.0f;  // 1.5 * 2^23
+  uint32_t span = 0;
+  uint32_t risky = 0;
+#pragma unroll
+  for (int j4 = 0; j4 < GEMM_CW / 4; ++j4) {
+    const float4 s4 = reinterpret_cast<const float4*>(sc)[j4];
+    const float4 b4 = reinterpret_cast<const float4*>(bi)[j4];
+    const float ss[4] = {s4.x, s4.y, s4.z, s4.w};
+    const float bb[4] = {b4.x, b4.y, b4.z, b4.w};
+    uint32_t mb[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const uint32_t t = r[4 * j4 + e] + 0x4B400000u;  // bits of the float 1.5 * 2^23 + acc while |acc| < 2^22
+      span |= t ^ 0x4B000000u;                          // any bit >= 23 set: acc outside that range
+      const float a = __uint_as_float(t) - MAGIC;       // == float(acc), exact
+      float g = ZEN_ADD(ZEN_MUL(ZEN_MUL(a, x_scale), ss[e]), bb[e]);  // == zen_det_dequant
+      if constexpr (ACT == ZEN_ACT_GELU) g = gelu_fast(g);
+      if constexpr (ACT == ZEN_ACT_RELU) g = fmaxf(g, 0.0f);
+      const float tc = fminf(fmaxf(g * inv_scale, -128.0f), 127.0f);  // NaN -> -128, as in the exact definition
+      const float m = tc + MAGIC;                                      // low mantissa byte == int8 bits of rint(tc)
+      // |tc - rint(tc)| close to 0.5 <=> close to a rounding boundary (a clamped value has distance 0)
+      if (fmaf(fabsf(tc), 4e-6f, fabsf(tc - (m - MAGIC))) > 0.5f - 2e-6f) risky |= 1u << (4 * j4 + e);
+      mb[e] = __float_as_uint(m);
+    }
+    w[j4] = __byte_perm(__byte_perm(mb[0], mb[1], 0x0040), __byte_perm(mb[2], mb[3], 0x0040), 0x5410);
+  }
+  return span >= 0x00800000u ? (1u << GEMM_CW) - 1u : risky;
+}
+
+// The exact definition for the columns flagged in `any` (the union of the lanes' masks), one column
+// per iteration, starting at tensor-memory address `taddr` (the whole warp must call this: the loads
+// are warp-collective).  Each lane overwrites the output bytes at `dst` that its own mask flags.
+template <int ACT>
+__device__ __noinline__ void requant_i8_fixup(uint32_t taddr, const float* sc, const float* bi, float x_scale,
+                                              float out_scale, uint32_t any, uint32_t mine, int8_t* dst) {
+  while (any != 0) {
+    const int j = __ffs(int(any)) - 1;
+    any &= any - 1u;
+    uint32_t v;
+    tmem_ld_32x1(taddr + uint32_t(j), v);
+    tmem_wait_ld();
+    if (mine & (1u << j)) {
+      const float y = zen_det_dequant(int32_t(v), x_scale, sc[j], bi[j]);
+      dst[j] = int8_t(zen_det_round_clamp_i8(ZEN_DIV(zen_det_act(y, ACT), out_scale), 0));
+    }
+    __syncwarp();
+  }
+}
+
+// One step of the int8 -> int8 nearest-even epilogue (all 32 lanes must call it).
+template <int ACT>
+__device__ __forceinline__ void epilogue_step_s8(const uint32_t (&r)[GEMM_CW], uint32_t taddr, const float* sc,
+                                                 const float* bi, const GemmParams& p, int row, int col0, bool row_ok,
+                                                 bool vec_ok, float inv_scale, uint8_t* stage, int lane, int istep) {
+  uint32_t w[GEMM_CW / 4];
+  uint32_t redo = requant_i8_step<ACT>(r, sc, bi, p.x_scale, inv_scale, w);
+  const int nvalid = p.N - col0;
+  int8_t* dst;
+  bool live;
+  if (stage != nullptr) {
+    dst = reinterpret_cast<int8_t*>(stage + lane * 64 + ((istep ^ ((lane >> 1) & 3)) << 4));
+    live = true;
+    *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+  } else {
+    dst = static_cast<int8_t*>(p.out) + int64_t(row) * p.ldo + col0;
+    live = row_ok && nvalid > 0;
+    if (live) {
+      if (vec_ok && nvalid >= GEMM_CW) store_words<GEMM_CW / 4>(dst, w);
+      else {
+#pragma unroll
+        for (int j = 0; j < GEMM_CW; ++j)
+          if (j < nvalid) dst[j] = int8_t((w[j >> 2] >> (8 * (j & 3))) & 0xffu);
+      }
+    }
+  }
+  if (!live) redo = 0;
+  else if (stage == nullptr && nvalid < GEMM_CW) redo &= (1u << nvalid) - 1u;
+  const uint32_t any = __reduce_or_sync(0xffffffffu, redo);
+  if (any != 0) requant_i8_fixup<ACT>(taddr, sc, bi, p.x_scale, p.out_scale, any, redo, dst);
+}
+
 template <int KIND, int OUT>
 __device__ __forceinline__ void epilogue_chunk_act(const uint32_t (&r)[GEMM_CW], const float* sc, const float* bi,
                                                    const GemmParams& p, int row, int col0, bool full, float inv_scale,
@@ -445,6 +539,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           tmem_ld_32x16(tacc + uint32_t(i * GEMM_CW), r);
           tmem_wait_ld();
           const int col0 = n0 + i * GEMM_CW;
+          if constexpr (KIND == KIND_I8) {
+            if (p.out_dtype == ZEN_DT_S8 && p.round_mode == 0) {
+              const float* sc = s_scale + i * GEMM_CW;
+              const float* bi = s_bias + i * GEMM_CW;
+              const uint32_t ta = tacc + uint32_t(i * GEMM_CW);
+              if (p.act == ZEN_ACT_GELU)
+                epilogue_step_s8<ZEN_ACT_GELU>(r, ta, sc, bi, p, row, col0, row_ok, vec_ok, inv_scale, stage, lane, i);
+              else if (p.act == ZEN_ACT_RELU)
+                epilogue_step_s8<ZEN_ACT_RELU>(r, ta, sc, bi, p, row, col0, row_ok, vec_ok, inv_scale, stage, lane, i);
+              else
+                epilogue_step_s8<ZEN_ACT_NONE>(r, ta, sc, bi, p, row, col0, row_ok, vec_ok, inv_scale, stage, lane, i);
+              continue;
+            }
+          }
           if (!staged && (!row_ok || col0 >= p.N)) continue;
           const bool full = vec_ok && (col0 + GEMM_CW <= p.N);
           const float* sc = s_scale + i * GEMM_CW;
