@@ -74,6 +74,16 @@ int zen_linear_i8(const int8_t* xq, int64_t ldx, const int8_t* wq, int64_t ldw, 
                   const float* w_scale, const float* bias, int act, int out_dtype, float out_scale, int round_mode,
                   void* out, int64_t ldo, void* stream);
 
+/* zen_linear_i8 plus an L2 prefetch hint: while its CTAs wait for their own operands the kernel asks the
+ * memory system to bring up to two read-only ranges into L2 (typically the weights of the GEMMs that
+ * follow; a pass's weights do not stay in L2 beside the activations, so each GEMM otherwise starts on
+ * HBM-cold weights).  The ranges are only hinted at, never read: results are those of zen_linear_i8.
+ * A range with 0 bytes is ignored.  No counterpart in the reference. */
+int zen_linear_i8_prefetch(const int8_t* xq, int64_t ldx, const int8_t* wq, int64_t ldw, int M, int N, int K,
+                           float x_scale, const float* w_scale, const float* bias, int act, int out_dtype,
+                           float out_scale, int round_mode, void* out, int64_t ldo, const void* next0,
+                           size_t next0_bytes, const void* next1, size_t next1_bytes, void* stream);
+
 /* W8A8 Linear + residual add + LayerNorm in one kernel, for projections whose output width is the hidden
  * size (attention output, FFN2):
  *   t = (float(acc) * x_scale) * w_scale[n] + bias[n] + residual[m,n];   y = LayerNorm_n(t) * gamma + beta

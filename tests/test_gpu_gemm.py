@@ -66,6 +66,25 @@ def test_int8_fused_epilogue_bit_exact(cuda, act, out):
     assert np.array_equal(got.view(np.uint8), want.view(np.uint8))
 
 
+def test_prefetch_hint_changes_nothing(cuda):
+    """zen_linear_i8_prefetch: odd sizes and unaligned ranges are accepted, the ranges are not modified and the
+    result is that of the plain call."""
+    M, N, K = 300, 520, 256
+    x = dev(rng(1).integers(-128, 128, (M, K), dtype=np.int8), cuda)
+    w = dev(rng(2).integers(-128, 128, (N, K), dtype=np.int8), cuda)
+    ws = dev((rng(3).random(N) * 1e-3).astype(np.float32), cuda)
+    nxt = torch.arange(3_000_001, dtype=torch.int32, device=cuda).to(torch.int8)
+    keep = nxt.clone()
+    kw = dict(act="gelu", out_dtype=torch.int8, out_scale=0.05)
+    plain = ops.linear_int8(x, w, 0.02, ws, None, **kw)
+    for hint in ((nxt,), (nxt[1:], nxt[5:77]), (nxt[3:4],)):
+        assert torch.equal(ops.linear_int8(x, w, 0.02, ws, None, prefetch=hint, **kw), plain)
+    assert torch.equal(nxt, keep)
+    with pytest.raises(RuntimeError):
+        ops.linear_int8(x, w, 0.02, ws, None, prefetch=(nxt, nxt, nxt), **kw)
+    assert _capi.device_status() == 0
+
+
 def test_int8_epilogue_trunc_rounding_and_no_scale_no_bias(cuda):
     x = rng(5).integers(-128, 128, (64, 64), dtype=np.int8)
     w = rng(6).integers(-128, 128, (48, 64), dtype=np.int8)

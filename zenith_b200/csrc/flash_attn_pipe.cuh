@@ -336,17 +336,29 @@ flash_attn_pipe_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         for (int i = 0; i < 4; ++i)
           reinterpret_cast<uint4*>(orow + c * 32)[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
         if (p.oq) {
+          // the int8 copy quantizes the fp16 values that were stored (branch-free rounding, exact
+          // division only next to a rounding boundary)
           uint32_t qw[8];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            uint32_t pkq = 0;
+          for (int g = 0; g < 2; ++g) {
+            float val[16];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const __half2 hh = *reinterpret_cast<const __half2*>(&w[(4 * i + e) / 2]);
-              const float val = (e & 1) ? __high2float(hh) : __low2float(hh);
-              pkq |= (uint32_t(quantize_exact(val, p.o_scale, inv_o_scale, 0)) & 0xffu) << (8 * e);
+            for (int e = 0; e < 8; ++e) {
+              const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&w[8 * g + e]));
+              val[2 * e] = f2.x;
+              val[2 * e + 1] = f2.y;
             }
-            qw[i] = pkq;
+            int qi[16];
+            const uint32_t risky = quantize_fast_rn<16>(val, inv_o_scale, qi);
+            if (risky) {
+#pragma unroll
+              for (int e = 0; e < 16; ++e)
+                if (risky & (1u << e)) qi[e] = zen_det_round_clamp_i8(ZEN_DIV(val[e], p.o_scale), 0);
+            }
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              qw[4 * g + e] = (uint32_t(qi[4 * e]) & 0xffu) | ((uint32_t(qi[4 * e + 1]) & 0xffu) << 8) |
+                              ((uint32_t(qi[4 * e + 2]) & 0xffu) << 16) | ((uint32_t(qi[4 * e + 3]) & 0xffu) << 24);
           }
           int8_t* qrow = p.oq + off + c * 32;
           reinterpret_cast<uint4*>(qrow)[0] = make_uint4(qw[0], qw[1], qw[2], qw[3]);

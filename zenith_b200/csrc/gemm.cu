@@ -134,7 +134,16 @@ int zen_gemm_set_tile_n(int bn) {
 int zen_linear_i8(const int8_t* xq, int64_t ldx, const int8_t* wq, int64_t ldw, int M, int N, int K, float x_scale,
                   const float* w_scale, const float* bias, int act, int out_dtype, float out_scale, int round_mode,
                   void* out, int64_t ldo, void* stream) {
+  return zen_linear_i8_prefetch(xq, ldx, wq, ldw, M, N, K, x_scale, w_scale, bias, act, out_dtype, out_scale,
+                                round_mode, out, ldo, nullptr, 0, nullptr, 0, stream);
+}
+
+int zen_linear_i8_prefetch(const int8_t* xq, int64_t ldx, const int8_t* wq, int64_t ldw, int M, int N, int K,
+                           float x_scale, const float* w_scale, const float* bias, int act, int out_dtype,
+                           float out_scale, int round_mode, void* out, int64_t ldo, const void* next0,
+                           size_t next0_bytes, const void* next1, size_t next1_bytes, void* stream) {
   if (!xq || !wq || !out || M <= 0 || N <= 0 || K <= 0) return ZEN_ERR_INVALID_ARG;
+  if ((next0_bytes != 0 && !next0) || (next1_bytes != 0 && !next1)) return ZEN_ERR_INVALID_ARG;
   if (out_dtype < ZEN_DT_S32 || out_dtype > ZEN_DT_S8 || act < ZEN_ACT_NONE || act > ZEN_ACT_RELU)
     return ZEN_ERR_INVALID_ARG;
   if (round_mode != ZEN_ROUND_NEAREST_EVEN && round_mode != ZEN_ROUND_TRUNC) return ZEN_ERR_INVALID_ARG;
@@ -144,6 +153,17 @@ int zen_linear_i8(const int8_t* xq, int64_t ldx, const int8_t* wq, int64_t ldw, 
   p.M = M; p.N = N; p.K = K;
   p.out = out; p.ldo = ldo; p.out_dtype = out_dtype; p.act = act; p.round_mode = round_mode;
   p.x_scale = x_scale; p.out_scale = out_scale; p.w_scale = w_scale; p.bias = bias;
+  const void* next[2] = {next0, next1};
+  const size_t next_bytes[2] = {next0_bytes, next1_bytes};
+  for (int i = 0; i < 2; ++i) {
+    // whole 16-byte units only: a hint may skip the ragged ends
+    const uintptr_t lo = (reinterpret_cast<uintptr_t>(next[i]) + 15u) & ~uintptr_t(15);
+    const uintptr_t hi = (reinterpret_cast<uintptr_t>(next[i]) + next_bytes[i]) & ~uintptr_t(15);
+    if (next_bytes[i] != 0 && hi > lo) {
+      p.pf_ptr[i] = reinterpret_cast<const uint8_t*>(lo);
+      p.pf_bytes[i] = uint64_t(hi - lo);
+    }
+  }
   static const int allowed[] = {64, 128, 192, 256};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (pick_bn(M, N, allowed, 4)) {

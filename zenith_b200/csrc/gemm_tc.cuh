@@ -37,7 +37,23 @@ struct GemmParams {
   const float* w_scale;
   const float* bias;
   int staged_store;  // 1: fp16 / int8 output leaves through shared memory and TMA stores
+  // L2 prefetch hint: read-only ranges (16-byte aligned, sizes multiples of 16) that later kernels will
+  // read, e.g. the next GEMMs' weights; every CTA asks for its slice while it waits for its own operands
+  const uint8_t* pf_ptr[2];
+  uint64_t pf_bytes[2];
 };
+
+// One CTA's share of an L2 prefetch range, in requests of at most 32 KB (a hint: nothing waits on it).
+__device__ __forceinline__ void prefetch_slice_l2(const uint8_t* ptr, uint64_t bytes, uint32_t cta, uint32_t n_ctas) {
+  const uint64_t per = ((bytes + n_ctas - 1) / n_ctas + 127u) & ~uint64_t(127);
+  const uint64_t lo = uint64_t(cta) * per;
+  if (lo >= bytes) return;
+  const uint64_t hi = lo + per < bytes ? lo + per : bytes;
+  for (uint64_t off = lo; off < hi; off += 32768u) {
+    const uint32_t sz = uint32_t(hi - off < 32768u ? hi - off : 32768u);
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(ptr + off), "r"(sz) : "memory");
+  }
+}
 
 template <int KIND>
 struct GemmKind;
@@ -418,6 +434,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 1) {
+    // constants of later kernels: safe to ask for before the previous kernel has finished
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+      if (p.pf_bytes[i] != 0) prefetch_slice_l2(p.pf_ptr[i], p.pf_bytes[i], blockIdx.x, gridDim.x);
+  }
   grid_launch_dependents();
   grid_dependency_wait();  // operands and output buffers may belong to the previous kernel until here
 

@@ -163,6 +163,12 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void*
                "r"(smem_u32(smem_src)), "r"(x), "r"(y)
                : "memory");
 }
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, const void* smem_src, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
+}
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // all committed stores of this thread have finished READING shared memory (the source may be reused)
 __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
@@ -310,16 +316,19 @@ __device__ __forceinline__ int quantize_exact(float x, float scale, float inv_sc
 
 // Branch-free nearest-even form of quantize_exact for N values at once: q[] receives the fast
 // roundings, the returned mask flags the values that lie too close to a rounding boundary and
-// must be recomputed with the true division (a few per thousand).
+// must be recomputed with the true division.  t = x * (1 / scale) differs from the quotient by less
+// than 2e-7 |t|, so only values within 4e-6 |t| + 2e-6 of a boundary can round differently (a few
+// per hundred thousand; a fixed 1e-3 margin flagged one value in nearly every warp-wide batch, and
+// the divergent recomputation then cost more than the rounding itself).
 template <int N>
 __device__ __forceinline__ uint32_t quantize_fast_rn(const float (&x)[N], float inv_scale, int (&q)[N]) {
   uint32_t risky = 0;
 #pragma unroll
   for (int j = 0; j < N; ++j) {
-    const float tc = fminf(fmaxf(x[j] * inv_scale, -128.0f), 127.0f);
+    const float tc = fminf(fmaxf(x[j] * inv_scale, -128.0f), 127.0f);  // NaN -> -128, as in the definition
     const float m = tc + 12582912.0f;
     q[j] = __float_as_int(m) - 0x4B400000;
-    if (fabsf(tc - (m - 12582912.0f)) > 0.5f - 1e-3f) risky |= 1u << j;
+    if (fabsf(tc - (m - 12582912.0f)) > fmaf(fabsf(tc), -4e-6f, 0.5f - 2e-6f)) risky |= 1u << j;
   }
   return risky;
 }

@@ -296,7 +296,7 @@ class Int8Encoder(_EncoderBase):
     """W8A8 encoder: int8 GEMM operands, int32 accumulation, fp16 residual stream / LayerNorm / softmax."""
 
     def __init__(self, cfg: EncoderConfig, params: dict, scales: Int8Scales, device="cuda:0", micro_batches: int = 1,
-                 fuse_layernorm: bool | None = None):
+                 fuse_layernorm: bool | None = None, prefetch_weights: bool = True):
         """``fuse_layernorm``: run attention-output and FFN2 as one GEMM + residual + LayerNorm kernel each
         (5 launches per layer instead of 7).  Possible for hidden 768 and 1024; on by default for 768 only (at
         BERT-large's 12k-token shards the separate kernels measured faster: 8.98 vs 10.26 ms per pass).  In the
@@ -306,6 +306,10 @@ class Int8Encoder(_EncoderBase):
         if self.fuse_layernorm and cfg.hidden not in (768, 1024):
             raise RuntimeError("the fused GEMM + LayerNorm kernel needs hidden == 768 or 1024")
         self.launches_per_layer = 5 if self.fuse_layernorm else 7
+        # The QKV GEMM hints the attention-output and FFN1 weights into L2 and the FFN1 GEMM the FFN2 and
+        # next layer's QKV weights (zen_linear_i8_prefetch): a pass's weights do not stay in L2 beside
+        # the activations, and a GEMM that starts on HBM-cold weights loses about a microsecond.
+        self.prefetch_weights = bool(prefetch_weights)
         d = self.device
         self.act_scales = scales.act
         self.layers = []
@@ -354,8 +358,12 @@ class Int8Encoder(_EncoderBase):
             a = sc[li]
             x, xq, xn, xqn = self.x[cur], self.xq[cur], self.x[cur ^ 1], self.xq[cur ^ 1]
             last = li == n_layers - 1
-            self._add("zen_linear_i8", P(xq), H, L["wqkv"].data_ptr(), H, T, 3 * H, H, a["x"], L["wqkv_s"].data_ptr(),
-                      L["bqkv"].data_ptr(), ACT_NONE, DT_F16, 1.0, ROUND_NEAREST_EVEN, P(self.qkv), 3 * H)
+            nbytes = lambda t: t.numel() * t.element_size()
+            pf = lambda *ts: [v for t in ts for v in ((t.data_ptr(), nbytes(t)) if self.prefetch_weights and t is not None
+                                                       else (None, 0))]
+            self._add("zen_linear_i8_prefetch", P(xq), H, L["wqkv"].data_ptr(), H, T, 3 * H, H, a["x"],
+                      L["wqkv_s"].data_ptr(), L["bqkv"].data_ptr(), ACT_NONE, DT_F16, 1.0, ROUND_NEAREST_EVEN,
+                      P(self.qkv), 3 * H, *pf(L["wo"], L["w1"]))
             self._add("zen_flash_attention_f16", P(self.qkv), P(self.qkv) + 2 * H, P(self.qkv) + 4 * H, P(self.ctx),
                       P(self.ctxq), a["ctx"], B, nh, S, hd, *qs, *qs, *qs, *os_, kv, 0, 1.0 / math.sqrt(hd))
             if self.fuse_layernorm:
@@ -368,8 +376,9 @@ class Int8Encoder(_EncoderBase):
                           P(self.ao), H)
                 self._add("zen_add_layernorm_f16", P(self.ao), P(x), L["ln1_g"].data_ptr(), L["ln1_b"].data_ptr(),
                           P(self.h1), P(self.h1q), a["h1"], ROUND_NEAREST_EVEN, T, H, cfg.eps)
-            self._add("zen_linear_i8", P(self.h1q), H, L["w1"].data_ptr(), H, T, F, H, a["h1"], L["w1_s"].data_ptr(),
-                      L["b1"].data_ptr(), ACT_GELU, DT_S8, a["gelu"], ROUND_NEAREST_EVEN, P(self.gq), F)
+            self._add("zen_linear_i8_prefetch", P(self.h1q), H, L["w1"].data_ptr(), H, T, F, H, a["h1"],
+                      L["w1_s"].data_ptr(), L["b1"].data_ptr(), ACT_GELU, DT_S8, a["gelu"], ROUND_NEAREST_EVEN,
+                      P(self.gq), F, *pf(L["w2"], None if last else self.layers[li + 1]["wqkv"]))
             if self.fuse_layernorm:
                 self._add("zen_linear_i8_add_layernorm", P(self.gq), F, L["w2"].data_ptr(), F, T, H, F, a["gelu"],
                           L["w2_s"].data_ptr(), L["b2"].data_ptr(), P(self.h1), H, L["ln2_g"].data_ptr(),

@@ -56,7 +56,7 @@ def _call(fn: str, *args) -> None:
 # GEMMs
 # --------------------------------------------------------------------------------------------
 def linear_int8(xq, wq, x_scale: float, w_scale=None, bias=None, *, act="none", out_dtype=torch.float32,
-                out_scale: float | None = None, round="nearest_even", out=None):
+                out_scale: float | None = None, round="nearest_even", out=None, prefetch=()):
     """W8A8 Linear: ``acc = xq @ wq.T`` in int32, then the fused epilogue.
 
     ``out_dtype=torch.int32`` returns the raw accumulators.  Otherwise
@@ -64,11 +64,16 @@ def linear_int8(xq, wq, x_scale: float, w_scale=None, bias=None, *, act="none", 
     output or requantisation ``clamp(round(y / out_scale))`` to int8.
     Follows core/src/cuda_kernels.cu:1010-1049 (fused_int8_linear_kernel) with per-output-channel
     weight scales (zenith/optimization/qat.py:195-199).
+
+    ``prefetch``: up to two CUDA tensors (e.g. the weights of the GEMMs that follow) that the kernel
+    hints into L2 while it runs; they are not read and the result does not depend on them.
     """
     _require(xq, "xq", torch.int8, 2)
     _require(wq, "wq", torch.int8, 2)
     M, K = xq.shape
     N, K2 = wq.shape
+    if len(prefetch) > 2 or any(not t.is_cuda for t in prefetch):
+        raise RuntimeError("prefetch takes at most two CUDA tensors")
     if K != K2:
         raise RuntimeError(f"inner dimensions differ: xq {tuple(xq.shape)} vs wq {tuple(wq.shape)}")
     if w_scale is not None:
@@ -89,9 +94,10 @@ def linear_int8(xq, wq, x_scale: float, w_scale=None, bias=None, *, act="none", 
         _require(out, "out", out_dtype, 2)
     if M == 0 or N == 0:
         return out
-    _call("zen_linear_i8", xq.data_ptr(), K, wq.data_ptr(), K, M, N, K, float(x_scale), _ptr(w_scale), _ptr(bias),
-          _ACT[act], _OUT[out_dtype], float(out_scale if out_scale is not None else 1.0), _ROUND[round],
-          out.data_ptr(), out.stride(0), _stream())
+    hint = [v for t in prefetch for v in (t.data_ptr(), t.numel() * t.element_size())] + [None, 0] * (2 - len(prefetch))
+    _call("zen_linear_i8_prefetch", xq.data_ptr(), K, wq.data_ptr(), K, M, N, K, float(x_scale), _ptr(w_scale),
+          _ptr(bias), _ACT[act], _OUT[out_dtype], float(out_scale if out_scale is not None else 1.0), _ROUND[round],
+          out.data_ptr(), out.stride(0), *hint, _stream())
     return out
 
 
