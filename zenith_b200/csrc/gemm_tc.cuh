@@ -279,32 +279,53 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[GEMM_CW], con
 // memory, so the straight-line step body stays small.  Returns the mask of this lane's elements that
 // must be recomputed.
 // ---------------------------------------------------------------------------------------------
+// The FP32 arithmetic runs on column pairs with the packed fp32x2 instructions of sm_100 (individually
+// rounded, so bit-identical to the scalar forms): one issue slot for two operations.
 template <int ACT>
 __device__ __forceinline__ uint32_t requant_i8_step(const uint32_t (&r)[GEMM_CW], const float* sc, const float* bi,
-                                                float x_scale, float inv_scale, uint32_t (&w)[GEMM_CW / 4]) {
+                                                    float x_scale, float inv_scale, uint32_t (&w)[GEMM_CW / 4]) {
   constexpr float MAGIC = 12582912.0f;  // 1.5 * 2^23
+  const float2 neg_magic = make_float2(-MAGIC, -MAGIC);
+  const float2 pos_magic = make_float2(MAGIC, MAGIC);
+  const float2 xs2 = make_float2(x_scale, x_scale);
+  const float2 inv2 = make_float2(inv_scale, inv_scale);
   uint32_t span = 0;
   uint32_t risky = 0;
 #pragma unroll
   for (int j4 = 0; j4 < GEMM_CW / 4; ++j4) {
     const float4 s4 = reinterpret_cast<const float4*>(sc)[j4];
     const float4 b4 = reinterpret_cast<const float4*>(bi)[j4];
-    const float ss[4] = {s4.x, s4.y, s4.z, s4.w};
-    const float bb[4] = {b4.x, b4.y, b4.z, b4.w};
     uint32_t mb[4];
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const uint32_t t = r[4 * j4 + e] + 0x4B400000u;  // bits of the float 1.5 * 2^23 + acc while |acc| < 2^22
-      span |= t ^ 0x4B000000u;                          // any bit >= 23 set: acc outside that range
-      const float a = __uint_as_float(t) - MAGIC;       // == float(acc), exact
-      float g = ZEN_ADD(ZEN_MUL(ZEN_MUL(a, x_scale), ss[e]), bb[e]);  // == zen_det_dequant
-      if constexpr (ACT == ZEN_ACT_GELU) g = gelu_fast(g);
-      if constexpr (ACT == ZEN_ACT_RELU) g = fmaxf(g, 0.0f);
-      const float tc = fminf(fmaxf(g * inv_scale, -128.0f), 127.0f);  // NaN -> -128, as in the exact definition
-      const float m = tc + MAGIC;                                      // low mantissa byte == int8 bits of rint(tc)
+    for (int h = 0; h < 2; ++h) {
+      const int j = 4 * j4 + 2 * h;
+      const uint32_t t0 = r[j] + 0x4B400000u;  // bits of the float 1.5 * 2^23 + acc while |acc| < 2^22
+      const uint32_t t1 = r[j + 1] + 0x4B400000u;
+      span |= (t0 ^ 0x4B000000u) | (t1 ^ 0x4B000000u);  // any bit >= 23 set: acc outside that range
+      const float2 a = __fadd2_rn(make_float2(__uint_as_float(t0), __uint_as_float(t1)), neg_magic);  // == float(acc), exact
+      const float2 ss = h ? make_float2(s4.z, s4.w) : make_float2(s4.x, s4.y);
+      const float2 bb = h ? make_float2(b4.z, b4.w) : make_float2(b4.x, b4.y);
+      float2 g = __fadd2_rn(__fmul2_rn(__fmul2_rn(a, xs2), ss), bb);  // == zen_det_dequant
+      if constexpr (ACT == ZEN_ACT_GELU) {
+        // gelu_fast on both halves: x / (1 + 2^(v * c)), v = x (1 + 0.044715 x^2)
+        const float2 x2 = __fmul2_rn(g, g);
+        const float2 wv = __ffma2_rn(make_float2(0.044715f, 0.044715f), x2, make_float2(1.0f, 1.0f));
+        const float2 v = __fmul2_rn(g, wv);
+        const float2 arg = __fmul2_rn(v, make_float2(-2.302208198144325f, -2.302208198144325f));
+        const float2 den = __fadd2_rn(make_float2(1.0f, 1.0f), make_float2(ex2_approx(arg.x), ex2_approx(arg.y)));
+        g = __fmul2_rn(g, make_float2(rcp_approx(den.x), rcp_approx(den.y)));
+      }
+      if constexpr (ACT == ZEN_ACT_RELU) g = make_float2(fmaxf(g.x, 0.0f), fmaxf(g.y, 0.0f));
+      const float2 t = __fmul2_rn(g, inv2);
+      // NaN -> -128, as in the exact definition
+      const float2 tc = make_float2(fminf(fmaxf(t.x, -128.0f), 127.0f), fminf(fmaxf(t.y, -128.0f), 127.0f));
+      const float2 m = __fadd2_rn(tc, pos_magic);  // low mantissa byte == int8 bits of rint(tc)
+      const float2 d = __ffma2_rn(__fadd2_rn(m, neg_magic), make_float2(-1.0f, -1.0f), tc);  // tc - rint(tc), exact
       // |tc - rint(tc)| close to 0.5 <=> close to a rounding boundary (a clamped value has distance 0)
-      if (fmaf(fabsf(tc), 4e-6f, fabsf(tc - (m - MAGIC))) > 0.5f - 2e-6f) risky |= 1u << (4 * j4 + e);
-      mb[e] = __float_as_uint(m);
+      if (fmaf(fabsf(tc.x), 4e-6f, fabsf(d.x)) > 0.5f - 2e-6f) risky |= 1u << j;
+      if (fmaf(fabsf(tc.y), 4e-6f, fabsf(d.y)) > 0.5f - 2e-6f) risky |= 1u << (j + 1);
+      mb[2 * h] = __float_as_uint(m.x);
+      mb[2 * h + 1] = __float_as_uint(m.y);
     }
     w[j4] = __byte_perm(__byte_perm(mb[0], mb[1], 0x0040), __byte_perm(mb[2], mb[3], 0x0040), 0x5410);
   }
