@@ -12,8 +12,9 @@ over 30522 words, the last 0..32 positions of each row masked).  Ranks are indep
 states.  Rank 0 prints ONE JSON line.
 
 `value`      sequences/s with token ids already in HBM (CUDA-graph replay of the 61 launches).
-`e2e`        the same through the public driver with HOST buffers: pinned ids / lengths copied to the
-             device and the fp16 hidden states copied back inside the timed region, every step.
+`e2e`        the same through the public host API (zenith_b200.serve.HostPipeline) with HOST buffers: every
+             step copies pinned ids / lengths to the device and the fp16 hidden states back to pinned host
+             memory inside the timed region; the copy back of step i overlaps the compute of step i + 1.
 `roofline`   the int8 tcgen05 GEMM (4 shapes x 12 layers per step), timed alone with CUDA events.
 `cpu_baseline` the CPU restatement of the reference's quantized executor (fake-quant + fp32 BLAS
              matmul), timed on this host's cores on a bounded sample.
@@ -216,6 +217,7 @@ def run_ours(args) -> None:
     from zenith_b200.calibrate import calibrate
     from zenith_b200.dist import OutputGatherer, init_from_env
     from zenith_b200.encoder import BERT_BASE, Int8Encoder, init_params
+    from zenith_b200.serve import HostPipeline
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback); use --impl reference for the CPU arm")
@@ -233,7 +235,6 @@ def run_ours(args) -> None:
     ids_np, lens_np = make_batch(MASTER_SEED + 1000 + rank, cfg.vocab)
     ids_h = torch.from_numpy(ids_np).pin_memory()
     lens_h = torch.from_numpy(lens_np).pin_memory()
-    out_h = torch.empty((BATCH * SEQ, cfg.hidden), dtype=torch.float16).pin_memory()
     enc.capture(BATCH, SEQ)
     enc.set_inputs(ids_h.to(dev), lens_h.to(dev))
     gatherer = OutputGatherer(BATCH * world, SEQ, cfg.hidden, torch.float16, dev) if world > 1 else None
@@ -254,12 +255,29 @@ def run_ours(args) -> None:
         if gatherer is not None:
             gatherer.gather(enc.out)
 
-    def step_e2e():
-        enc.set_inputs(ids_h, lens_h)          # pinned host -> device
-        enc.replay()
-        if gatherer is not None:
-            gatherer.gather(enc.out)
-        out_h.copy_(enc.out, non_blocking=True)  # device -> pinned host
+    # End to end through the public host API (zenith_b200.serve.HostPipeline): every step copies its ids /
+    # lengths from pinned host memory and its hidden states back to pinned host memory; the device->host
+    # copy of step i runs on a copy stream while step i + 1 computes, and the host waits for step i - 1's
+    # result before it queues step i + 1 (the loop a server would run).
+    pipe = HostPipeline(enc, BATCH, SEQ, after_replay=(gatherer.gather if gatherer is not None else None))
+
+    def timed_e2e(steps):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        s.record()
+        prev = None
+        for _ in range(steps):
+            t = pipe.submit(ids_h, lens_h)
+            if prev is not None:
+                pipe.result(prev)
+            prev = t
+        pipe.result(prev)
+        e.record()
+        barrier()
+        t = torch.tensor([s.elapsed_time(e)], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
 
     def timed(step_fn, steps):
         starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
@@ -286,9 +304,9 @@ def run_ours(args) -> None:
     launches0 = ops.launch_count
     total_ms = timed(step_device, K)
     launches = ops.launch_count - launches0
-    for _ in range(W):
-        step_e2e()
-    e2e_ms = timed(step_e2e, K)
+    timed_e2e(W)
+    e2e_ms = timed_e2e(K)
+    e2e_launches = enc.launches_per_forward + 1  # + the device copy that parks the result for the copy stream
     clocks = sampler.stop() if sampler else None
     status = _capi.device_status()
 
@@ -307,8 +325,13 @@ def run_ours(args) -> None:
         "config": {"workload": WORKLOAD, "global_batch": BATCH * world, "seq_len": SEQ, "parallelism": f"replicas x{world}",
                    "l2": "256 MB buffer written between timed steps", "launch": f"CUDA-graph replay of {enc.launches_per_forward} kernels in {args.micro_batches} concurrent micro-batch(es)"},
         "e2e": {"value": e2e_value, "unit": "sequences/s", "ms_per_step": e2e_ms / K,
-                "h2d_bytes_per_step": int(ids_h.numel() * 4 + lens_h.numel() * 4),
-                "d2h_bytes_per_step": int(out_h.numel() * 2)},
+                "h2d_bytes_per_step": int(ids_h.numel() * ids_h.element_size() + lens_h.numel() * lens_h.element_size()),
+                "d2h_bytes_per_step": int(pipe.host_out[0].numel() * 2),
+                "how": "zenith_b200.serve.HostPipeline: one event pair around all steps; per step pinned-host ids -> device, "
+                       "graph replay, hidden states -> pinned host on a copy stream that overlaps the next step's compute; "
+                       "no L2 flush in this loop (a step's working set, 85 MB of weights + 60 MB of activations, exceeds "
+                       "the 126 MB L2; flushing changed the device-resident step time by 0.3 %)",
+                "launches_per_step": e2e_launches},
         "gpu_launches": int(launches),
         "clocks": clocks,
         "device_status": status,

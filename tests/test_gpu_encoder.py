@@ -12,6 +12,7 @@ import torch
 
 from oracle import encoder_ref as ER
 from oracle import oracle as O
+from zenith_b200 import _capi
 from zenith_b200.calibrate import activation_scales_from_ranges, calibrate, quantize_weights
 from zenith_b200.encoder import EncoderConfig, Fp16Encoder, Int8Encoder, Int8Scales, init_params
 
@@ -143,3 +144,33 @@ def test_int8_encoder_with_fused_layernorm_kernels(cuda):
     enc.capture(*ids.shape)
     enc.set_inputs(*tdev(ids, lens, cuda))
     assert torch.equal(enc.replay(), eager)
+
+
+def test_host_pipeline_returns_every_batch(cuda):
+    """HostPipeline: different batches streamed back to back from pinned host memory come back, in host
+    memory, equal to what a plain forward pass gives for each of them."""
+    from zenith_b200.serve import HostPipeline
+
+    cfg = EncoderConfig(layers=2, hidden=768, heads=12, ffn=1024, vocab=2000, max_pos=128)
+    params = init_params(cfg, 11, random_affine=True)
+    mk = lambda s: (rng(s).integers(0, cfg.vocab, (4, 64)), rng(s + 100).integers(1, 65, 4).astype(np.int32))
+    scales = ER.calibrate_on_oracle(cfg, params, [mk(s) for s in range(2)], quantize_weights,
+                                    activation_scales_from_ranges, Int8Scales)
+    enc = Int8Encoder(cfg, params, scales, cuda)
+    batches = [mk(20 + i) for i in range(5)]
+    want = [enc.forward(*tdev(i, l, cuda)).cpu().clone() for i, l in batches]
+    pipe = HostPipeline(enc, 4, 64)
+    host = [(torch.from_numpy(i).pin_memory(), torch.from_numpy(l).pin_memory()) for i, l in batches]
+    got, prev = [], None
+    for ids_h, lens_h in host:
+        t = pipe.submit(ids_h, lens_h)
+        if prev is not None:
+            got.append(pipe.result(prev).clone())
+        prev = t
+    got.append(pipe.result(prev).clone())
+    pipe.drain()
+    for g, w in zip(got, want):
+        assert torch.equal(g, w)
+    with pytest.raises(ValueError):
+        pipe.result(0)  # its slot has been reused
+    assert _capi.device_status() == 0

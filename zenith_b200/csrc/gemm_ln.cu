@@ -304,26 +304,32 @@ gemm_i8_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           }
           tmem_wait_ld();
           const __half2* rh = reinterpret_cast<const __half2*>(rr);
-          float y[GEMM_CW];
-          float s = 0.f;
+          // column pairs on the packed fp32x2 instructions (one issue slot for two operations)
+          float2 y[GEMM_CW / 2];
+          float2 s2 = make_float2(0.f, 0.f);
 #pragma unroll
-          for (int j = 0; j < GEMM_CW; j += 2) {
-            const float2 rf = __half22float2(rh[j >> 1]);
-            y[j] = fmaf(float(int32_t(a[j])), cs[j], bs[j]) + rf.x;
-            y[j + 1] = fmaf(float(int32_t(a[j + 1])), cs[j + 1], bs[j + 1]) + rf.y;
-            s += y[j] + y[j + 1];
+          for (int j = 0; j < GEMM_CW / 2; ++j) {
+            const float2 af = make_float2(float(int32_t(a[2 * j])), float(int32_t(a[2 * j + 1])));
+            y[j] = f2add(f2fma(af, make_float2(cs[2 * j], cs[2 * j + 1]), make_float2(bs[2 * j], bs[2 * j + 1])),
+                              __half22float2(rh[j]));
+            s2 = f2add(s2, y[j]);
           }
           uint32_t yb[GEMM_CW];
 #pragma unroll
-          for (int j = 0; j < GEMM_CW; ++j) yb[j] = __float_as_uint(y[j]);
-          tmem_st_32x16(tacc + uint32_t(i * GEMM_CW), yb);
-          const float mu = s * (1.0f / GEMM_CW);
-          float q2 = 0.f;
-#pragma unroll
-          for (int j = 0; j < GEMM_CW; ++j) {
-            const float d = y[j] - mu;
-            q2 = fmaf(d, d, q2);
+          for (int j = 0; j < GEMM_CW / 2; ++j) {
+            yb[2 * j] = __float_as_uint(y[j].x);
+            yb[2 * j + 1] = __float_as_uint(y[j].y);
           }
+          tmem_st_32x16(tacc + uint32_t(i * GEMM_CW), yb);
+          const float mu = (s2.x + s2.y) * (1.0f / GEMM_CW);
+          const float2 nmu = make_float2(-mu, -mu);
+          float2 q22 = make_float2(0.f, 0.f);
+#pragma unroll
+          for (int j = 0; j < GEMM_CW / 2; ++j) {
+            const float2 d = f2add(y[j], nmu);
+            q22 = f2fma(d, d, q22);
+          }
+          const float q2 = q22.x + q22.y;
           if (i == 0) {
             mean = mu;
             m2 = q2;
@@ -385,14 +391,18 @@ gemm_i8_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           tmem_wait_ld();
           uint32_t w[GEMM_CW / 2];
           float of[GEMM_CW];
+          const float2 nmu = make_float2(-mu, -mu);
+          const float2 rstd2 = make_float2(rstd, rstd);
 #pragma unroll
           for (int j = 0; j < GEMM_CW; j += 2) {
-            const float o0 = fmaf((__uint_as_float(yb[j]) - mu) * rstd, gs[j], bs[j]);
-            const float o1 = fmaf((__uint_as_float(yb[j + 1]) - mu) * rstd, gs[j + 1], bs[j + 1]);
-            const __half2 h = __floats2half2_rn(o0, o1);
+            const float2 yv = make_float2(__uint_as_float(yb[j]), __uint_as_float(yb[j + 1]));
+            const float2 o = f2fma(f2mul(f2add(yv, nmu), rstd2), make_float2(gs[j], gs[j + 1]),
+                                        make_float2(bs[j], bs[j + 1]));
+            const __half2 h = __floats2half2_rn(o.x, o.y);
             w[j >> 1] = *reinterpret_cast<const uint32_t*>(&h);
-            of[j] = __low2float(h);  // the int8 copy quantizes the value that was stored
-            of[j + 1] = __high2float(h);
+            const float2 hf = __half22float2(h);  // the int8 copy quantizes the value that was stored
+            of[j] = hf.x;
+            of[j + 1] = hf.y;
           }
           uint8_t* srow = sty + lane * 128;
           *reinterpret_cast<uint4*>(srow + (((2 * i) ^ (lane & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);

@@ -199,11 +199,21 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[GEMM_CW], con
       const float4 b4 = reinterpret_cast<const float4*>(bi)[j4];
       const float ss[4] = {s4.x, s4.y, s4.z, s4.w};
       const float bb[4] = {b4.x, b4.y, b4.z, b4.w};
+      if constexpr (KIND == KIND_I8) {
+        // zen_det_dequant on column pairs: packed fp32x2 products, each rounded before the bias add
+        const float2 xs2 = make_float2(p.x_scale, p.x_scale);
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int j = 4 * j4 + e;
-        if constexpr (KIND == KIND_I8) y[j] = zen_det_dequant(int32_t(r[j]), p.x_scale, ss[e], bb[e]);
-        else y[j] = ZEN_ADD(__uint_as_float(r[j]), bb[e]);
+        for (int h = 0; h < 2; ++h) {
+          const int j = 4 * j4 + 2 * h;
+          const float2 a = make_float2(float(int32_t(r[j])), float(int32_t(r[j + 1])));
+          const float2 v = f2mul_then_add(f2mul(a, xs2), make_float2(ss[2 * h], ss[2 * h + 1]),
+                                          make_float2(bb[2 * h], bb[2 * h + 1]));
+          y[j] = v.x;
+          y[j + 1] = v.y;
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) y[4 * j4 + e] = ZEN_ADD(__uint_as_float(r[4 * j4 + e]), bb[e]);
       }
     }
     if constexpr (OUT == ZEN_DT_S8) {
@@ -302,25 +312,25 @@ __device__ __forceinline__ uint32_t requant_i8_step(const uint32_t (&r)[GEMM_CW]
       const uint32_t t0 = r[j] + 0x4B400000u;  // bits of the float 1.5 * 2^23 + acc while |acc| < 2^22
       const uint32_t t1 = r[j + 1] + 0x4B400000u;
       span |= (t0 ^ 0x4B000000u) | (t1 ^ 0x4B000000u);  // any bit >= 23 set: acc outside that range
-      const float2 a = __fadd2_rn(make_float2(__uint_as_float(t0), __uint_as_float(t1)), neg_magic);  // == float(acc), exact
+      const float2 a = f2add(make_float2(__uint_as_float(t0), __uint_as_float(t1)), neg_magic);  // == float(acc), exact
       const float2 ss = h ? make_float2(s4.z, s4.w) : make_float2(s4.x, s4.y);
       const float2 bb = h ? make_float2(b4.z, b4.w) : make_float2(b4.x, b4.y);
-      float2 g = __fadd2_rn(__fmul2_rn(__fmul2_rn(a, xs2), ss), bb);  // == zen_det_dequant
+      float2 g = f2mul_then_add(f2mul(a, xs2), ss, bb);  // == zen_det_dequant (product rounded before the bias add)
       if constexpr (ACT == ZEN_ACT_GELU) {
         // gelu_fast on both halves: x / (1 + 2^(v * c)), v = x (1 + 0.044715 x^2)
-        const float2 x2 = __fmul2_rn(g, g);
-        const float2 wv = __ffma2_rn(make_float2(0.044715f, 0.044715f), x2, make_float2(1.0f, 1.0f));
-        const float2 v = __fmul2_rn(g, wv);
-        const float2 arg = __fmul2_rn(v, make_float2(-2.302208198144325f, -2.302208198144325f));
-        const float2 den = __fadd2_rn(make_float2(1.0f, 1.0f), make_float2(ex2_approx(arg.x), ex2_approx(arg.y)));
-        g = __fmul2_rn(g, make_float2(rcp_approx(den.x), rcp_approx(den.y)));
+        const float2 x2 = f2mul(g, g);
+        const float2 wv = f2fma(make_float2(0.044715f, 0.044715f), x2, make_float2(1.0f, 1.0f));
+        const float2 v = f2mul(g, wv);
+        const float2 arg = f2mul(v, make_float2(-2.302208198144325f, -2.302208198144325f));
+        const float2 den = f2add(make_float2(1.0f, 1.0f), make_float2(ex2_approx(arg.x), ex2_approx(arg.y)));
+        g = f2mul(g, make_float2(rcp_approx(den.x), rcp_approx(den.y)));
       }
       if constexpr (ACT == ZEN_ACT_RELU) g = make_float2(fmaxf(g.x, 0.0f), fmaxf(g.y, 0.0f));
-      const float2 t = __fmul2_rn(g, inv2);
+      const float2 t = f2mul(g, inv2);
       // NaN -> -128, as in the exact definition
       const float2 tc = make_float2(fminf(fmaxf(t.x, -128.0f), 127.0f), fminf(fmaxf(t.y, -128.0f), 127.0f));
-      const float2 m = __fadd2_rn(tc, pos_magic);  // low mantissa byte == int8 bits of rint(tc)
-      const float2 d = __ffma2_rn(__fadd2_rn(m, neg_magic), make_float2(-1.0f, -1.0f), tc);  // tc - rint(tc), exact
+      const float2 m = f2add(tc, pos_magic);  // low mantissa byte == int8 bits of rint(tc)
+      const float2 d = f2fma(f2add(m, neg_magic), make_float2(-1.0f, -1.0f), tc);  // tc - rint(tc), exact
       // |tc - rint(tc)| close to 0.5 <=> close to a rounding boundary (a clamped value has distance 0)
       if (fmaf(fabsf(tc.x), 4e-6f, fabsf(d.x)) > 0.5f - 2e-6f) risky |= 1u << j;
       if (fmaf(fabsf(tc.y), 4e-6f, fabsf(d.y)) > 0.5f - 2e-6f) risky |= 1u << (j + 1);
@@ -554,15 +564,33 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const float inv_scale = ZEN_DIV(1.0f, p.out_scale);
       int acc = 0;
       uint32_t acc_phase = 0;
+      // Per-column scale and bias of the slab: lane l holds columns l and l + 32.  The values of the
+      // next tile are fetched while the current tile's steps run, so that no tile starts on a global load.
+      auto fetch_cols = [&](int tile, float (&sv)[2], float (&bv)[2]) {
+        const int nn = (tile / p.tiles_m) * BN + sub * 64;
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int col = nn + lane + 32 * u;
+          // predicated loads with no dependent instruction behind them: the warp issues in order and
+          // would otherwise sit on the load until it returns
+          sv[u] = 1.0f;
+          bv[u] = 0.0f;
+          if (p.w_scale != nullptr && col < p.N) sv[u] = __ldg(p.w_scale + col);
+          if (p.bias != nullptr && col < p.N) bv[u] = __ldg(p.bias + col);
+        }
+      };
+      float sv[2] = {1.0f, 1.0f}, bv[2] = {0.0f, 0.0f};
+      if (int(blockIdx.x) < num_tiles) fetch_cols(blockIdx.x, sv, bv);
       for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
         const int m0 = (tile % p.tiles_m) * GEMM_BM;
         const int n0 = (tile / p.tiles_m) * BN + sub * 64;
         __syncwarp();
-        for (int i = lane; i < 64; i += 32) {
-          const int col = n0 + i;
-          s_scale[i] = (p.w_scale != nullptr && col < p.N) ? __ldg(p.w_scale + col) : 1.0f;
-          s_bias[i] = (p.bias != nullptr && col < p.N) ? __ldg(p.bias + col) : 0.0f;
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          s_scale[lane + 32 * u] = sv[u];
+          s_bias[lane + 32 * u] = bv[u];
         }
+        if (tile + int(gridDim.x) < num_tiles) fetch_cols(tile + gridDim.x, sv, bv);
         if (staged) {
           if (lane == 0) tma_store_wait_read();  // the previous tile's store has finished reading the block
         }

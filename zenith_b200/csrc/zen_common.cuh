@@ -291,6 +291,43 @@ __device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t (&r
       : "memory");
 }
 
+// ---------------------------------------------------------------------------
+// Packed fp32x2 arithmetic of sm_100: two individually rounded (RN) operations in one instruction.
+// CAUTION: a packed multiply whose only use is a packed add comes back as ONE fused multiply-add,
+// even when both are written mul.rn.f32x2 / add.rn.f32x2 (measured: the last bit of a bit-exact
+// epilogue changed).  Where a product must be rounded before it is added to, do the add with the
+// scalar __fadd_rn on the two halves.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float2 f2mul(float2 a, float2 b) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "mul.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+__device__ __forceinline__ float2 f2add(float2 a, float2 b) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "add.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+__device__ __forceinline__ float2 f2fma(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
+      "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+  return d;
+}
+// (a * b) rounded, then + c rounded: the product is never fused into the sum
+__device__ __forceinline__ float2 f2mul_then_add(float2 a, float2 b, float2 c) {
+  const float2 p = f2mul(a, b);
+  return make_float2(__fadd_rn(p.x, c.x), __fadd_rn(p.y, c.y));
+}
+
 // 32 lanes x one 32-bit column.
 __device__ __forceinline__ void tmem_ld_32x1(uint32_t taddr, uint32_t& r) {
   asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(r) : "r"(taddr) : "memory");
