@@ -194,6 +194,24 @@ int zen_flash_attention_f16(const void* q, const void* k, const void* v, void* o
 int zen_convert_f32_to_f16(const float* x, void* y, int64_t n, void* stream);
 int zen_convert_f16_to_f32(const void* x, float* y, int64_t n, void* stream);
 
+/* Calibration reductions on the device (a calibration pass then needs no host read-back per tensor).
+ *
+ * zen_minmax_*: running range of an activation tensor: minmax[0] = min(minmax[0], min x),
+ *   minmax[1] = max(minmax[1], max x); minmax is fp32[2] in device memory, initialised by the caller
+ *   (+inf, -inf); NaNs are skipped.  Two launches, no atomics; `workspace` (device, 8-byte aligned) must
+ *   hold zen_minmax_workspace_bytes().  Replaces TensorStats.update (zenith/optimization/quantization.py:
+ *   69-72) and the min / max observer kernels (core/src/qat_cuda.cu:146-227).
+ * zen_absmax_rows_f32: out[r] = max_c |w[r, c]|, the per-output-channel observer
+ *   (zenith/optimization/qat.py:195-199).
+ * zen_quantize_rows_f32: q[r, c] = clamp(round(w[r, c] / scale[r]), -128, 127), per-channel int8 weights
+ *   (the int8 form of core/src/qat_cuda.cu:90-114). */
+size_t zen_minmax_workspace_bytes(void);
+int zen_minmax_f32(const float* x, int64_t n, float* minmax, void* workspace, size_t workspace_bytes, void* stream);
+int zen_minmax_f16(const void* x, int64_t n, float* minmax, void* workspace, size_t workspace_bytes, void* stream);
+int zen_absmax_rows_f32(const float* w, int rows, int cols, int64_t ld, float* out, void* stream);
+int zen_quantize_rows_f32(const float* w, const float* scale, int rows, int cols, int64_t ldw, int8_t* q, int64_t ldq,
+                          int round_mode, void* stream);
+
 /* out[t,:] = LayerNorm(word[ids[t]] + pos[t % seq] + type[type_ids[t]]) in fp16, plus optional
  * int8 copy.  ids/type_ids int32 [tokens]; type_ids may be NULL (row 0 of the type table).
  * core/src/transformer_kernels.cu:236-262 (embedding_f32: word-table gather only). */

@@ -48,9 +48,15 @@ SIGNATURES = {
     "zen_flash_attention_f16": [_p, _p, _p, _p, _p, _f, _i, _i, _i, _i] + [_i64] * 12 + [_p, _i, _f, _p],
     "zen_convert_f32_to_f16": [_p, _p, _i64, _p],
     "zen_convert_f16_to_f32": [_p, _p, _i64, _p],
+    "zen_minmax_workspace_bytes": [],
+    "zen_minmax_f32": [_p, _i64, _p, _p, C.c_size_t, _p],
+    "zen_minmax_f16": [_p, _i64, _p, _p, C.c_size_t, _p],
+    "zen_absmax_rows_f32": [_p, _i, _i, _i64, _p, _p],
+    "zen_quantize_rows_f32": [_p, _p, _i, _i, _i64, _p, _i64, _i, _p],
     "zen_embed_layernorm_f16": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _f, _i, _i, _i, _i, _i, _f, _p],
 }
-_RESTYPES = {"zen_status_string": C.c_char_p, "zen_matmul_f32_workspace_bytes": C.c_size_t}
+_RESTYPES = {"zen_status_string": C.c_char_p, "zen_matmul_f32_workspace_bytes": C.c_size_t,
+             "zen_minmax_workspace_bytes": C.c_size_t}
 
 _lib = None
 

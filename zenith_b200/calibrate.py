@@ -41,12 +41,35 @@ def activation_scales_from_ranges(ranges: dict, n_layers: int) -> list:
 
 
 def calibrate(cfg: EncoderConfig, params: dict, batches, device="cuda:0") -> Int8Scales:
-    """``batches``: iterable of ``(ids [B,S] integer tensor, kv_lens [B] int32 tensor or None)``."""
+    """``batches``: iterable of ``(ids [B,S] integer tensor, kv_lens [B] int32 tensor or None)``.
+
+    The activation ranges accumulate on the device (``ops.RangeObserver``: running min / max, the statistic of
+    ``TensorStats.update``) over all batches and are read back once; min / max select among the inputs, so
+    the scales are those the per-batch host observers would give."""
     enc = Fp16Encoder(cfg, params, device)
-    ranges = {p: [[] for _ in range(cfg.layers)] for p in ACT_POINTS}
+    observers = enc.make_observers()
     for ids, kv_lens in batches:
-        taps = enc.forward_with_taps(ids, kv_lens)
-        for p in ACT_POINTS:
-            for li, mm in enumerate(taps[p]):
-                ranges[p][li].append(mm)
+        enc.forward_with_taps(ids, kv_lens, observers)
+    ranges = {p: [[observers[p][li].range()] for li in range(cfg.layers)] for p in ACT_POINTS}
     return Int8Scales(act=activation_scales_from_ranges(ranges, cfg.layers), weights=quantize_weights(params))
+
+
+def quantize_weights_on_device(params: dict, device="cuda:0") -> list:
+    """``quantize_weights`` with the observer and the conversion on the device (``ops.absmax_rows``,
+    ``ops.quantize_rows``): same int8 weights and scales, bit for bit (symmetric per-output-channel,
+    ``scale = absmax / 127.5`` floored at 1e-8, zenith/optimization/qat.py:222-228)."""
+    import torch
+
+    from . import ops
+
+    out = []
+    for lp in params["layers"]:
+        layer = {}
+        for k in LAYER_WEIGHTS:
+            w = torch.as_tensor(lp[k], dtype=torch.float32).to(device).contiguous()
+            peak = ops.absmax_rows(w)
+            # tensor / tensor: a true fp32 division (torch turns a Python-scalar divisor into a reciprocal multiply)
+            scale = torch.clamp_min(peak / torch.full_like(peak, 127.5), 1e-8)
+            layer[k] = (ops.quantize_rows(w, scale).cpu().numpy(), scale.cpu().numpy())
+        out.append(layer)
+    return out

@@ -49,6 +49,7 @@ __device__ __forceinline__ void st_cluster_f32x2(uint32_t cluster_addr, float a,
 __device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_bar_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar_addr) : "memory");
 }
+__device__ __forceinline__ void fence_acq_rel_cluster() { asm volatile("fence.acq_rel.cluster;" ::: "memory"); }
 __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -158,7 +159,7 @@ gemm_i8_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     for (int i = 0; i < 2; ++i) {
       mbar_init(&tfull_bar[i], 1);
       mbar_init(&tempty_bar[i], GEMM_EPI_WARPS * 32);
-      mbar_init(&stats_bar[i], LN_CLUSTER * 128);  // one arrival per row from each CTA of the cluster
+      mbar_init(&stats_bar[i], LN_CLUSTER * 4);  // one arrival per row-owning warp of each CTA of the cluster
     }
     mbar_init(slab_bar, EPI_ACTIVE);
     for (int i = 0; i < SLABS * 4; ++i) mbar_init(&res_bar[i], 1);
@@ -356,9 +357,14 @@ gemm_i8_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           const uint32_t slot = smem_u32(&xstats[(par * LN_CLUSTER + int(rank)) * 128 + r]);
           const uint32_t bar = smem_u32(&stats_bar[par]);
 #pragma unroll
-          for (uint32_t dst = 0; dst < LN_CLUSTER; ++dst) {
-            st_cluster_f32x2(map_to_cta(slot, dst), mu, q2);
-            mbar_arrive_remote(map_to_cta(bar, dst));
+          for (uint32_t dst = 0; dst < LN_CLUSTER; ++dst) st_cluster_f32x2(map_to_cta(slot, dst), mu, q2);
+          // one release per warp instead of one per row: the 32 lanes' stores are ordered before lane
+          // 0's fence by the warp barrier, the fence before its arrivals
+          __syncwarp();
+          if (lane == 0) {
+            fence_acq_rel_cluster();
+#pragma unroll
+            for (uint32_t dst = 0; dst < LN_CLUSTER; ++dst) mbar_arrive_remote(map_to_cta(bar, dst));
           }
         }
         // ---- all four partials of every row have arrived (phase of stats_bar[par] flips every 2 tiles)

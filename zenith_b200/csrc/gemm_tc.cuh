@@ -601,7 +601,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const bool row_ok = row < p.M;
         const uint32_t tacc = tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * BN + sub * 64);
         // The loop is kept rolled: the step body (above all the GELU + requant one) is large, and
-        // unrolling it made instruction fetch the bottleneck.
+        // unrolling it made instruction fetch the bottleneck.  (Requesting the columns of step i + 1
+        // before working on step i was tried twice and lost both times: 16 more live registers.)
 #pragma unroll 1
         for (int i = 0; i < STEPS; ++i) {
           if (i * GEMM_CW >= slab_cols) break;

@@ -336,22 +336,10 @@ __device__ __forceinline__ void tmem_ld_32x1(uint32_t taddr, uint32_t& r) {
 // ---------------------------------------------------------------------------
 // exact int8 quantisation at low cost
 // ---------------------------------------------------------------------------
-// clamp(round(x / scale), -128, 127), bit-identical to the division-based definition of det_math.h.
-// Nearest-even: the quotient is formed with a reciprocal multiply (inv_scale = 1 / scale, off by at
-// most 2 ulp, i.e. < 2e-5 of an int8 step) and rounded with the 1.5 * 2^23 constant; only when it
-// lies within 1e-3 of a half-integer is the true division evaluated.  Truncation always divides.
-__device__ __forceinline__ int quantize_exact(float x, float scale, float inv_scale, int round_mode) {
-  if (round_mode != 0) return zen_det_round_clamp_i8(ZEN_DIV(x, scale), round_mode);
-  const float t = x * inv_scale;
-  const float tc = fminf(fmaxf(t, -128.0f), 127.0f);  // NaN -> -128, as in the definition
-  const float m = tc + 12582912.0f;
-  int q = __float_as_int(m) - 0x4B400000;
-  const float d = 0.5f - fabsf(tc - (m - 12582912.0f));
-  if (d < 1e-3f && fabsf(t) < 130.0f) q = zen_det_round_clamp_i8(ZEN_DIV(x, scale), 0);
-  return q;
-}
-
-// Branch-free nearest-even form of quantize_exact for N values at once: q[] receives the fast
+// clamp(round(x / scale), -128, 127), bit-identical to the division-based definition of det_math.h:
+// the quotient is formed with a reciprocal multiply (inv_scale = 1 / scale) and rounded with the
+// 1.5 * 2^23 constant; only values next to a rounding boundary are recomputed with the true division.
+// Branch-free nearest-even form for N values at once: q[] receives the fast
 // roundings, the returned mask flags the values that lie too close to a rounding boundary and
 // must be recomputed with the true division.  t = x * (1 / scale) differs from the quotient by less
 // than 2e-7 |t|, so only values within 4e-6 |t| + 2e-6 of a boundary can round differently (a few

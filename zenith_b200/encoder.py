@@ -259,29 +259,41 @@ class Fp16Encoder(_EncoderBase):
                       P(xn), None, 1.0, ROUND_NEAREST_EVEN, T, H, cfg.eps)
             cur ^= 1
 
-    def forward_with_taps(self, ids, kv_lens=None) -> dict:
-        """One pass that also returns, per layer, (min, max) of the four tensors that feed a GEMM in the
-        W8A8 dataflow: layer input ``x``, attention output ``ctx``, post-LN ``h1`` and GELU output
-        ``gelu``.  Cold path used by calibration: runs layer by layer and reads back 8 floats per layer."""
+    def forward_with_taps(self, ids, kv_lens=None, observers: dict | None = None) -> dict | None:
+        """One pass that also observes, per layer, the range of the four tensors that feed a GEMM in the
+        W8A8 dataflow: layer input ``x``, attention output ``ctx``, post-LN ``h1`` and GELU output ``gelu``.
+
+        ``observers``: ``{point: [ops.RangeObserver per layer]}``; the ranges then accumulate on the device
+        over any number of passes and nothing is read back here (returns None).  Without it the pass
+        creates fresh observers and returns ``{point: [(min, max) per layer]}`` of this batch alone.
+        Cold path used by calibration: runs layer by layer."""
         self.set_inputs(ids, kv_lens)
         if len(self._micro) != 1:
             raise RuntimeError("forward_with_taps needs micro_batches == 1")
+        own = observers is None
+        if own:
+            observers = self.make_observers()
         stream = torch.cuda.current_stream().cuda_stream
-        taps = {p: [] for p in ACT_POINTS}
         per_layer = 7
         f, name, args = self._launches[0]
         _capi.check(name, f(*args, stream))
         cur = 0
         for li in range(len(self.layers)):
-            taps["x"].append(torch.aminmax(self.x[cur]))
+            observers["x"][li].observe(self.x[cur])
             for f, name, args in self._launches[1 + li * per_layer: 1 + (li + 1) * per_layer]:
                 _capi.check(name, f(*args, stream))
-            taps["ctx"].append(torch.aminmax(self.ctx))
-            taps["h1"].append(torch.aminmax(self.h1))
-            taps["gelu"].append(torch.aminmax(self.g))
+            observers["ctx"][li].observe(self.ctx)
+            observers["h1"][li].observe(self.h1)
+            observers["gelu"][li].observe(self.g)
             cur ^= 1
         ops.launch_count += len(self._launches)
-        return {p: [(float(lo), float(hi)) for lo, hi in v] for p, v in taps.items()}
+        if not own:
+            return None
+        return {p: [o.range() for o in v] for p, v in observers.items()}
+
+    def make_observers(self) -> dict:
+        """``{point: [RangeObserver per layer]}`` for ``forward_with_taps``."""
+        return {p: [ops.RangeObserver(self.device) for _ in self.layers] for p in ACT_POINTS}
 
 
 @dataclass

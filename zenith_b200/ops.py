@@ -26,13 +26,15 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
-def _require(t: torch.Tensor, name: str, dtype=None, ndim=None) -> None:
+def _require(t: torch.Tensor, name: str, dtype=None, ndim=None, rows_may_be_strided: bool = False) -> None:
     if not isinstance(t, torch.Tensor) or not t.is_cuda:
         raise RuntimeError(f"{name} must be a CUDA tensor")
     if dtype is not None and t.dtype != dtype:
         raise RuntimeError(f"{name} must be {dtype}, got {t.dtype}")
     if ndim is not None and t.dim() != ndim:
         raise RuntimeError(f"{name} must be {ndim}-D, got {t.dim()}-D")
+    if rows_may_be_strided and t.dim() == 2 and (t.shape[1] <= 1 or t.stride(1) == 1) and t.stride(0) >= t.shape[1]:
+        return
     if not t.is_contiguous():
         raise RuntimeError(f"{name} must be contiguous")
 
@@ -311,6 +313,52 @@ def dequantize(q, scale: float, zero_point: int = 0):
     if q.numel():
         _call("zen_dequantize_f32", q.data_ptr(), x.data_ptr(), q.numel(), float(scale), int(zero_point), _stream())
     return x
+
+
+class RangeObserver:
+    """Running (min, max) of every tensor shown to it, kept on the device: two floats and no host
+    read-back until ``range()`` is called.  Same statistic as ``TensorStats.update``
+    (zenith/optimization/quantization.py:69-72); NaNs are skipped."""
+
+    def __init__(self, device):
+        self.minmax = torch.tensor([float("inf"), float("-inf")], dtype=torch.float32, device=device)
+        nbytes = _capi.lib().zen_minmax_workspace_bytes()
+        self._workspace = torch.empty(nbytes, dtype=torch.uint8, device=device)
+
+    def observe(self, x: torch.Tensor) -> None:
+        if not x.is_cuda or x.dtype not in (torch.float16, torch.float32) or not x.is_contiguous():
+            raise RuntimeError("RangeObserver.observe wants a contiguous CUDA fp16 / fp32 tensor")
+        fn = "zen_minmax_f16" if x.dtype == torch.float16 else "zen_minmax_f32"
+        _call(fn, x.data_ptr(), x.numel(), self.minmax.data_ptr(), self._workspace.data_ptr(), self._workspace.numel(),
+              _stream())
+        launch_count_add(1)  # two launches in all: _call counted the first
+
+    def range(self) -> tuple:
+        lo, hi = self.minmax.tolist()
+        return lo, hi
+
+
+def absmax_rows(w):
+    """``max_c |w[r, c]|`` per row of a CUDA fp32 matrix: the per-output-channel weight observer
+    (zenith/optimization/qat.py:195-199)."""
+    _require(w, "w", torch.float32, 2, rows_may_be_strided=True)
+    out = torch.empty(w.shape[0], dtype=torch.float32, device=w.device)
+    if w.shape[0]:
+        _call("zen_absmax_rows_f32", w.data_ptr(), w.shape[0], w.shape[1], w.stride(0), out.data_ptr(), _stream())
+    return out
+
+
+def quantize_rows(w, scale, *, round="nearest_even"):
+    """``clamp(round(w[r, c] / scale[r]), -128, 127)`` as int8: per-output-channel weight conversion."""
+    _require(w, "w", torch.float32, 2, rows_may_be_strided=True)
+    _require(scale, "scale", torch.float32, 1)
+    if scale.numel() != w.shape[0]:
+        raise RuntimeError("scale must have one entry per row")
+    q = torch.empty(w.shape, dtype=torch.int8, device=w.device)
+    if w.numel():
+        _call("zen_quantize_rows_f32", w.data_ptr(), scale.data_ptr(), w.shape[0], w.shape[1], w.stride(0), q.data_ptr(),
+              q.stride(0), _ROUND[round], _stream())
+    return q
 
 
 def to_fp16(x):
