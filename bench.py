@@ -259,7 +259,7 @@ def run_ours(args) -> None:
     # lengths from pinned host memory and its hidden states back to pinned host memory; the device->host
     # copy of step i runs on a copy stream while step i + 1 computes, and the host waits for step i - 1's
     # result before it queues step i + 1 (the loop a server would run).
-    pipe = HostPipeline(enc, BATCH, SEQ, after_replay=(gatherer.gather if gatherer is not None else None))
+    pipe = HostPipeline(enc, BATCH, SEQ, gatherer=gatherer)
 
     def timed_e2e(steps):
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -272,6 +272,7 @@ def run_ours(args) -> None:
                 pipe.result(prev)
             prev = t
         pipe.result(prev)
+        pipe.drain()  # the last gathers are ordered before the end event
         e.record()
         barrier()
         t = torch.tensor([s.elapsed_time(e)], dtype=torch.float64, device=dev)

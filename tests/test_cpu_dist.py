@@ -46,7 +46,12 @@ def _worker(rank, world, port, gb, fail_rank, out):
         if fail_rank is None:
             full = g.gather(local)
             want = torch.arange(gb * seq, dtype=torch.float32)[:, None] + torch.zeros(hidden)[None, :]
-            out[rank] = bool(torch.equal(full, want))
+            ok = bool(torch.equal(full, want))
+            # two gathers in flight in their own result buffers
+            a = g.gather_async(local, 0)
+            b = g.gather_async(local + 1, 1)
+            ok = ok and bool(torch.equal(a.wait(), want)) and bool(torch.equal(b.wait(), want + 1))
+            out[rank] = ok
         else:
             out[rank] = "skipped"  # the host learns of the peer's failure before launching the collective
     finally:

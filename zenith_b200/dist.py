@@ -53,6 +53,7 @@ class OutputGatherer:
         self.seq, self.hidden = seq, hidden
         self.bounds = [shard_bounds(global_batch, self.world, r) for r in range(self.world)]
         self.full = torch.empty((global_batch * seq, hidden), dtype=dtype, device=device)
+        self._slots: list = []  # result buffers of gather_async
         self.even = len({c for _, c in self.bounds}) == 1
         self.views = [self.full[s * seq:(s + c) * seq] for s, c in self.bounds]
         # collectives need equal contributions: uneven shards travel padded to the largest shard
@@ -75,3 +76,38 @@ class OutputGatherer:
             for r, view in enumerate(self.views):
                 view.copy_(self.padded[r * self.max_rows:r * self.max_rows + view.shape[0]])
         return self.full
+
+    def gather_async(self, local: torch.Tensor, slot: int = 0) -> "PendingGather":
+        """Start the gather of ``local`` into the ``slot``-th result buffer (allocated on first use) without
+        making the calling stream wait for it: the collective runs on the backend's own stream, beside
+        whatever the caller launches next.  ``local`` must stay untouched until ``wait()`` has been called
+        on the returned object.  Uneven shards take the blocking path."""
+        while len(self._slots) <= slot:
+            self._slots.append(torch.empty_like(self.full))
+        out = self._slots[slot]
+        start, count = self.bounds[self.rank]
+        if tuple(local.shape) != (count * self.seq, self.hidden):
+            raise RuntimeError(f"rank {self.rank}: expected {(count * self.seq, self.hidden)}, got {tuple(local.shape)}")
+        if self.world == 1:
+            out.copy_(local)
+            return PendingGather(None, out)
+        if not self.even:
+            out.copy_(self.gather(local))
+            return PendingGather(None, out)
+        work = dist.all_gather_into_tensor(out, local.contiguous(), group=self.group, async_op=True)
+        return PendingGather(work, out)
+
+
+class PendingGather:
+    """A gather in flight; ``wait()`` orders the calling stream (the host, for CPU backends) after it and
+    returns the gathered tensor."""
+
+    def __init__(self, work, out: torch.Tensor):
+        self._work = work
+        self.out = out
+
+    def wait(self) -> torch.Tensor:
+        if self._work is not None:
+            self._work.wait()
+            self._work = None
+        return self.out

@@ -16,16 +16,17 @@ class HostPipeline:
     """``submit`` a batch, get a ticket; ``result(ticket)`` blocks until that batch's hidden states are
     in host memory and returns them (a pinned buffer that the ticket after next will reuse)."""
 
-    def __init__(self, encoder, batch: int, seq: int, depth: int = 2, after_replay=None):
+    def __init__(self, encoder, batch: int, seq: int, depth: int = 2, gatherer=None):
         """``encoder``: an ``Int8Encoder`` / ``Fp16Encoder``; it is captured for (batch, seq) here.
-        ``after_replay``: optional callable run on the compute stream after each pass (e.g. the
-        multi-GPU gather)."""
+        ``gatherer``: optional ``dist.OutputGatherer``; every batch's hidden states are then also gathered
+        across the ranks (``gathered(ticket)``), on the collective's own stream, beside the next batch."""
         if depth < 2:
             raise ValueError("depth must be at least 2")
         self.enc = encoder
         encoder.capture(batch, seq)
         self.depth = depth
-        self.after_replay = after_replay
+        self.gatherer = gatherer
+        self._gathers = [None] * depth
         self.copy_stream = torch.cuda.Stream(device=encoder.device)
         self.dev_out = [torch.empty_like(encoder.out) for _ in range(depth)]
         self.host_out = [torch.empty(encoder.out.shape, dtype=encoder.out.dtype).pin_memory() for _ in range(depth)]
@@ -40,12 +41,14 @@ class HostPipeline:
         main = torch.cuda.current_stream(self.enc.device)
         if self._copied[slot] is not None:
             main.wait_event(self._copied[slot])  # the slot's device buffer is free again
+        if self._gathers[slot] is not None:
+            self._gathers[slot].wait()
         self.enc.set_inputs(ids_host, kv_lens_host)  # host -> device, asynchronous on the compute stream
         self.enc.replay()
-        if self.after_replay is not None:
-            self.after_replay(self.enc.out)
         # the encoder's output buffer is overwritten by the first kernel of the next pass: park the result
         self.dev_out[slot].copy_(self.enc.out, non_blocking=True)
+        if self.gatherer is not None:
+            self._gathers[slot] = self.gatherer.gather_async(self.dev_out[slot], slot)
         ready = torch.cuda.Event()
         ready.record(main)
         self.copy_stream.wait_event(ready)
@@ -64,8 +67,20 @@ class HostPipeline:
         self._copied[slot].synchronize()
         return self.host_out[slot]
 
+    def gathered(self, ticket: int) -> torch.Tensor:
+        """All ranks' hidden states of ``ticket`` (device tensor; the current stream is ordered after the gather)."""
+        if self.gatherer is None:
+            raise RuntimeError("no gatherer was given")
+        if not 0 <= ticket < self._count or ticket < self._count - self.depth:
+            raise ValueError("ticket is not in flight")
+        return self._gathers[ticket % self.depth].wait()
+
     def drain(self) -> None:
-        """Block until every queued batch has reached host memory."""
+        """Block until every queued batch has reached host memory (and every gather has been ordered
+        before the current stream)."""
+        for g in self._gathers:
+            if g is not None:
+                g.wait()
         for ev in self._copied:
             if ev is not None:
                 ev.synchronize()
