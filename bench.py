@@ -142,6 +142,28 @@ def cpu_executor(sample_seqs: int, steps: int, warmup: int) -> dict:
             f"(numpy fake-quant + fp32 BLAS matmul, all host threads)"}
 
 
+_RESULT_FD = None
+
+
+def quiet_stdout() -> None:
+    """Route everything libraries write to stdout (NCCL prints its version line there) to stderr and keep the
+    real stdout for the one JSON line."""
+    global _RESULT_FD
+    if _RESULT_FD is None:
+        sys.stdout.flush()
+        _RESULT_FD = os.dup(1)
+        os.dup2(2, 1)
+
+
+def emit(line: dict) -> None:
+    data = (json.dumps(line) + "\n").encode()
+    if _RESULT_FD is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_RESULT_FD, data)
+
+
 def run_reference_arm(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -158,7 +180,7 @@ def run_reference_arm(args) -> None:
         "e2e": {"value": r["seq_per_s"], "unit": "sequences/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 # ------------------------------------------------------------------------------------------------
@@ -359,12 +381,13 @@ def run_ours(args) -> None:
         except Exception as exc:  # the CPU leg must never take the GPU numbers down with it
             line["cpu_baseline"] = {"value": None, "unit": "sequences/s", "cores": os.cpu_count(), "kind": "port",
                                     "sample": f"failed: {exc}"}
-    print(json.dumps(line), flush=True)
+    emit(line)
     if world > 1:
         dist.destroy_process_group()
 
 
 def main() -> None:
+    quiet_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
