@@ -15,7 +15,8 @@ states.  Rank 0 prints ONE JSON line.
 `e2e`        the same through the public host API (zenith_b200.serve.HostPipeline) with HOST buffers: every
              step copies pinned ids / lengths to the device and the fp16 hidden states back to pinned host
              memory inside the timed region; the copy back of step i overlaps the compute of step i + 1.
-`roofline`   the int8 tcgen05 GEMM (4 shapes x 12 layers per step), timed alone with CUDA events.
+`roofline`   the int8 tcgen05 GEMM family (4 shapes x 12 layers per step): average launch durations measured with
+             CUDA events inside a graph of 12 launches per shape, as the step runs them.
 `cpu_baseline` the CPU restatement of the reference's quantized executor (fake-quant + fp32 BLAS
              matmul), timed on this host's cores on a bounded sample.
 `--impl reference` times that CPU executor alone, on the same workload definition.
@@ -187,36 +188,40 @@ def run_reference_arm(args) -> None:
 # GPU arm
 # ------------------------------------------------------------------------------------------------
 def time_gemm_shapes(torch, ops, dev, flush) -> dict:
-    """The four int8 GEMM launches of one encoder layer, each timed alone with CUDA events (L2 flushed before
-    every launch), with the epilogue it has in the encoder: QKV (-> fp16), attention-out (+ residual +
-    LayerNorm, cluster kernel), FFN1 (+ GELU + requant), FFN2 (+ residual + LayerNorm)."""
-    T, H, F = BATCH * SEQ, 768, 3072
+    """The four int8 GEMM launches of one encoder layer with the epilogue each has in the encoder: QKV (-> fp16),
+    attention-out (+ residual + LayerNorm, cluster kernel), FFN1 (+ GELU + requant), FFN2 (+ residual +
+    LayerNorm), timed with CUDA events in two ways:
+
+    * ``in_step``: as the step runs them - a CUDA graph of 12 back-to-back launches of the shape, one per layer,
+      each with its own weight matrix, L2 flushed before every replay (so the weights come from HBM, as in the
+      step); average launch duration = replay time / 12.  `roofline.achieved` uses these.
+    * ``cold``: one launch alone, L2 flushed, launch latency included (the upper bound a profiler also sees).
+    """
+    T, H, F, LAYERS = BATCH * SEQ, 768, 3072, 12
 
     def plain(N, K, **kw):
         x = torch.randint(-128, 128, (T, K), dtype=torch.int8, device=dev)
-        w = torch.randint(-128, 128, (N, K), dtype=torch.int8, device=dev)
+        ws_ = [torch.randint(-128, 128, (N, K), dtype=torch.int8, device=dev) for _ in range(LAYERS)]
         ws, b = torch.rand(N, device=dev) * 1e-3, torch.randn(N, device=dev)
         out = torch.empty((T, N), dtype=kw["out_dtype"], device=dev)
-        return lambda: ops.linear_int8(x, w, 0.02, ws, b, out=out, **kw)
+        return lambda i: ops.linear_int8(x, ws_[i], 0.02, ws, b, out=out, **kw)
 
     def with_ln(K):
         x = torch.randint(-128, 128, (T, K), dtype=torch.int8, device=dev)
-        w = torch.randint(-128, 128, (H, K), dtype=torch.int8, device=dev)
+        ws_ = [torch.randint(-128, 128, (H, K), dtype=torch.int8, device=dev) for _ in range(LAYERS)]
         ws, b = torch.rand(H, device=dev) * 1e-3, torch.randn(H, device=dev)
         res = torch.randn(T, H, device=dev, dtype=torch.float16)
         g, be = torch.ones(H, device=dev, dtype=torch.float16), torch.zeros(H, device=dev, dtype=torch.float16)
-        return lambda: ops.linear_int8_add_layernorm(x, w, 0.02, ws, b, res, g, be, 1e-12, out_scale=0.03)
+        return lambda i: ops.linear_int8_add_layernorm(x, ws_[i], 0.02, ws, b, res, g, be, 1e-12, out_scale=0.03)
 
     shapes = [("qkv", 3 * H, H, plain(3 * H, H, out_dtype=torch.float16)),
               ("attn_out_add_layernorm", H, H, with_ln(H)),
               ("ffn1_gelu_requant", F, H, plain(F, H, act="gelu", out_dtype=torch.int8, out_scale=0.05)),
               ("ffn2_add_layernorm", H, F, with_ln(F))]
-    per_shape, tot_ops, tot_us = {}, 0.0, 0.0
-    for name, N, K, fn in shapes:
-        for _ in range(3):
-            fn()
+
+    def event_us(fn, reps):
         us = []
-        for _ in range(10):
+        for _ in range(reps):
             flush()
             s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             s.record()
@@ -224,10 +229,30 @@ def time_gemm_shapes(torch, ops, dev, flush) -> dict:
             e.record()
             e.synchronize()
             us.append(s.elapsed_time(e) * 1e3)
-        t = statistics.median(us)
-        per_shape[name] = {"us": round(t, 2), "tops": round(2.0 * T * N * K / t / 1e6, 1)}
-        tot_ops += 2.0 * T * N * K
-        tot_us += t
+        return statistics.median(us)
+
+    per_shape, tot_ops, tot_us = {}, 0.0, 0.0
+    for name, N, K, fn in shapes:
+        def all_layers():
+            for i in range(LAYERS):
+                fn(i)
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            all_layers()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            all_layers()
+        for _ in range(3):
+            graph.replay()
+        in_step = event_us(graph.replay, 9) / LAYERS
+        cold = event_us(lambda: fn(0), 9)
+        ops_ = 2.0 * T * N * K
+        per_shape[name] = {"us": round(in_step, 2), "tops": round(ops_ / in_step / 1e6, 1), "cold_us": round(cold, 2)}
+        tot_ops += ops_
+        tot_us += in_step
     return {"per_shape": per_shape, "ops_per_layer": tot_ops, "us_per_layer": tot_us}
 
 
@@ -373,7 +398,11 @@ def run_ours(args) -> None:
             # DRAM bytes of the same four launches from profiles/gemm_i8_bert_base_layer_shapes.md (ncu): reads
             # only and equal to the operand (+ residual) bytes; the outputs are still in L2 when each kernel ends
             "traffic": 42.0e6, "traffic_unit": "bytes per layer (4 launches)",
-            "algorithmic_bytes": 92.1e6, "per_shape": g["per_shape"]}
+            "algorithmic_bytes": 92.1e6, "per_shape": g["per_shape"],
+            "gemm_share_of_step": 12.0 * g["us_per_layer"] / (total_ms / K * 1e3),
+            "duration": "average launch duration inside a CUDA graph of 12 back-to-back launches of the shape (one per "
+                        "layer, 12 different weight matrices, L2 flushed before every replay), CUDA events; cold_us: one "
+                        "launch alone after an L2 flush, launch latency included"}
         try:
             r = cpu_executor(8, 3, 1)
             line["cpu_baseline"] = {"value": r["seq_per_s"], "unit": "sequences/s", "cores": r["cores"], "kind": "port",
