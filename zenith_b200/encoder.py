@@ -119,8 +119,11 @@ class _EncoderBase:
         self._shape = (B, S)
         self._graph = None
         d = self.device
-        self.ids = torch.zeros(B * S, dtype=torch.int32, device=d)
-        self.kv_lens = torch.full((B,), S, dtype=torch.int32, device=d)
+        # token ids and key lengths share one allocation, so that a host can feed both with one copy
+        self.inputs = torch.zeros(B * S + B, dtype=torch.int32, device=d)
+        self.ids = self.inputs[:B * S]
+        self.kv_lens = self.inputs[B * S:]
+        self.kv_lens.fill_(S)
         self._alloc(B, S)
         # Sequences are independent through the whole encoder, so the batch may be cut into micro-batches
         # whose launch sequences run side by side (separate streams / graph branches): the fill and
@@ -172,6 +175,13 @@ class _EncoderBase:
             self.kv_lens.copy_(kv_lens, non_blocking=True)
         else:
             self.kv_lens.fill_(S)
+
+    def set_inputs_packed(self, packed) -> None:
+        """One copy for both inputs: ``packed`` is int32 ``[B*S + B]`` = token ids followed by key lengths, laid
+        out like ``self.inputs`` (any device; a pinned host tensor makes the copy asynchronous)."""
+        if self._shape is None or packed.numel() != self.inputs.numel() or packed.dtype != torch.int32:
+            raise RuntimeError("packed inputs must be int32 [B*S + B] for the prepared shape")
+        self.inputs.copy_(packed, non_blocking=True)
 
     def forward(self, ids, kv_lens=None) -> torch.Tensor:
         """Hidden states ``[B*S, hidden]`` fp16 (a static buffer, overwritten by the next call)."""

@@ -30,7 +30,12 @@ class HostPipeline:
         self.copy_stream = torch.cuda.Stream(device=encoder.device)
         self.dev_out = [torch.empty_like(encoder.out) for _ in range(depth)]
         self.host_out = [torch.empty(encoder.out.shape, dtype=encoder.out.dtype).pin_memory() for _ in range(depth)]
+        # ids and key lengths travel as one pinned block (one host->device copy per batch instead of two)
+        self.host_in = [torch.empty(encoder.inputs.numel(), dtype=torch.int32).pin_memory() for _ in range(depth)]
+        self._n_ids = batch * seq
+        self._seq = seq
         self._copied = [None] * depth  # event: the slot's device->host copy has finished
+        self._in_done = [None] * depth  # event: the slot's host->device copy has finished
         self._count = 0
 
     def submit(self, ids_host: torch.Tensor, kv_lens_host: torch.Tensor | None = None) -> int:
@@ -43,7 +48,17 @@ class HostPipeline:
             main.wait_event(self._copied[slot])  # the slot's device buffer is free again
         if self._gathers[slot] is not None:
             self._gathers[slot].wait()
-        self.enc.set_inputs(ids_host, kv_lens_host)  # host -> device, asynchronous on the compute stream
+        staged = self.host_in[slot]
+        if self._in_done[slot] is not None:
+            self._in_done[slot].synchronize()  # the copy that last read this block has run (back-pressure on the host)
+        staged[:self._n_ids].copy_(ids_host.reshape(-1))
+        if kv_lens_host is not None:
+            staged[self._n_ids:].copy_(kv_lens_host)
+        else:
+            staged[self._n_ids:].fill_(self._seq)
+        self.enc.set_inputs_packed(staged)  # host -> device, asynchronous on the compute stream
+        self._in_done[slot] = torch.cuda.Event()
+        self._in_done[slot].record(main)
         self.enc.replay()
         # the encoder's output buffer is overwritten by the first kernel of the next pass: park the result
         self.dev_out[slot].copy_(self.enc.out, non_blocking=True)
