@@ -38,6 +38,24 @@ struct Vec16<__half> {
   }
   // the value a later reader of the stored row will see
   static __device__ __forceinline__ float stored(float v) { return __half2float(__float2half_rn(v)); }
+  // column pairs (for the packed fp32x2 arithmetic of the row kernels)
+  static __device__ __forceinline__ void load2(const __half* p, float2 (&v)[4]) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = __half22float2(h[i]);
+  }
+  // stores the row piece and returns, in `seen`, the values a later reader of it will see
+  static __device__ __forceinline__ void store2(__half* p, const float2 (&v)[4], float2 (&seen)[4]) {
+    uint4 u;
+    __half2* h = reinterpret_cast<__half2*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      h[i] = __floats2half2_rn(v[i].x, v[i].y);
+      seen[i] = __half22float2(h[i]);
+    }
+    *reinterpret_cast<uint4*>(p) = u;
+  }
 };
 template <>
 struct Vec16<float> {
@@ -53,6 +71,16 @@ struct Vec16<float> {
     *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
   }
   static __device__ __forceinline__ float stored(float v) { return v; }
+  static __device__ __forceinline__ void load2(const float* p, float2 (&v)[2]) {
+    const float4 f = *reinterpret_cast<const float4*>(p);
+    v[0] = make_float2(f.x, f.y);
+    v[1] = make_float2(f.z, f.w);
+  }
+  static __device__ __forceinline__ void store2(float* p, const float2 (&v)[2], float2 (&seen)[2]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0].x, v[0].y, v[1].x, v[1].y);
+    seen[0] = v[0];
+    seen[1] = v[1];
+  }
 };
 
 __device__ __forceinline__ float warp_sum(float v) {
@@ -137,49 +165,54 @@ __global__ void __launch_bounds__(ROW_WARPS * 32) ln_warp_kernel(const RowParams
   }
   const T* res = SRC == 1 ? static_cast<const T*>(p.residual) + int64_t(row) * H : nullptr;
 
-  float v[VPL][N];
-  float sum = 0.f;
+  // The row lives in registers as column pairs; sums, deviations and the normalisation run on the
+  // packed fp32x2 instructions (the kernel is bound by instruction issue, not by HBM).
+  constexpr int P = N / 2;
+  float2 v[VPL][P];
+  float2 sum2 = make_float2(0.f, 0.f);
 #pragma unroll
   for (int i = 0; i < VPL; ++i) {
     const int c = (i * 32 + lane) * N;
     if (c < H) {
-      Vec16<T>::load(x + c, v[i]);
+      Vec16<T>::load2(x + c, v[i]);
       if constexpr (SRC == 1) {
-        float r[N];
-        Vec16<T>::load(res + c, r);
+        float2 r[P];
+        Vec16<T>::load2(res + c, r);
 #pragma unroll
-        for (int j = 0; j < N; ++j) v[i][j] += r[j];
+        for (int j = 0; j < P; ++j) v[i][j] = f2add(v[i][j], r[j]);
       }
       if constexpr (SRC == 2) {
-        float r[N];
-        Vec16<T>::load(pos + c, r);
+        float2 r[P];
+        Vec16<T>::load2(pos + c, r);
 #pragma unroll
-        for (int j = 0; j < N; ++j) v[i][j] += r[j];
-        Vec16<T>::load(typ + c, r);
+        for (int j = 0; j < P; ++j) v[i][j] = f2add(v[i][j], r[j]);
+        Vec16<T>::load2(typ + c, r);
 #pragma unroll
-        for (int j = 0; j < N; ++j) v[i][j] += r[j];
+        for (int j = 0; j < P; ++j) v[i][j] = f2add(v[i][j], r[j]);
       }
 #pragma unroll
-      for (int j = 0; j < N; ++j) sum += v[i][j];
+      for (int j = 0; j < P; ++j) sum2 = f2add(sum2, v[i][j]);
     } else {
 #pragma unroll
-      for (int j = 0; j < N; ++j) v[i][j] = 0.f;
+      for (int j = 0; j < P; ++j) v[i][j] = make_float2(0.f, 0.f);
     }
   }
-  const float mean = warp_sum(sum) / float(H);
-  float sq = 0.f;
+  const float mean = warp_sum(sum2.x + sum2.y) / float(H);
+  const float2 nmean = make_float2(-mean, -mean);
+  float2 sq2 = make_float2(0.f, 0.f);
 #pragma unroll
   for (int i = 0; i < VPL; ++i) {
     const int c = (i * 32 + lane) * N;
     if (c < H) {
 #pragma unroll
-      for (int j = 0; j < N; ++j) {
-        const float d = v[i][j] - mean;
-        sq += d * d;
+      for (int j = 0; j < P; ++j) {
+        const float2 d = f2add(v[i][j], nmean);
+        sq2 = f2fma(d, d, sq2);
       }
     }
   }
-  const float rstd = rsqrtf(warp_sum(sq) / float(H) + p.eps);
+  const float rstd = rsqrtf(warp_sum(sq2.x + sq2.y) / float(H) + p.eps);
+  const float2 rstd2 = make_float2(rstd, rstd);
   const float inv_q_scale = ZEN_DIV(1.0f, p.q_scale);
   const T* gamma = static_cast<const T*>(p.gamma);
   const T* beta = static_cast<const T*>(p.beta);
@@ -189,17 +222,21 @@ __global__ void __launch_bounds__(ROW_WARPS * 32) ln_warp_kernel(const RowParams
   for (int i = 0; i < VPL; ++i) {
     const int c = (i * 32 + lane) * N;
     if (c < H) {
-      float g[N], b[N], o[N];
-      Vec16<T>::load(gamma + c, g);
-      Vec16<T>::load(beta + c, b);
+      float2 g[P], b[P], o[P], seen[P];
+      Vec16<T>::load2(gamma + c, g);
+      Vec16<T>::load2(beta + c, b);
 #pragma unroll
-      for (int j = 0; j < N; ++j) o[j] = (v[i][j] - mean) * rstd * g[j] + b[j];
-      Vec16<T>::store(y + c, o);
+      for (int j = 0; j < P; ++j) o[j] = f2fma(f2mul(f2add(v[i][j], nmean), rstd2), g[j], b[j]);
+      Vec16<T>::store2(y + c, o, seen);
       if (yq) {
         // quantize the value that was stored, so that yq == quantize(y) exactly
+        float q[N];
 #pragma unroll
-        for (int j = 0; j < N; ++j) o[j] = Vec16<T>::stored(o[j]);
-        store_q<N>(yq + c, o, p.q_scale, inv_q_scale, p.round_mode);
+        for (int j = 0; j < P; ++j) {
+          q[2 * j] = seen[j].x;
+          q[2 * j + 1] = seen[j].y;
+        }
+        store_q<N>(yq + c, q, p.q_scale, inv_q_scale, p.round_mode);
       }
     }
   }
