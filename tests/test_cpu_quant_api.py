@@ -174,3 +174,21 @@ def test_reexported_names_resolve():  # zenith/optimization/__init__.py:96-118
     for n in ("QATScheme", "ObserverType", "QATConfig", "FakeQuantize", "QATModule", "QATTrainer",
               "prepare_model_for_qat", "convert_qat_to_quantized", "simulate_qat_forward", "measure_qat_error"):
         assert hasattr(zq, n)
+
+
+def test_scale_table_round_trips_through_a_file(tmp_path):
+    from zenith_b200.calibrate import activation_scales_from_ranges, quantize_weights
+    from zenith_b200.encoder import ACT_POINTS, EncoderConfig, Int8Scales, init_params
+
+    cfg = EncoderConfig(layers=2, hidden=64, heads=2, ffn=128, vocab=100, max_pos=16)
+    params = init_params(cfg, 5)
+    ranges = {p: [[(-1.0 - li, 2.0 + i)] for li in range(cfg.layers)] for i, p in enumerate(ACT_POINTS)}
+    scales = Int8Scales(act=activation_scales_from_ranges(ranges, cfg.layers), weights=quantize_weights(params))
+    path = tmp_path / "scales.npz"
+    scales.save(path)
+    back = Int8Scales.load(path)
+    assert back.act == scales.act
+    for a, b in zip(scales.weights, back.weights):
+        assert a.keys() == b.keys()
+        for k in a:
+            assert b[k][0].dtype == np.int8 and np.array_equal(a[k][0], b[k][0]) and np.array_equal(a[k][1], b[k][1])

@@ -313,6 +313,26 @@ class Int8Scales:
     act: list  # [{"x":..,"ctx":..,"h1":..,"gelu":..}] per layer
     weights: list  # [{"wqkv": (int8 [N,K], float32 [N]), ...}] per layer
 
+    def save(self, path) -> None:
+        """One ``.npz``: ``act`` float64 [layers, 4] in ``ACT_POINTS`` order, and per layer and weight the
+        packed int8 matrix (``L{i}.{name}.q``) with its per-output-channel scales (``L{i}.{name}.s``)."""
+        arrays = {"act": np.array([[a[p] for p in ACT_POINTS] for a in self.act], dtype=np.float64)}
+        for li, layer in enumerate(self.weights):
+            for name, (q, sc) in layer.items():
+                arrays[f"L{li}.{name}.q"] = np.asarray(q, dtype=np.int8)
+                arrays[f"L{li}.{name}.s"] = np.asarray(sc, dtype=np.float32)
+        np.savez(path, **arrays)
+
+    @classmethod
+    def load(cls, path) -> "Int8Scales":
+        with np.load(path) as z:
+            act = [{p: float(v) for p, v in zip(ACT_POINTS, row)} for row in z["act"]]
+            weights = []
+            for li in range(len(act)):
+                names = sorted({k.split(".")[1] for k in z.files if k.startswith(f"L{li}.")})
+                weights.append({n: (z[f"L{li}.{n}.q"], z[f"L{li}.{n}.s"]) for n in names})
+        return cls(act=act, weights=weights)
+
 
 class Int8Encoder(_EncoderBase):
     """W8A8 encoder: int8 GEMM operands, int32 accumulation, fp16 residual stream / LayerNorm / softmax."""
