@@ -7,7 +7,7 @@ import pytest
 import torch
 
 import zenith_b200
-from zenith_b200 import registry
+from zenith_b200 import _capi, registry
 
 pytestmark = pytest.mark.gpu
 
@@ -98,3 +98,38 @@ def test_registry_plugin(cuda):
     r = torch.randn(32, 64, device=cuda)
     y = by_op["FusedAddLayerNorm"].kernel_fn(x, r, g, be, 1e-5)
     assert torch.allclose(y, torch.nn.functional.layer_norm(x + r, (64,), g, be, 1e-5), atol=1e-4, rtol=1e-4)
+
+
+def test_fx_rewritten_module_matches_the_original(cuda):
+    """A traced attention + GELU + LayerNorm + Linear-GELU block, rewritten onto the kernels by the FX patterns,
+    computes what the PyTorch original computes (fp16 attention / TF32 GEMM tolerances)."""
+    import torch.fx
+    import torch.nn.functional as F
+
+    from zenith_b200 import fx_patterns as P
+
+    class Block(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.w = torch.nn.Parameter(1 + 0.1 * torch.randn(64))
+            self.b = torch.nn.Parameter(0.1 * torch.randn(64))
+            self.fc = torch.nn.Linear(64, 128)
+
+        def forward(self, q, k, v, mask):
+            a = P.sdpa_pattern(q, k, v)
+            c = P.causal_sdpa_pattern(q, k, v, mask)
+            g = P.gelu_tanh_pattern(a + c)
+            n = P.layernorm_pattern(g, self.w, self.b, 1e-5)
+            return F.gelu(F.linear(n, self.fc.weight, self.fc.bias), approximate="tanh")
+
+    torch.manual_seed(0)
+    blk = Block().to(cuda)
+    q, k, v = (torch.randn(2, 4, 96, 64, device=cuda) for _ in range(3))
+    mask = torch.full((96, 96), float("-inf"), device=cuda).triu(1)
+    want = blk(q, k, v, mask)
+    gm = torch.fx.symbolic_trace(blk)
+    counts = P.apply_patterns(gm)
+    assert sum(counts.values()) == 5
+    got = gm(q, k, v, mask)
+    assert got.shape == want.shape and (got - want).abs().max().item() < 2e-2
+    assert _capi.device_status() == 0
