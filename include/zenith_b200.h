@@ -102,6 +102,13 @@ int zen_linear_i8_add_layernorm(const int8_t* xq, int64_t ldx, const int8_t* wq,
  * Process-wide, not thread-safe; meant for benchmarks.  No counterpart in the reference. */
 int zen_gemm_set_tile_n(int tile_n);
 
+/* Promise (1) or withdraw (0, the default) that the int8 weight operands given to zen_linear_i8,
+ * zen_linear_i8_prefetch and zen_linear_i8_add_layernorm are constants: never written by work that may still
+ * be running on the device when those calls are made.  With the promise a kernel requests the first weight
+ * tiles of each CTA before it waits for the kernel ahead of it in the stream (programmatic dependent launch),
+ * which hides their HBM latency behind that kernel's tail.  Process-wide.  No counterpart in the reference. */
+int zen_gemm_set_constant_weights(int on);
+
 /* FP16 Linear: y = x[M,K] . w[N,K]^T (+ bias[n], fp32) ; act ; out F16 or F32.  fp32 accumulate,
  * tcgen05 kind::f16.  K, ldx, ldw multiples of 8.
  * Replaces core/src/fp16_kernels.cu:92-122 (linear_fp16 = cublasGemmEx + add_bias_fp16_kernel)

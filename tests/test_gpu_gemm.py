@@ -85,6 +85,31 @@ def test_prefetch_hint_changes_nothing(cuda):
     assert _capi.device_status() == 0
 
 
+def test_constant_weights_promise_changes_nothing(cuda):
+    """zen_gemm_set_constant_weights: with the promise the kernels request weight tiles before their dependency
+    wait; results are the same, for one tile per CTA and for several, plain and fused with LayerNorm."""
+    for (M, N, K) in [(200, 520, 256), (4096, 3072, 768), (128, 768, 64)]:
+        x = dev(rng(1).integers(-128, 128, (M, K), dtype=np.int8), cuda)
+        w = dev(rng(2).integers(-128, 128, (N, K), dtype=np.int8), cuda)
+        ws = dev((rng(3).random(N) * 1e-3).astype(np.float32), cuda)
+        kw = dict(act="gelu", out_dtype=torch.int8, out_scale=0.05)
+        res = dev(rng(4).standard_normal((M, 768)).astype(np.float16), cuda)
+        g = torch.ones(768, dtype=torch.float16, device=cuda)
+        outs = []
+        for on in (False, True):
+            ops.set_constant_weights(on)
+            try:
+                o = [ops.linear_int8(x, w, 0.02, ws, None, **kw), ops.linear_int8(x, w, 0.02, ws, None, out_dtype=torch.float16)]
+                if N == 768:
+                    o += list(ops.linear_int8_add_layernorm(x, w, 0.02, ws, None, res, g, g, 1e-5, out_scale=0.03))
+            finally:
+                ops.set_constant_weights(False)
+            outs.append(o)
+        for a, b in zip(*outs):
+            assert torch.equal(a, b)
+    assert _capi.device_status() == 0
+
+
 def test_int8_epilogue_trunc_rounding_and_no_scale_no_bias(cuda):
     x = rng(5).integers(-128, 128, (64, 64), dtype=np.int8)
     w = rng(6).integers(-128, 128, (48, 64), dtype=np.int8)

@@ -131,6 +131,11 @@ int zen_gemm_set_tile_n(int bn) {
   return ZEN_OK;
 }
 
+int zen_gemm_set_constant_weights(int on) {
+  constant_weights_flag().store(on ? 1 : 0, std::memory_order_relaxed);
+  return ZEN_OK;
+}
+
 int zen_linear_i8(const int8_t* xq, int64_t ldx, const int8_t* wq, int64_t ldw, int M, int N, int K, float x_scale,
                   const float* w_scale, const float* bias, int act, int out_dtype, float out_scale, int round_mode,
                   void* out, int64_t ldo, void* stream) {
@@ -153,6 +158,7 @@ int zen_linear_i8_prefetch(const int8_t* xq, int64_t ldx, const int8_t* wq, int6
   p.M = M; p.N = N; p.K = K;
   p.out = out; p.ldo = ldo; p.out_dtype = out_dtype; p.act = act; p.round_mode = round_mode;
   p.x_scale = x_scale; p.out_scale = out_scale; p.w_scale = w_scale; p.bias = bias;
+  p.early_b = constant_weights_flag().load(std::memory_order_relaxed) ? 1 : 0;
   const void* next[2] = {next0, next1};
   const size_t next_bytes[2] = {next0_bytes, next1_bytes};
   for (int i = 0; i < 2; ++i) {

@@ -29,6 +29,7 @@ struct GemmLnParams {
   const __half* gamma;
   const __half* beta;
   int emit_q;  // write the int8 copy
+  int early_b;  // 1: the weights are constant: their first tiles may be requested before the dependency wait
 };
 
 constexpr int LN_CLUSTER = 4;
@@ -176,6 +177,16 @@ gemm_i8_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   grid_launch_dependents();
+  // constant weights: request the first weight tiles while the previous kernel may still be running
+  // (see gemm_tc_kernel); `pre` lives in the producer thread
+  int pre = 0;
+  if (threadIdx.x == 0 && p.early_b && cluster_id < p.tiles_m) {
+    pre = nkb < STAGES ? nkb : STAGES;
+    for (int kb = 0; kb < pre; ++kb) {
+      mbar_arrive_expect_tx(&full_bar[kb], STAGE_BYTES);
+      tma_load_2d(smem + size_t(kb) * STAGE_BYTES + A_BYTES, &tmap_b, &full_bar[kb], kb * BK, n_base);
+    }
+  }
   grid_dependency_wait();
 
   if (warp == 0) {
@@ -187,11 +198,19 @@ gemm_i8_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       for (int mt = cluster_id; mt < p.tiles_m && ok; mt += num_clusters) {
         const int m0 = mt * GEMM_BM;
         for (int kb = 0; kb < nkb; ++kb) {
+          uint8_t* sa = smem + size_t(stage) * STAGE_BYTES;
+          if (mt == cluster_id && kb < pre) {
+            tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * BK, m0);
+            if (++stage == STAGES) {
+              stage = 0;
+              phase ^= 1u;
+            }
+            continue;
+          }
           if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) {
             ok = false;
             break;
           }
-          uint8_t* sa = smem + size_t(stage) * STAGE_BYTES;
           mbar_arrive_expect_tx(&full_bar[stage], STAGE_BYTES);
           tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * BK, m0);
           tma_load_2d(sa + A_BYTES, &tmap_b, &full_bar[stage], kb * BK, n_base);
@@ -519,6 +538,7 @@ extern "C" int zen_linear_i8_add_layernorm(const int8_t* xq, int64_t ldx, const 
   p.residual = static_cast<const __half*>(residual); p.ldr = ldr;
   p.gamma = static_cast<const __half*>(gamma); p.beta = static_cast<const __half*>(beta);
   p.emit_q = yq ? 1 : 0;
+  p.early_b = constant_weights_flag().load(std::memory_order_relaxed) ? 1 : 0;
   CUtensorMap ta, tb, ty, tq, tr;
   int st = encode_tmap_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, xq, uint64_t(K), uint64_t(M), uint64_t(ldx), 128, GEMM_BM);
   if (st == ZEN_OK) st = encode_tmap_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, wq, uint64_t(K), uint64_t(N), uint64_t(ldw), 128, BN);

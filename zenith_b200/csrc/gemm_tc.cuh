@@ -41,6 +41,8 @@ struct GemmParams {
   // read, e.g. the next GEMMs' weights; every CTA asks for its slice while it waits for its own operands
   const uint8_t* pf_ptr[2];
   uint64_t pf_bytes[2];
+  // 1: B is constant (weights): its first tiles may be requested before the kernel waits for its predecessor
+  int early_b;
 };
 
 // One CTA's share of an L2 prefetch range, in requests of at most 32 KB (a hint: nothing waits on it).
@@ -472,6 +474,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       if (p.pf_bytes[i] != 0) prefetch_slice_l2(p.pf_ptr[i], p.pf_bytes[i], blockIdx.x, gridDim.x);
   }
   grid_launch_dependents();
+  // Constant weights: the B tiles of the first tile's first k-blocks are requested now, while the previous
+  // kernel may still be running (this CTA became resident when that kernel's CTA left the SM); only the A
+  // tiles, which the previous kernel may be writing, wait.  `pre` lives in the producer thread.
+  int pre = 0;
+  if constexpr (!B_MN) {
+    if (threadIdx.x == 0 && p.early_b && int(blockIdx.x) < num_tiles) {
+      const int n0 = (int(blockIdx.x) / p.tiles_m) * BN;
+      pre = nkb < STAGES ? nkb : STAGES;
+      for (int kb = 0; kb < pre; ++kb) {
+        mbar_arrive_expect_tx(&full_bar[kb], STAGE_BYTES);
+        tma_load_2d(smem + size_t(kb) * STAGE_BYTES + A_BYTES, &tmap_b, &full_bar[kb], kb * BK, n0);
+      }
+    }
+  }
   grid_dependency_wait();  // operands and output buffers may belong to the previous kernel until here
 
   if (warp == 0) {
@@ -484,12 +500,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const int m0 = (tile % p.tiles_m) * GEMM_BM;
         const int n0 = (tile / p.tiles_m) * BN;
         for (int kb = 0; kb < nkb; ++kb) {
+          uint8_t* sa = smem + size_t(stage) * STAGE_BYTES;
+          uint8_t* sb = sa + A_BYTES;
+          if (tile == int(blockIdx.x) && kb < pre) {
+            // stage kb: fresh, its barrier already expects the bytes and its B tile is on the way
+            tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * BK, m0);
+            if (++stage == STAGES) {
+              stage = 0;
+              phase ^= 1u;
+            }
+            continue;
+          }
           if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) {
             ok = false;
             break;
           }
-          uint8_t* sa = smem + size_t(stage) * STAGE_BYTES;
-          uint8_t* sb = sa + A_BYTES;
           mbar_arrive_expect_tx(&full_bar[stage], STAGE_BYTES);
           tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * BK, m0);
           if constexpr (!B_MN) {

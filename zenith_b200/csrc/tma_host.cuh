@@ -2,6 +2,7 @@
 // CUDA runtime so that the library links against cudart only and loads on a machine without
 // a driver (where every compute entry point then fails with ZEN_ERR_DRIVER / ZEN_ERR_LAUNCH).
 #pragma once
+#include <atomic>
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -62,6 +63,14 @@ inline int encode_tmap_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* 
   const uint64_t str[1] = {row_stride_bytes};
   const uint32_t box[2] = {box_inner, box_outer};
   return encode_tmap(map, dt, 2, base, dims, str, box, swizzle);
+}
+
+// Promise of the host (zen_gemm_set_constant_weights): the weight operand of the int8 linear entry points is
+// never written by work that may still be running when they are launched, so a kernel may request its
+// first weight tiles before it waits for its predecessor.  One flag for the whole library.
+inline std::atomic<int>& constant_weights_flag() {
+  static std::atomic<int> flag{0};
+  return flag;
 }
 
 // Launch with the programmatic-stream-serialization attribute (see grid_dependency_wait()).  Only for

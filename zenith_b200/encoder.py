@@ -352,6 +352,8 @@ class Int8Encoder(_EncoderBase):
         # next layer's QKV weights (zen_linear_i8_prefetch): a pass's weights do not stay in L2 beside
         # the activations, and a GEMM that starts on HBM-cold weights loses about a microsecond.
         self.prefetch_weights = bool(prefetch_weights)
+        # the int8 weights below are written once, here: the GEMMs may fetch them ahead of their dependency wait
+        ops.set_constant_weights(True)
         d = self.device
         self.act_scales = scales.act
         self.layers = []

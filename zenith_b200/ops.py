@@ -450,6 +450,13 @@ def embed_layernorm(ids, type_ids, word, pos, typ, gamma, beta, eps: float, seq:
     return y if yq is None else (y, yq)
 
 
+def set_constant_weights(on: bool) -> None:
+    """Promise that int8 weight tensors are never written while a GEMM that reads them may be queued
+    (``zen_gemm_set_constant_weights``): the GEMMs then fetch their first weight tiles ahead of the
+    dependency wait.  The encoder drivers make the promise for their own (immutable) weights."""
+    _capi.check("zen_gemm_set_constant_weights", _capi.lib().zen_gemm_set_constant_weights(1 if on else 0))
+
+
 def set_gemm_tile_n(tile_n: int) -> None:
     """Force the GEMM tile width (0 = automatic).  Benchmark hook."""
     _capi.call("zen_gemm_set_tile_n", int(tile_n))
