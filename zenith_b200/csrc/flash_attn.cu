@@ -296,14 +296,12 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
           for (int i = 0; i < 16; ++i) ov[i] = 0u;
         }
         uint32_t w[8];
-        float val[16];
+        float2 val[8];  // the fp16 values that are stored: the int8 copy quantizes these
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           const __half2 hh = __floats2half2_rn(__uint_as_float(ov[2 * i]) * inv, __uint_as_float(ov[2 * i + 1]) * inv);
           w[i] = *reinterpret_cast<const uint32_t*>(&hh);
-          const float2 f2 = __half22float2(hh);  // the int8 copy quantizes the fp16 values that are stored
-          val[2 * i] = f2.x;
-          val[2 * i + 1] = f2.y;
+          val[i] = __half22float2(hh);
         }
         // 16 columns = two 16-byte units (2g, 2g+1) of the row's 128-byte chunk g / 4
         uint8_t* srow = sty + (g / 4) * (4 * 4096) + lane * 128;
@@ -311,18 +309,14 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         *reinterpret_cast<uint4*>(srow + ((((2 * g + 1) & 7) ^ (lane & 7)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
         if (p.oq) {
           // branch-free fast rounding, exact division only for the few values next to a rounding boundary
-          int qi[16];
-          const uint32_t risky = quantize_fast_rn<16>(val, inv_o_scale, qi);
+          uint32_t qw[4];
+          const uint32_t risky = quantize_pairs_rn<16>(val, inv_o_scale, qw);
           if (risky) {
 #pragma unroll
             for (int e = 0; e < 16; ++e)
-              if (risky & (1u << e)) qi[e] = zen_det_round_clamp_i8(ZEN_DIV(val[e], p.o_scale), 0);
+              if (risky & (1u << e))
+                patch_q_byte(qw, e, zen_det_round_clamp_i8(ZEN_DIV((e & 1) ? val[e >> 1].y : val[e >> 1].x, p.o_scale), 0));
           }
-          uint32_t qw[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e)
-            qw[e] = (uint32_t(qi[4 * e]) & 0xffu) | ((uint32_t(qi[4 * e + 1]) & 0xffu) << 8) |
-                    ((uint32_t(qi[4 * e + 2]) & 0xffu) << 16) | ((uint32_t(qi[4 * e + 3]) & 0xffu) << 24);
           // 16 values = 16-byte unit g % 4 of the row's 64-byte chunk g / 4
           *reinterpret_cast<uint4*>(stq + (g / 4) * (4 * 2048) + lane * 64 + (((g % 4) ^ ((lane >> 1) & 3)) << 4)) =
               make_uint4(qw[0], qw[1], qw[2], qw[3]);

@@ -341,24 +341,19 @@ flash_attn_pipe_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
           uint32_t qw[8];
 #pragma unroll
           for (int g = 0; g < 2; ++g) {
-            float val[16];
+            float2 val[8];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&w[8 * g + e]));
-              val[2 * e] = f2.x;
-              val[2 * e + 1] = f2.y;
-            }
-            int qi[16];
-            const uint32_t risky = quantize_fast_rn<16>(val, inv_o_scale, qi);
+            for (int e = 0; e < 8; ++e) val[e] = __half22float2(*reinterpret_cast<const __half2*>(&w[8 * g + e]));
+            uint32_t q4[4];
+            const uint32_t risky = quantize_pairs_rn<16>(val, inv_o_scale, q4);
             if (risky) {
 #pragma unroll
               for (int e = 0; e < 16; ++e)
-                if (risky & (1u << e)) qi[e] = zen_det_round_clamp_i8(ZEN_DIV(val[e], p.o_scale), 0);
+                if (risky & (1u << e))
+                  patch_q_byte(q4, e, zen_det_round_clamp_i8(ZEN_DIV((e & 1) ? val[e >> 1].y : val[e >> 1].x, p.o_scale), 0));
             }
 #pragma unroll
-            for (int e = 0; e < 4; ++e)
-              qw[4 * g + e] = (uint32_t(qi[4 * e]) & 0xffu) | ((uint32_t(qi[4 * e + 1]) & 0xffu) << 8) |
-                              ((uint32_t(qi[4 * e + 2]) & 0xffu) << 16) | ((uint32_t(qi[4 * e + 3]) & 0xffu) << 24);
+            for (int e = 0; e < 4; ++e) qw[4 * g + e] = q4[e];
           }
           int8_t* qrow = p.oq + off + c * 32;
           reinterpret_cast<uint4*>(qrow)[0] = make_uint4(qw[0], qw[1], qw[2], qw[3]);

@@ -415,34 +415,39 @@ gemm_i8_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           }
           tmem_wait_ld();
           uint32_t w[GEMM_CW / 2];
-          float of[GEMM_CW];
+          float2 of[GEMM_CW / 2];  // the values that are stored: the int8 copy quantizes these
           const float2 nmu = make_float2(-mu, -mu);
           const float2 rstd2 = make_float2(rstd, rstd);
 #pragma unroll
           for (int j = 0; j < GEMM_CW; j += 2) {
             const float2 yv = make_float2(__uint_as_float(yb[j]), __uint_as_float(yb[j + 1]));
             const float2 o = f2fma(f2mul(f2add(yv, nmu), rstd2), make_float2(gs[j], gs[j + 1]),
-                                        make_float2(bs[j], bs[j + 1]));
+                                   make_float2(bs[j], bs[j + 1]));
             const __half2 h = __floats2half2_rn(o.x, o.y);
             w[j >> 1] = *reinterpret_cast<const uint32_t*>(&h);
-            const float2 hf = __half22float2(h);  // the int8 copy quantizes the value that was stored
-            of[j] = hf.x;
-            of[j + 1] = hf.y;
+            of[j >> 1] = __half22float2(h);
           }
           uint8_t* srow = sty + lane * 128;
           *reinterpret_cast<uint4*>(srow + (((2 * i) ^ (lane & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
           *reinterpret_cast<uint4*>(srow + (((2 * i + 1) ^ (lane & 7)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
           if (p.emit_q) {
             // branch-free fast rounding of all 16 values, exact recomputation only for the flagged ones
-            int q[GEMM_CW];
-            uint32_t risky = requant_fast<ZEN_ACT_NONE>(of, inv_q, p.round_mode, q);
-            if (risky) {
+            uint32_t qw[GEMM_CW / 4];
+            if (p.round_mode == 0) {
+              const uint32_t risky = quantize_pairs_rn<GEMM_CW>(of, inv_q, qw);
+              if (risky) {
+#pragma unroll
+                for (int j = 0; j < GEMM_CW; ++j)
+                  if (risky & (1u << j))
+                    patch_q_byte(qw, j, zen_det_round_clamp_i8(ZEN_DIV((j & 1) ? of[j >> 1].y : of[j >> 1].x, p.out_scale), 0));
+              }
+            } else {
+              int q[GEMM_CW];
 #pragma unroll
               for (int j = 0; j < GEMM_CW; ++j)
-                if (risky & (1u << j)) q[j] = zen_det_round_clamp_i8(ZEN_DIV(of[j], p.out_scale), p.round_mode);
+                q[j] = zen_det_round_clamp_i8(ZEN_DIV((j & 1) ? of[j >> 1].y : of[j >> 1].x, p.out_scale), p.round_mode);
+              pack_q(q, qw);
             }
-            uint32_t qw[GEMM_CW / 4];
-            pack_q(q, qw);
             *reinterpret_cast<uint4*>(stq + lane * 64 + ((i ^ ((lane >> 1) & 3)) << 4)) = make_uint4(qw[0], qw[1], qw[2], qw[3]);
           }
         }

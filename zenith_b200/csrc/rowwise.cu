@@ -117,6 +117,33 @@ __device__ __forceinline__ void store_q(int8_t* p, const float (&v)[N], float sc
   else *reinterpret_cast<uint32_t*>(p) = w[0];
 }
 
+// int8 copy of N values held as column pairs (nearest-even on the packed path, truncation by division)
+template <int N>
+__device__ __forceinline__ void store_q_pairs(int8_t* p, const float2 (&v)[N / 2], float scale, float inv_scale, int round_mode) {
+  uint32_t w[N / 4];
+  if (round_mode == 0) {
+    const uint32_t risky = quantize_pairs_rn<N>(v, inv_scale, w);
+    if (risky) {
+#pragma unroll
+      for (int j = 0; j < N; ++j)
+        if (risky & (1u << j)) patch_q_byte(w, j, zen_det_round_clamp_i8(ZEN_DIV((j & 1) ? v[j >> 1].y : v[j >> 1].x, scale), 0));
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < N / 4; ++i) {
+      uint32_t acc = 0;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int j = 4 * i + e;
+        acc |= (uint32_t(zen_det_round_clamp_i8(ZEN_DIV((j & 1) ? v[j >> 1].y : v[j >> 1].x, scale), round_mode)) & 0xffu) << (8 * e);
+      }
+      w[i] = acc;
+    }
+  }
+  if constexpr (N == 8) *reinterpret_cast<uint2*>(p) = make_uint2(w[0], w[1]);
+  else *reinterpret_cast<uint32_t*>(p) = w[0];
+}
+
 // ------------------------------------------------------------------------------------------
 // LayerNorm family.  SRC: 0 = x, 1 = x + residual, 2 = word[id] + pos[t % seq] + type[tid]
 // ------------------------------------------------------------------------------------------
@@ -230,13 +257,7 @@ __global__ void __launch_bounds__(ROW_WARPS * 32) ln_warp_kernel(const RowParams
       Vec16<T>::store2(y + c, o, seen);
       if (yq) {
         // quantize the value that was stored, so that yq == quantize(y) exactly
-        float q[N];
-#pragma unroll
-        for (int j = 0; j < P; ++j) {
-          q[2 * j] = seen[j].x;
-          q[2 * j + 1] = seen[j].y;
-        }
-        store_q<N>(yq + c, q, p.q_scale, inv_q_scale, p.round_mode);
+        store_q_pairs<N>(yq + c, seen, p.q_scale, inv_q_scale, p.round_mode);
       }
     }
   }

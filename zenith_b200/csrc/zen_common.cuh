@@ -328,6 +328,40 @@ __device__ __forceinline__ float2 f2mul_then_add(float2 a, float2 b, float2 c) {
   return make_float2(__fadd_rn(p.x, c.x), __fadd_rn(p.y, c.y));
 }
 
+// quantize_fast_rn on column pairs with the packed fp32x2 instructions, packed straight to bytes: w[] receives
+// the int8 values four to a word (the low mantissa byte of t + 1.5 * 2^23 is the two's-complement byte),
+// the returned mask flags the values to recompute with the true division (patch them with patch_q_byte).
+template <int N>
+__device__ __forceinline__ uint32_t quantize_pairs_rn(const float2 (&x)[N / 2], float inv_scale, uint32_t (&w)[N / 4]) {
+  constexpr float MAGIC = 12582912.0f;
+  const float2 inv2 = make_float2(inv_scale, inv_scale);
+  const float2 pm = make_float2(MAGIC, MAGIC), nm = make_float2(-MAGIC, -MAGIC), neg1 = make_float2(-1.0f, -1.0f);
+  uint32_t risky = 0;
+  uint32_t mb[N];
+#pragma unroll
+  for (int j = 0; j < N / 2; ++j) {
+    const float2 t = f2mul(x[j], inv2);
+    // NaN -> -128, as in the definition
+    const float2 tc = make_float2(fminf(fmaxf(t.x, -128.0f), 127.0f), fminf(fmaxf(t.y, -128.0f), 127.0f));
+    const float2 m = f2add(tc, pm);
+    const float2 d = f2fma(f2add(m, nm), neg1, tc);  // tc - rint(tc), exact
+    if (fmaf(fabsf(tc.x), 4e-6f, fabsf(d.x)) > 0.5f - 2e-6f) risky |= 1u << (2 * j);
+    if (fmaf(fabsf(tc.y), 4e-6f, fabsf(d.y)) > 0.5f - 2e-6f) risky |= 1u << (2 * j + 1);
+    mb[2 * j] = __float_as_uint(m.x);
+    mb[2 * j + 1] = __float_as_uint(m.y);
+  }
+#pragma unroll
+  for (int k = 0; k < N / 4; ++k)
+    w[k] = __byte_perm(__byte_perm(mb[4 * k], mb[4 * k + 1], 0x0040), __byte_perm(mb[4 * k + 2], mb[4 * k + 3], 0x0040), 0x5410);
+  return risky;
+}
+// replaces byte j of the packed int8 words by q
+template <int NW>
+__device__ __forceinline__ void patch_q_byte(uint32_t (&w)[NW], int j, int q) {
+  const int sh = 8 * (j & 3);
+  w[j >> 2] = (w[j >> 2] & ~(0xffu << sh)) | ((uint32_t(q) & 0xffu) << sh);
+}
+
 // 32 lanes x one 32-bit column.
 __device__ __forceinline__ void tmem_ld_32x1(uint32_t taddr, uint32_t& r) {
   asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(r) : "r"(taddr) : "memory");
