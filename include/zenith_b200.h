@@ -98,6 +98,14 @@ int zen_linear_i8_add_layernorm(const int8_t* xq, int64_t ldx, const int8_t* wq,
                                 int64_t ldr, const void* gamma, const void* beta, float eps, void* y, int8_t* yq,
                                 float out_scale, int round_mode, void* stream);
 
+/* The same kernel with fp16 operands (fp32 accumulation, no scales): y = LayerNorm(x . w^T + bias + residual),
+ * x fp16 [M, K], w fp16 [N, K], N = 768 or 1024, K a multiple of 8.  Replaces linear_fp16 + add_fp16 +
+ * layernorm_fp16 (core/src/fp16_kernels.cu:92-122, 154-279). */
+int zen_linear_f16_add_layernorm(const void* x, int64_t ldx, const void* w, int64_t ldw, int M, int N, int K,
+                                 const float* bias, const void* residual, int64_t ldr, const void* gamma,
+                                 const void* beta, float eps, void* y, int8_t* yq, float out_scale, int round_mode,
+                                 void* stream);
+
 /* Tuning hook: force the GEMM tile width (64, 128, 192 or 256; 0 restores automatic selection).
  * Process-wide, not thread-safe; meant for benchmarks.  No counterpart in the reference. */
 int zen_gemm_set_tile_n(int tile_n);

@@ -174,3 +174,24 @@ def test_host_pipeline_returns_every_batch(cuda):
     with pytest.raises(ValueError):
         pipe.result(0)  # its slot has been reused
     assert _capi.device_status() == 0
+
+
+def test_fp16_encoder_with_fused_layernorm_kernels(cuda):
+    """hidden 768: the fp16 encoder runs attention-output and FFN2 as GEMM + residual + LayerNorm kernels."""
+    cfg = EncoderConfig(layers=2, hidden=768, heads=12, ffn=1024, vocab=2000, max_pos=128)
+    params = init_params(cfg, 11, random_affine=True)
+    ids = rng(50).integers(0, cfg.vocab, (2, 96))
+    lens = np.array([96, 70], np.int32)
+    enc = Fp16Encoder(cfg, params, cuda)
+    assert enc.fuse_layernorm and enc.launches_per_layer == 5
+    got = enc.forward(*tdev(ids, lens, cuda)).float().cpu().numpy()
+    want = ER.encoder_fp32(cfg, params, ids, lens)
+    assert np.max(np.abs(got - want)) < 3e-2 and np.mean(np.abs(got - want)) < 2e-3
+    unfused = Fp16Encoder(cfg, params, cuda, fuse_layernorm=False).forward(*tdev(ids, lens, cuda)).float().cpu().numpy()
+    assert np.mean(np.abs(unfused - got)) < 2e-3
+    eager = enc.out.clone()
+    enc.capture(*ids.shape)
+    enc.set_inputs(*tdev(ids, lens, cuda))
+    assert torch.equal(enc.replay(), eager)
+    taps = enc.forward_with_taps(*tdev(ids, lens, cuda))
+    assert len(taps["h1"]) == cfg.layers and all(lo < hi for lo, hi in taps["h1"])

@@ -66,3 +66,25 @@ def test_unsupported_width_is_refused(cuda):
     with pytest.raises(_capi.ZenithError) as e:
         ops.linear_int8_add_layernorm(x, w, 1.0, None, None, r, g, g, 1e-5)
     assert e.value.status == _capi.ERR_UNSUPPORTED
+
+
+@pytest.mark.parametrize("M,K,N", [(128, 768, 768), (300, 256, 768), (4096, 3072, 768), (1, 8, 768), (700, 1024, 1024)])
+def test_fp16_linear_add_layernorm(cuda, M, K, N):
+    """The fp16-operand form of the cluster kernel against an fp32 computation of the same thing."""
+    x = (rng(M).standard_normal((M, K)) * 0.5).astype(np.float16)
+    w = (rng(K).standard_normal((N, K)) * 0.05).astype(np.float16)
+    b = (rng(2).standard_normal(N) * 0.1).astype(np.float32)
+    res = rng(3).standard_normal((M, N)).astype(np.float16)
+    g = (1 + 0.1 * rng(4).standard_normal(N)).astype(np.float16)
+    be = (0.1 * rng(5).standard_normal(N)).astype(np.float16)
+    y, yq = ops.linear_fp16_add_layernorm(dev(x, cuda), dev(w, cuda), dev(b, cuda), dev(res, cuda), dev(g, cuda),
+                                          dev(be, cuda), 1e-12, out_scale=0.03)
+    t = x.astype(np.float32) @ w.astype(np.float32).T + b + res.astype(np.float32)
+    want = O.layernorm(t, g.astype(np.float32), be.astype(np.float32), 1e-12)
+    got = y.float().cpu().numpy()
+    assert not np.isnan(got).any()
+    assert np.max(np.abs(got - want)) < 1e-2 and np.mean(np.abs(got - want)) < 5e-4
+    assert np.array_equal(yq.cpu().numpy(), O.quantize(got, 0.03))
+    assert torch.equal(ops.linear_fp16_add_layernorm(dev(x, cuda), dev(w, cuda), dev(b, cuda), dev(res, cuda), dev(g, cuda),
+                                                     dev(be, cuda), 1e-12), y)
+    assert _capi.device_status() == 0

@@ -29,6 +29,7 @@ SIGNATURES = {
     "zen_linear_i8_prefetch": [_p, _i64, _p, _i64, _i, _i, _i, _f, _p, _p, _i, _i, _f, _i, _p, _i64, _p, C.c_size_t, _p,
                                C.c_size_t, _p],
     "zen_linear_i8_add_layernorm": [_p, _i64, _p, _i64, _i, _i, _i, _f, _p, _p, _p, _i64, _p, _p, _f, _p, _p, _f, _i, _p],
+    "zen_linear_f16_add_layernorm": [_p, _i64, _p, _i64, _i, _i, _i, _p, _p, _i64, _p, _p, _f, _p, _p, _f, _i, _p],
     "zen_linear_f16": [_p, _i64, _p, _i64, _i, _i, _i, _p, _i, _i, _p, _i64, _p],
     "zen_linear_f32": [_p, _i64, _p, _i64, _i, _i, _i, _p, _i, _p, _i64, _p],
     "zen_wmma_matmul_f16": [_p, _p, _p, _i, _i, _i, _p],

@@ -105,19 +105,21 @@ constexpr size_t gemm_ln_smem_bytes() {
          size_t(SLABS) * 128 * 8 + 256 + size_t(SLABS) * 4 * 4 * 64 * 4 + 1024;
 }
 
-template <int BN, int STAGES>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
-gemm_i8_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                  const __grid_constant__ CUtensorMap tmap_y, const __grid_constant__ CUtensorMap tmap_q,
-                  const __grid_constant__ CUtensorMap tmap_r, const GemmLnParams p) {
-  constexpr int BK = 128, UK = 32;
+// KIND_I8: int8 operands, s32 accumulators, dequantised with x_scale * w_scale[n]; KIND_F16: fp16 operands, fp32
+// accumulators (the scale row holds ones).  Everything after the accumulator is shared.
+template <int KIND, int BN, int STAGES>
+__device__ __forceinline__ void gemm_ln_body(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b, const CUtensorMap& tmap_y,
+                                             const CUtensorMap& tmap_q, const CUtensorMap& tmap_r, const GemmLnParams& p) {
+  constexpr int ELEM = GemmKind<KIND>::ELEM;
+  constexpr int BK = 128 / ELEM, UK = 32 / ELEM;
   constexpr int A_BYTES = GEMM_BM * 128;
   constexpr int B_BYTES = BN * 128;
   constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   constexpr int SLABS = BN / 64;
   constexpr int EPI_ACTIVE = SLABS * 4 * 32;  // epilogue threads that own a slab
   constexpr uint32_t TMEM_COLS = gemm_tmem_cols<BN>();
-  constexpr uint32_t IDESC = make_idesc(IDESC_C_S32, IDESC_S8, IDESC_S8, 0, 0, GEMM_BM, BN);
+  constexpr uint32_t IDESC = KIND == KIND_I8 ? make_idesc(IDESC_C_S32, IDESC_S8, IDESC_S8, 0, 0, GEMM_BM, BN)
+                                             : make_idesc(IDESC_C_F32, IDESC_F16, IDESC_F16, 0, 0, GEMM_BM, BN);
   constexpr int STEPS = 64 / GEMM_CW;
   static_assert(BN % 64 == 0 && BN <= 256, "BN");
 
@@ -246,8 +248,8 @@ gemm_i8_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           const uint32_t b_addr = a_addr + A_BYTES;
 #pragma unroll
           for (int k = 0; k < BK / UK; ++k)
-            mma_i8_ss(d_tmem, make_smem_desc_sw128(a_addr + k * 32, 1024, 16),
-                      make_smem_desc_sw128(b_addr + k * 32, 1024, 16), IDESC, (kb | k) != 0 ? 1u : 0u);
+            issue_mma<KIND>(d_tmem, make_smem_desc_sw128(a_addr + k * 32, 1024, 16),
+                            make_smem_desc_sw128(b_addr + k * 32, 1024, 16), IDESC, (kb | k) != 0 ? 1u : 0u);
           tc_commit(&empty_bar[stage]);
           if (++stage == STAGES) {
             stage = 0;
@@ -329,7 +331,8 @@ gemm_i8_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           float2 s2 = make_float2(0.f, 0.f);
 #pragma unroll
           for (int j = 0; j < GEMM_CW / 2; ++j) {
-            const float2 af = make_float2(float(int32_t(a[2 * j])), float(int32_t(a[2 * j + 1])));
+            const float2 af = KIND == KIND_I8 ? make_float2(float(int32_t(a[2 * j])), float(int32_t(a[2 * j + 1])))
+                                              : make_float2(__uint_as_float(a[2 * j]), __uint_as_float(a[2 * j + 1]));
             y[j] = f2add(f2fma(af, make_float2(cs[2 * j], cs[2 * j + 1]), make_float2(bs[2 * j], bs[2 * j + 1])),
                               __half22float2(rh[j]));
             s2 = f2add(s2, y[j]);
@@ -486,9 +489,25 @@ gemm_i8_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 }
 
 template <int BN, int STAGES>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_i8_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                  const __grid_constant__ CUtensorMap tmap_y, const __grid_constant__ CUtensorMap tmap_q,
+                  const __grid_constant__ CUtensorMap tmap_r, const GemmLnParams p) {
+  gemm_ln_body<KIND_I8, BN, STAGES>(tmap_a, tmap_b, tmap_y, tmap_q, tmap_r, p);
+}
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_f16_ln_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                   const __grid_constant__ CUtensorMap tmap_y, const __grid_constant__ CUtensorMap tmap_q,
+                   const __grid_constant__ CUtensorMap tmap_r, const GemmLnParams p) {
+  gemm_ln_body<KIND_F16, BN, STAGES>(tmap_a, tmap_b, tmap_y, tmap_q, tmap_r, p);
+}
+
+template <int KIND, int BN, int STAGES>
 static int launch_gemm_ln(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& ty, const CUtensorMap& tq,
                           const CUtensorMap& tr, const GemmLnParams& p, cudaStream_t stream) {
-  auto kernel = gemm_i8_ln_kernel<BN, STAGES>;
+  auto kernel = KIND == KIND_I8 ? gemm_i8_ln_kernel<BN, STAGES> : gemm_f16_ln_kernel<BN, STAGES>;
   constexpr size_t smem = gemm_ln_smem_bytes<BN, STAGES>();
   if (int st = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), smem); st != ZEN_OK) return st;
   int clusters = num_sms() / LN_CLUSTER;
@@ -520,33 +539,37 @@ using namespace zen;
 
 ZEN_DEFINE_TU_STATUS(gemm_ln)
 
-extern "C" int zen_linear_i8_add_layernorm(const int8_t* xq, int64_t ldx, const int8_t* wq, int64_t ldw, int M, int N,
-                                           int K, float x_scale, const float* w_scale, const float* bias,
-                                           const void* residual, int64_t ldr, const void* gamma, const void* beta,
-                                           float eps, void* y, int8_t* yq, float out_scale, int round_mode,
-                                           void* stream) {
-  if (!xq || !wq || !residual || !gamma || !beta || !y || M <= 0 || N <= 0 || K <= 0) return ZEN_ERR_INVALID_ARG;
+template <int KIND>
+static int run_linear_add_layernorm(const void* x, int64_t ldx, const void* w, int64_t ldw, int M, int N, int K, float x_scale,
+                                    const float* w_scale, const float* bias, const void* residual, int64_t ldr,
+                                    const void* gamma, const void* beta, float eps, void* y, int8_t* yq, float out_scale,
+                                    int round_mode, void* stream) {
+  constexpr int ELEM = GemmKind<KIND>::ELEM;  // bytes per operand element
+  constexpr int KA = 16 / ELEM;               // elements per 16 bytes: the unit K and the row strides must be a multiple of
+  if (!x || !w || !residual || !gamma || !beta || !y || M <= 0 || N <= 0 || K <= 0) return ZEN_ERR_INVALID_ARG;
   if (round_mode != ZEN_ROUND_NEAREST_EVEN && round_mode != ZEN_ROUND_TRUNC) return ZEN_ERR_INVALID_ARG;
   if (yq && !(out_scale > 0.0f)) return ZEN_ERR_INVALID_ARG;
   if (N != 768 && N != 1024) return ZEN_ERR_UNSUPPORTED;  // four CTAs x 192 (or 256) columns hold one row
-  if (K % 16 || ldx % 16 || ldw % 16 || ldx < K || ldw < K || ldr % 8 || ldr < N) return ZEN_ERR_UNSUPPORTED;
+  if (K % KA || ldx % KA || ldw % KA || ldx < K || ldw < K || ldr % 8 || ldr < N) return ZEN_ERR_UNSUPPORTED;
   if (reinterpret_cast<uintptr_t>(y) % 16 || reinterpret_cast<uintptr_t>(yq) % 16 ||
       reinterpret_cast<uintptr_t>(residual) % 16)
     return ZEN_ERR_UNSUPPORTED;
   const int BN = N / LN_CLUSTER;
+  constexpr int BK = 128 / ELEM;
   GemmLnParams p{};
   p.M = M; p.N = N; p.K = K;
   p.tiles_m = (M + GEMM_BM - 1) / GEMM_BM;
-  p.num_k_blocks = (K + 127) / 128;
+  p.num_k_blocks = (K + BK - 1) / BK;
   p.x_scale = x_scale; p.out_scale = yq ? out_scale : 1.0f; p.eps = eps; p.round_mode = round_mode;
   p.w_scale = w_scale; p.bias = bias;
   p.residual = static_cast<const __half*>(residual); p.ldr = ldr;
   p.gamma = static_cast<const __half*>(gamma); p.beta = static_cast<const __half*>(beta);
   p.emit_q = yq ? 1 : 0;
   p.early_b = constant_weights_flag().load(std::memory_order_relaxed) ? 1 : 0;
+  const CUtensorMapDataType dt = KIND == KIND_I8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   CUtensorMap ta, tb, ty, tq, tr;
-  int st = encode_tmap_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, xq, uint64_t(K), uint64_t(M), uint64_t(ldx), 128, GEMM_BM);
-  if (st == ZEN_OK) st = encode_tmap_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, wq, uint64_t(K), uint64_t(N), uint64_t(ldw), 128, BN);
+  int st = encode_tmap_2d(&ta, dt, x, uint64_t(K), uint64_t(M), uint64_t(ldx) * ELEM, BK, GEMM_BM);
+  if (st == ZEN_OK) st = encode_tmap_2d(&tb, dt, w, uint64_t(K), uint64_t(N), uint64_t(ldw) * ELEM, BK, BN);
   if (st == ZEN_OK)
     st = encode_tmap_2d(&ty, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, y, uint64_t(N), uint64_t(M), uint64_t(N) * 2, 64, 32,
                         CU_TENSOR_MAP_SWIZZLE_128B);
@@ -558,6 +581,23 @@ extern "C" int zen_linear_i8_add_layernorm(const int8_t* xq, int64_t ldx, const 
     st = encode_tmap_2d(&tr, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, residual, uint64_t(N), uint64_t(M), uint64_t(ldr) * 2, 64, 32,
                         CU_TENSOR_MAP_SWIZZLE_128B);
   if (st != ZEN_OK) return st;
-  if (BN == 192) return launch_gemm_ln<192, 3>(ta, tb, ty, tq, tr, p, static_cast<cudaStream_t>(stream));
-  return launch_gemm_ln<256, 2>(ta, tb, ty, tq, tr, p, static_cast<cudaStream_t>(stream));
+  if (BN == 192) return launch_gemm_ln<KIND, 192, 3>(ta, tb, ty, tq, tr, p, static_cast<cudaStream_t>(stream));
+  return launch_gemm_ln<KIND, 256, 2>(ta, tb, ty, tq, tr, p, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int zen_linear_i8_add_layernorm(const int8_t* xq, int64_t ldx, const int8_t* wq, int64_t ldw, int M, int N,
+                                           int K, float x_scale, const float* w_scale, const float* bias,
+                                           const void* residual, int64_t ldr, const void* gamma, const void* beta,
+                                           float eps, void* y, int8_t* yq, float out_scale, int round_mode,
+                                           void* stream) {
+  return run_linear_add_layernorm<KIND_I8>(xq, ldx, wq, ldw, M, N, K, x_scale, w_scale, bias, residual, ldr, gamma, beta, eps,
+                                           y, yq, out_scale, round_mode, stream);
+}
+
+extern "C" int zen_linear_f16_add_layernorm(const void* x, int64_t ldx, const void* w, int64_t ldw, int M, int N, int K,
+                                            const float* bias, const void* residual, int64_t ldr, const void* gamma,
+                                            const void* beta, float eps, void* y, int8_t* yq, float out_scale,
+                                            int round_mode, void* stream) {
+  return run_linear_add_layernorm<KIND_F16>(x, ldx, w, ldw, M, N, K, 1.0f, nullptr, bias, residual, ldr, gamma, beta, eps, y,
+                                            yq, out_scale, round_mode, stream);
 }

@@ -214,8 +214,16 @@ class _EncoderBase:
 class Fp16Encoder(_EncoderBase):
     """fp16 weights and activations, fp32 accumulation and statistics."""
 
-    def __init__(self, cfg: EncoderConfig, params: dict, device="cuda:0", micro_batches: int = 1):
+    def __init__(self, cfg: EncoderConfig, params: dict, device="cuda:0", micro_batches: int = 1,
+                 fuse_layernorm: bool | None = None):
+        """``fuse_layernorm``: attention-output and FFN2 as one GEMM + residual + LayerNorm kernel each (5 launches
+        per layer instead of 7); possible for hidden 768 and 1024, on by default for 768."""
         super().__init__(cfg, params, device, micro_batches)
+        self.fuse_layernorm = (cfg.hidden == 768) if fuse_layernorm is None else bool(fuse_layernorm)
+        if self.fuse_layernorm and cfg.hidden not in (768, 1024):
+            raise RuntimeError("the fused GEMM + LayerNorm kernel needs hidden == 768 or 1024")
+        self.launches_per_layer = 5 if self.fuse_layernorm else 7
+        ops.set_constant_weights(True)  # the weights below are written once, here
         d = self.device
         self.layers = []
         for lp in params["layers"]:
@@ -257,16 +265,26 @@ class Fp16Encoder(_EncoderBase):
                       ACT_NONE, DT_F16, P(self.qkv), 3 * H)
             self._add("zen_flash_attention_f16", P(self.qkv), P(self.qkv) + 2 * H, P(self.qkv) + 4 * H, P(self.ctx), None,
                       1.0, B, nh, S, hd, *qs, *qs, *qs, *os_, kv, 0, 1.0 / math.sqrt(hd))
-            self._add("zen_linear_f16", P(self.ctx), H, L["wo"].data_ptr(), H, T, H, H, L["bo"].data_ptr(),
-                      ACT_NONE, DT_F16, P(self.ao), H)
-            self._add("zen_add_layernorm_f16", P(self.ao), P(x), L["ln1_g"].data_ptr(), L["ln1_b"].data_ptr(),
-                      P(self.h1), None, 1.0, ROUND_NEAREST_EVEN, T, H, cfg.eps)
+            if self.fuse_layernorm:
+                self._add("zen_linear_f16_add_layernorm", P(self.ctx), H, L["wo"].data_ptr(), H, T, H, H, L["bo"].data_ptr(),
+                          P(x), H, L["ln1_g"].data_ptr(), L["ln1_b"].data_ptr(), cfg.eps, P(self.h1), None, 1.0,
+                          ROUND_NEAREST_EVEN)
+            else:
+                self._add("zen_linear_f16", P(self.ctx), H, L["wo"].data_ptr(), H, T, H, H, L["bo"].data_ptr(),
+                          ACT_NONE, DT_F16, P(self.ao), H)
+                self._add("zen_add_layernorm_f16", P(self.ao), P(x), L["ln1_g"].data_ptr(), L["ln1_b"].data_ptr(),
+                          P(self.h1), None, 1.0, ROUND_NEAREST_EVEN, T, H, cfg.eps)
             self._add("zen_linear_f16", P(self.h1), H, L["w1"].data_ptr(), H, T, F, H, L["b1"].data_ptr(),
                       ACT_GELU, DT_F16, P(self.g), F)
-            self._add("zen_linear_f16", P(self.g), F, L["w2"].data_ptr(), F, T, H, F, L["b2"].data_ptr(),
-                      ACT_NONE, DT_F16, P(self.o), H)
-            self._add("zen_add_layernorm_f16", P(self.o), P(self.h1), L["ln2_g"].data_ptr(), L["ln2_b"].data_ptr(),
-                      P(xn), None, 1.0, ROUND_NEAREST_EVEN, T, H, cfg.eps)
+            if self.fuse_layernorm:
+                self._add("zen_linear_f16_add_layernorm", P(self.g), F, L["w2"].data_ptr(), F, T, H, F, L["b2"].data_ptr(),
+                          P(self.h1), H, L["ln2_g"].data_ptr(), L["ln2_b"].data_ptr(), cfg.eps, P(xn), None, 1.0,
+                          ROUND_NEAREST_EVEN)
+            else:
+                self._add("zen_linear_f16", P(self.g), F, L["w2"].data_ptr(), F, T, H, F, L["b2"].data_ptr(),
+                          ACT_NONE, DT_F16, P(self.o), H)
+                self._add("zen_add_layernorm_f16", P(self.o), P(self.h1), L["ln2_g"].data_ptr(), L["ln2_b"].data_ptr(),
+                          P(xn), None, 1.0, ROUND_NEAREST_EVEN, T, H, cfg.eps)
             cur ^= 1
 
     def forward_with_taps(self, ids, kv_lens=None, observers: dict | None = None) -> dict | None:
@@ -284,7 +302,7 @@ class Fp16Encoder(_EncoderBase):
         if own:
             observers = self.make_observers()
         stream = torch.cuda.current_stream().cuda_stream
-        per_layer = 7
+        per_layer = self.launches_per_layer
         f, name, args = self._launches[0]
         _capi.check(name, f(*args, stream))
         cur = 0

@@ -131,6 +131,30 @@ def linear_int8_add_layernorm(xq, wq, x_scale: float, w_scale, bias, residual, g
     return y if yq is None else (y, yq)
 
 
+def linear_fp16_add_layernorm(x, w, bias, residual, gamma, beta, eps: float, *, out_scale: float | None = None,
+                              round="nearest_even"):
+    """``LayerNorm(x @ w.T + bias + residual) * gamma + beta`` with fp16 operands in one kernel (hidden 768 or
+    1024).  Returns fp16 ``y`` and, with ``out_scale``, also ``quantize(y, out_scale)``."""
+    _require(x, "x", torch.float16, 2)
+    _require(w, "w", torch.float16, 2)
+    _require(residual, "residual", torch.float16, 2)
+    _require(gamma, "gamma", torch.float16, 1)
+    _require(beta, "beta", torch.float16, 1)
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or tuple(residual.shape) != (M, N):
+        raise RuntimeError("shape mismatch")
+    if bias is not None:
+        _require(bias, "bias", torch.float32, 1)
+    y = torch.empty((M, N), dtype=torch.float16, device=x.device)
+    yq = torch.empty((M, N), dtype=torch.int8, device=x.device) if out_scale is not None else None
+    if M:
+        _call("zen_linear_f16_add_layernorm", x.data_ptr(), K, w.data_ptr(), K, M, N, K, _ptr(bias), residual.data_ptr(), N,
+              gamma.data_ptr(), beta.data_ptr(), float(eps), y.data_ptr(), _ptr(yq), float(out_scale or 1.0), _ROUND[round],
+              _stream())
+    return y if yq is None else (y, yq)
+
+
 def linear_fp16(x, w, bias=None, *, act="none", out_dtype=torch.float16, out=None):
     """``act(x @ w.T + bias)`` with fp16 operands, fp32 accumulation (core/src/fp16_kernels.cu:92-122)."""
     _require(x, "x", torch.float16, 2)
