@@ -8,8 +8,8 @@ A step is one forward pass of the encoder over one batch of 32 synthetic sequenc
 (BASELINE.json configs[2]: 12 layers, hidden 768, 12 heads, FFN 3072, post-LN, tanh-GELU, W8A8 with
 per-channel weight scales and min-max activation scales from 16 seeded batches; token ids uniform
 over 30522 words, the last 0..32 positions of each row masked).  Ranks are independent replicas
-(weak scaling, global batch 32 * N); for N > 1 each step ends with the NCCL all_gather of the hidden
-states.  Rank 0 prints ONE JSON line.
+(weak scaling, global batch 32 * N); for N > 1 each step ends with the NCCL gather of the hidden
+states onto rank 0.  Rank 0 prints ONE JSON line.
 
 `value`      sequences/s with token ids already in HBM (CUDA-graph replay of the 61 launches).
 `e2e`        the same through the public host API (zenith_b200.serve.HostPipeline) with HOST buffers: every
@@ -284,7 +284,7 @@ def run_ours(args) -> None:
     lens_h = torch.from_numpy(lens_np).pin_memory()
     enc.capture(BATCH, SEQ)
     enc.set_inputs(ids_h.to(dev), lens_h.to(dev))
-    gatherer = OutputGatherer(BATCH * world, SEQ, cfg.hidden, torch.float16, dev) if world > 1 else None
+    gatherer = OutputGatherer(BATCH * world, SEQ, cfg.hidden, torch.float16, dev, root=0) if world > 1 else None
 
     l2_flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # 2 x the 126 MB L2
 

@@ -51,6 +51,13 @@ def _worker(rank, world, port, gb, fail_rank, out):
             a = g.gather_async(local, 0)
             b = g.gather_async(local + 1, 1)
             ok = ok and bool(torch.equal(a.wait(), want)) and bool(torch.equal(b.wait(), want + 1))
+            # gather onto rank 0 only: the root holds everything, the others their own rows
+            g0 = OutputGatherer(gb, seq, hidden, torch.float32, "cpu", root=0)
+            for res in (g0.gather(local), g0.gather_async(local, 0).wait()):
+                if rank == 0:
+                    ok = ok and bool(torch.equal(res, want))
+                else:
+                    ok = ok and bool(torch.equal(res[start * seq:(start + count) * seq], local))
             out[rank] = ok
         else:
             out[rank] = "skipped"  # the host learns of the peer's failure before launching the collective

@@ -46,8 +46,13 @@ class OutputGatherer:
     """Gathers per-rank hidden states ``[count_r * seq, hidden]`` into one ``[global_batch * seq, hidden]``
     buffer that is allocated once.  Shards may be uneven: each rank's rows land at its own offset."""
 
-    def __init__(self, global_batch: int, seq: int, hidden: int, dtype, device, group=None):
+    def __init__(self, global_batch: int, seq: int, hidden: int, dtype, device, group=None, root: int | None = None):
+        """``root``: None gathers onto every rank (all_gather); a rank number gathers onto that rank only
+        (each other rank sends its shard once: an eighth of the all_gather's traffic per receiver-less rank,
+        and the form a single consumer of the hidden states needs).  On non-root ranks ``gather`` then returns
+        a buffer whose only valid rows are the rank's own."""
         self.group = group
+        self.root = root
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.seq, self.hidden = seq, hidden
@@ -68,6 +73,10 @@ class OutputGatherer:
             raise RuntimeError(f"rank {self.rank}: expected {(count * self.seq, self.hidden)}, got {tuple(local.shape)}")
         if self.world == 1:
             self.full.copy_(local)
+        elif self.even and self.root is not None:
+            dist.gather(local.contiguous(), self.views if self.rank == self.root else None, dst=self.root, group=self.group)
+            if self.rank != self.root:
+                self.views[self.rank].copy_(local)
         elif self.even:
             dist.all_gather_into_tensor(self.full, local.contiguous(), group=self.group)
         else:
@@ -94,6 +103,13 @@ class OutputGatherer:
         if not self.even:
             out.copy_(self.gather(local))
             return PendingGather(None, out)
+        if self.root is not None:
+            views = [out[s_ * self.seq:(s_ + c) * self.seq] for s_, c in self.bounds]
+            work = dist.gather(local.contiguous(), views if self.rank == self.root else None, dst=self.root, group=self.group,
+                               async_op=True)
+            if self.rank != self.root:
+                views[self.rank].copy_(local)
+            return PendingGather(work, out)
         work = dist.all_gather_into_tensor(out, local.contiguous(), group=self.group, async_op=True)
         return PendingGather(work, out)
 
