@@ -370,7 +370,7 @@ def run_ours(args) -> None:
         "metric": METRIC, "value": value, "unit": "sequences/s", "n_gpus": world, "steps": K, "warmup": W,
         "ms_per_step": total_ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "s8 operands, s32 accumulators (fp16 LayerNorm / softmax / residual)", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "global_batch": BATCH * world, "seq_len": SEQ, "parallelism": f"replicas x{world}",
+        "config": {"workload": WORKLOAD, "global_batch": BATCH * world, "seq_len": SEQ, "parallelism": f"replicas x{world}" + (", NCCL gather of the hidden states onto rank 0 inside every step" if world > 1 else ""),
                    "l2": "256 MB buffer written between timed steps", "launch": f"CUDA-graph replay of {enc.launches_per_forward} kernels in {args.micro_batches} concurrent micro-batch(es)"},
         "e2e": {"value": e2e_value, "unit": "sequences/s", "ms_per_step": e2e_ms / K,
                 "h2d_bytes_per_step": int(ids_h.numel() * ids_h.element_size() + lens_h.numel() * lens_h.element_size()),
