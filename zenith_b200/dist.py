@@ -3,7 +3,7 @@
 Every sequence is independent through the whole encoder (LayerNorm is per token, attention per
 sequence), so the global batch is split by rank, each rank holds a full weight replica and no
 collective sits inside a layer.  The only exchange is the gather of the final hidden states
-(``all_gather`` over NCCL on GPUs, gloo in CPU tests).  The reference has no distributed code; its
+(onto one rank with send / receive, or onto every rank with ``all_gather``; NCCL on GPUs, gloo in CPU tests).  The reference has no distributed code; its
 one multi-GPU helper runs independent replicas from a thread pool (benchmarks/mlperf_suite.py:750-850).
 """
 from __future__ import annotations
