@@ -120,7 +120,22 @@ class ClockSampler:
 # ------------------------------------------------------------------------------------------------
 # CPU arm: the reference's quantized executor restated (oracle/encoder_ref.py), host cores only
 # ------------------------------------------------------------------------------------------------
+def blas_threads_all() -> int:
+    """Let numpy's BLAS use every host core (torchrun exports OMP_NUM_THREADS=1 to its workers) and return the
+    number of threads it will really use."""
+    n = os.cpu_count() or 1
+    try:
+        from threadpoolctl import threadpool_info, threadpool_limits
+
+        threadpool_limits(limits=n)
+        used = [p.get("num_threads", 1) for p in threadpool_info() if p.get("user_api") == "blas"]
+        return max(used) if used else 1
+    except Exception:
+        return int(os.environ.get("OMP_NUM_THREADS", n))
+
+
 def cpu_executor(sample_seqs: int, steps: int, warmup: int) -> dict:
+    threads = blas_threads_all()
     from oracle import encoder_ref as ER
     from zenith_b200.calibrate import activation_scales_from_ranges, quantize_weights
     from zenith_b200.encoder import BERT_BASE, Int8Scales, init_params
@@ -139,8 +154,8 @@ def cpu_executor(sample_seqs: int, steps: int, warmup: int) -> dict:
         times.append(time.perf_counter() - t0)
     total = sum(times)
     return {"seq_per_s": sample_seqs * steps / total, "ms_per_step": 1e3 * total / steps,
-            "cores": os.cpu_count(), "sample": f"{steps} passes of {sample_seqs} sequences x {SEQ} tokens "
-            f"(numpy fake-quant + fp32 BLAS matmul, all host threads)"}
+            "cores": threads, "sample": f"{steps} passes of {sample_seqs} sequences x {SEQ} tokens "
+            f"(numpy fake-quant + fp32 BLAS matmul on {threads} BLAS threads of {os.cpu_count()} host cores)"}
 
 
 _RESULT_FD = None
