@@ -69,6 +69,39 @@ def test_elementwise_bit_exact(cuda, n):
     assert np.array_equal(ops.to_fp32(dev(h, cuda)).cpu().numpy(), h.astype(np.float32))
 
 
+@pytest.mark.parametrize("off", [1, 3])
+@pytest.mark.parametrize("n", [1, 37, 4099])
+def test_elementwise_on_unaligned_views(cuda, n, off):
+    """Contiguous views that start off a 16-byte boundary (``t[off:]``) take the element-by-element form of the
+    kernel: results are those of the aligned call and nothing outside the output view is written."""
+    x = (3 * rng(n + off).standard_normal(n + off)).astype(np.float32)
+    h = x.astype(np.float16)
+    q = rng(1).integers(-128, 128, n + off, dtype=np.int8)
+    xs, hs, qs = x[off:], h[off:], q[off:]
+    xd, hd, qd = dev(x, cuda)[off:], dev(h, cuda)[off:], dev(q, cuda)[off:]
+    assert np.array_equal(ops.gelu(xd).cpu().numpy().view(np.int32), O.gelu(xs).view(np.int32))
+    assert np.array_equal(ops.relu(xd).cpu().numpy(), np.maximum(xs, 0))
+    assert np.array_equal(ops.gelu(hd).cpu().numpy(), O.gelu(hs.astype(np.float32)).astype(np.float16))
+    assert np.array_equal(ops.quantize(xd, 0.05).cpu().numpy(), O.quantize(xs, 0.05))
+    assert np.array_equal(ops.quantize(hd, 0.05, 3).cpu().numpy(), O.quantize(hs.astype(np.float32), 0.05, 3))
+    assert np.array_equal(ops.dequantize(qd, 0.05, 3).cpu().numpy(), O.dequantize(qs, 0.05, 3))
+    assert np.array_equal(ops.to_fp16(xd).cpu().numpy(), hs)
+    assert np.array_equal(ops.to_fp32(hd).cpu().numpy(), hs.astype(np.float32))
+    # unaligned OUTPUT through the C ABI: canaries on both sides of the view stay intact
+    from zenith_b200 import _capi
+    stream = torch.cuda.current_stream().cuda_stream
+    for dt, fn, src, want in ((torch.int8, "zen_quantize_f16", hd, O.quantize(hs.astype(np.float32), 0.05)),
+                              (torch.float16, "zen_gelu_f16", hd, O.gelu(hs.astype(np.float32)).astype(np.float16))):
+        buf = torch.full((n + off + 16,), 77, dtype=dt, device=cuda)
+        out = buf[off:off + n]
+        args = (src.data_ptr(), out.data_ptr(), n) + ((0.05, 0, 0) if dt == torch.int8 else ()) + (stream,)
+        _capi.call(fn, *args)
+        got = buf.cpu().numpy()
+        assert np.array_equal(got[off:off + n], want)
+        assert np.all(got[:off] == 77) and np.all(got[off + n:] == 77)
+    assert _capi.device_status() == 0
+
+
 def test_gelu_meets_reference_tolerance(cuda):
     # benchmarks/bert_encoder.py:264-309: max_diff < 1e-4 against PyTorch
     x = torch.linspace(-8, 8, 100001, device=cuda)

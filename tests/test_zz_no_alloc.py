@@ -4,8 +4,8 @@ Some users of this library cannot allocate: a plug-in invoked while a stream is 
 CUDA graph must not call cudaMalloc, and a kernel called through a dispatcher that passes only inputs
 and outputs has no channel for a workspace.  For them the library keeps the scratch (the transposed
 right operand) in a fixed 4 MiB array of its own on each GPU.  This test calls that entry point through
-the C ABI twice in a row (the array is shared and still holds the first call's data during the
-second) and compares each result with the workspace-taking entry point, which must agree bit for bit.
+the C ABI three times in a row, the largest shape first (the array is shared and still holds the earlier
+calls' data, beyond the region a smaller call rewrites, during the later ones) and compares each result with the workspace-taking entry point, which must agree bit for bit.
 The file name sorts last so that a run stopping at the first failure has already run every other test.
 """
 import ctypes
@@ -33,7 +33,9 @@ def test_static_scratch_matmul_matches_workspace_matmul(cuda):
     lib = _capi.lib()
     stream = torch.cuda.current_stream().cuda_stream
     gen = torch.Generator(device="cpu").manual_seed(5)
-    for (M, N, K) in [(200, 328, 260), (64, 1000, 512)]:  # two calls in a row, different shapes
+    # calls in a row on the shared array: a large shape, then a smaller one that rewrites only the head of
+    # the scratch (stale data from the first call stays behind it), then a different one again
+    for (M, N, K) in [(64, 1000, 512), (200, 328, 260), (96, 40, 24)]:
         a = torch.randn(M, K, generator=gen).to(cuda)
         b = (torch.randn(K, N, generator=gen) * 0.1).to(cuda)
         c = torch.full((M, N), float("nan"), dtype=torch.float32, device=cuda)

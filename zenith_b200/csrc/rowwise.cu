@@ -384,29 +384,43 @@ __device__ __forceinline__ TO ew_apply(TI xin, const EwParams& p, int64_t idx) {
   }
 }
 
-// Each thread handles VEC consecutive elements per step (16 bytes of the wider side).
+// Unsigned type of exactly BYTES bytes: the unit one thread moves per step.
+template <int BYTES> struct EwWord;
+template <> struct EwWord<1> { using type = uint8_t; };
+template <> struct EwWord<2> { using type = uint16_t; };
+template <> struct EwWord<4> { using type = uint32_t; };
+template <> struct EwWord<8> { using type = uint2; };
+template <> struct EwWord<16> { using type = uint4; };
+
+// Each thread handles VEC consecutive elements per step (16 bytes of the wider side).  VEC == 1 is the
+// form for pointers that are not 16-byte aligned: plain element accesses, which need only the natural
+// alignment of the element type.
 template <int OP, typename TI, typename TO, int VEC>
 __global__ void __launch_bounds__(256) ew_kernel(const EwParams p) {
   const TI* x = static_cast<const TI*>(p.x);
   TO* y = static_cast<TO*>(p.y);
   const int64_t nvec = p.n / VEC;
   const int64_t stride = int64_t(gridDim.x) * blockDim.x;
-  for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += stride) {
-    TI in[VEC];
-    TO out[VEC];
-    using VI = typename std::conditional<sizeof(TI) * VEC == 16, uint4,
-                                         typename std::conditional<sizeof(TI) * VEC == 8, uint2, uint32_t>::type>::type;
-    using VO = typename std::conditional<sizeof(TO) * VEC == 16, uint4,
-                                         typename std::conditional<sizeof(TO) * VEC == 8, uint2, uint32_t>::type>::type;
-    *reinterpret_cast<VI*>(in) = reinterpret_cast<const VI*>(x)[i];
+  if constexpr (VEC == 1) {
+    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < p.n; i += stride)
+      y[i] = ew_apply<OP, TI, TO>(x[i], p, i);
+  } else {
+    using VI = typename EwWord<sizeof(TI) * VEC>::type;
+    using VO = typename EwWord<sizeof(TO) * VEC>::type;
+    static_assert(sizeof(VI) == sizeof(TI) * VEC && sizeof(VO) == sizeof(TO) * VEC, "vector width");
+    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+      union { VI v; TI e[VEC]; } in;
+      union { VO v; TO e[VEC]; } out;
+      in.v = reinterpret_cast<const VI*>(x)[i];
 #pragma unroll
-    for (int j = 0; j < VEC; ++j) out[j] = ew_apply<OP, TI, TO>(in[j], p, i * VEC + j);
-    reinterpret_cast<VO*>(y)[i] = *reinterpret_cast<VO*>(out);
+      for (int j = 0; j < VEC; ++j) out.e[j] = ew_apply<OP, TI, TO>(in.e[j], p, i * VEC + j);
+      reinterpret_cast<VO*>(y)[i] = out.v;
+    }
+    // tail
+    const int64_t tail0 = nvec * VEC;
+    for (int64_t i = tail0 + int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < p.n; i += stride)
+      y[i] = ew_apply<OP, TI, TO>(x[i], p, i);
   }
-  // tail
-  const int64_t tail0 = nvec * VEC;
-  for (int64_t i = tail0 + int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < p.n; i += stride)
-    y[i] = ew_apply<OP, TI, TO>(x[i], p, i);
 }
 
 template <int OP, typename TI, typename TO>
