@@ -57,6 +57,14 @@ const char* zen_status_string(int status);
 int zen_device_status_read(int* status_host);
 int zen_device_status_clear(void);
 
+/* Self-test of the wait limit: one small CTA waits on a barrier that nothing signals, in a build of the wait
+ * loop whose limit is 1 ms.  The wait gives up by itself, the kernel returns normally and leaves
+ * ZEN_ERR_TIMEOUT in the device status word (read it with zen_device_status_read, reset it with
+ * zen_device_status_clear).  result3 (device, 3 x uint64, may be NULL): [0] = 1 if the first wait gave up,
+ * [1] = 1 if a second waiter of the same CTA left because the abort flag was up, [2] = nanoseconds spent.
+ * The reference has host-side fault injectors only (tests/chaos/gpu_chaos.py:143-250). */
+int zen_selftest_wait_limit(unsigned long long* result3, void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * W8A8 Linear:  acc[m,n] = sum_k xq[m,k] * wq[n,k]   (int32, exact, tcgen05 kind::i8)
  *   out_dtype S32 : out = acc
@@ -106,16 +114,36 @@ int zen_linear_f16_add_layernorm(const void* x, int64_t ldx, const void* w, int6
                                  const void* beta, float eps, void* y, int8_t* yq, float out_scale, int round_mode,
                                  void* stream);
 
-/* Tuning hook: force the GEMM tile width (64, 128, 192 or 256; 0 restores automatic selection).
- * Process-wide, not thread-safe; meant for benchmarks.  No counterpart in the reference. */
-int zen_gemm_set_tile_n(int tile_n);
+/* Per-call options: the `flags` argument of the *_ex entry points (0 = the behaviour of the plain forms).
+ * The library keeps no process-wide switches; every option travels with the call it applies to.
+ *   ZEN_GEMM_CONST_WEIGHTS  promise that the weight operand (wq / w) of THIS call is a constant: not written by
+ *                           any work that may still be running on the device when the call is made.  The kernel
+ *                           then requests the first weight tiles of each CTA before it waits for the kernel ahead
+ *                           of it in the stream (programmatic dependent launch), hiding their latency behind that
+ *                           kernel's tail.  Without the flag every operand is read after that wait, so a weight
+ *                           matrix produced by the preceding kernel in the stream is safe.  Applies to the int8 and
+ *                           the fp16 forms alike.
+ *   ZEN_GEMM_TILE_N(bn)     force the tile width (64, 128, 192 or 256; a width the kernel family lacks is ignored);
+ *                           a tuning hook for benchmarks.  Not accepted by the *_add_layernorm_ex forms.
+ * None of this has a counterpart in the reference. */
+#define ZEN_GEMM_CONST_WEIGHTS 0x1u
+#define ZEN_GEMM_TILE_N(bn) ((unsigned)(bn) << 8)
 
-/* Promise (1) or withdraw (0, the default) that the int8 weight operands given to zen_linear_i8,
- * zen_linear_i8_prefetch and zen_linear_i8_add_layernorm are constants: never written by work that may still
- * be running on the device when those calls are made.  With the promise a kernel requests the first weight
- * tiles of each CTA before it waits for the kernel ahead of it in the stream (programmatic dependent launch),
- * which hides their HBM latency behind that kernel's tail.  Process-wide.  No counterpart in the reference. */
-int zen_gemm_set_constant_weights(int on);
+/* zen_linear_i8_prefetch with per-call options. */
+int zen_linear_i8_ex(const int8_t* xq, int64_t ldx, const int8_t* wq, int64_t ldw, int M, int N, int K, float x_scale,
+                     const float* w_scale, const float* bias, int act, int out_dtype, float out_scale, int round_mode,
+                     void* out, int64_t ldo, const void* next0, size_t next0_bytes, const void* next1,
+                     size_t next1_bytes, unsigned flags, void* stream);
+
+/* zen_linear_i8_add_layernorm / zen_linear_f16_add_layernorm with per-call options (ZEN_GEMM_CONST_WEIGHTS). */
+int zen_linear_i8_add_layernorm_ex(const int8_t* xq, int64_t ldx, const int8_t* wq, int64_t ldw, int M, int N, int K,
+                                   float x_scale, const float* w_scale, const float* bias, const void* residual,
+                                   int64_t ldr, const void* gamma, const void* beta, float eps, void* y, int8_t* yq,
+                                   float out_scale, int round_mode, unsigned flags, void* stream);
+int zen_linear_f16_add_layernorm_ex(const void* x, int64_t ldx, const void* w, int64_t ldw, int M, int N, int K,
+                                    const float* bias, const void* residual, int64_t ldr, const void* gamma,
+                                    const void* beta, float eps, void* y, int8_t* yq, float out_scale, int round_mode,
+                                    unsigned flags, void* stream);
 
 /* FP16 Linear: y = x[M,K] . w[N,K]^T (+ bias[n], fp32) ; act ; out F16 or F32.  fp32 accumulate,
  * tcgen05 kind::f16.  K, ldx, ldw multiples of 8.
@@ -123,6 +151,9 @@ int zen_gemm_set_constant_weights(int on);
  * and zenith/runtime/triton_kernels.py:118-207 (fused Linear+GELU). */
 int zen_linear_f16(const void* x, int64_t ldx, const void* w, int64_t ldw, int M, int N, int K, const float* bias,
                    int act, int out_dtype, void* out, int64_t ldo, void* stream);
+/* ... with per-call options (see ZEN_GEMM_CONST_WEIGHTS, ZEN_GEMM_TILE_N). */
+int zen_linear_f16_ex(const void* x, int64_t ldx, const void* w, int64_t ldw, int M, int N, int K, const float* bias,
+                      int act, int out_dtype, void* out, int64_t ldo, unsigned flags, void* stream);
 
 /* FP32 Linear on the tensor cores in TF32: y = act(x[M,K] . w[N,K]^T + bias), fp32 in and out.
  * K, ldx, ldw multiples of 4.  Replaces cuda.linear_gpu = cublasSgemm (TF32 math mode) +

@@ -48,7 +48,9 @@ def test_argument_validation_needs_no_device():
     assert lib.zen_flash_attention_f16(one, one, one, one, z, 1.0, 1, 1, 8, 32, *([8] * 12), z, 0, 1.0, z) == _capi.ERR_UNSUPPORTED
     assert lib.zen_quantize_f32(one, one, 4, 0.0, 0, 0, z) == _capi.ERR_INVALID_ARG
     assert lib.zen_layernorm_f32(z, z, z, z, 4, 8, 1e-5, z) == _capi.ERR_INVALID_ARG
-    assert lib.zen_gemm_set_tile_n(100) == _capi.ERR_INVALID_ARG and lib.zen_gemm_set_tile_n(0) == 0
+    # per-call options: an unknown flag bit or tile width is rejected
+    ex = lambda flags: lib.zen_linear_i8_ex(one, 16, one, 16, 4, 4, 16, 1.0, z, z, 0, 0, 1.0, 0, one, 4, z, 0, z, 0, flags, z)
+    assert ex(0x2) == _capi.ERR_INVALID_ARG and ex(_capi.gemm_tile_n(100)) == _capi.ERR_INVALID_ARG
     # zero-sized work is a no-op, not an error
     assert lib.zen_gelu_f32(z, z, 0, z) == 0 and lib.zen_layernorm_f16(z, z, z, z, 0, 8, 1e-5, z) == 0
 

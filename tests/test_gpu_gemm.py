@@ -31,11 +31,7 @@ def dev(a, cuda):
 def test_int8_accumulators_bit_exact(cuda, M, N, K, tile):
     x = rng(M + N).integers(-128, 128, (M, K), dtype=np.int8)
     w = rng(K).integers(-128, 128, (N, K), dtype=np.int8)
-    ops.set_gemm_tile_n(tile)
-    try:
-        acc = ops.linear_int8(dev(x, cuda), dev(w, cuda), 1.0, out_dtype=torch.int32).cpu().numpy()
-    finally:
-        ops.set_gemm_tile_n(0)
+    acc = ops.linear_int8(dev(x, cuda), dev(w, cuda), 1.0, out_dtype=torch.int32, tile_n=tile).cpu().numpy()
     want = O.gemm_s8(x, w) if M * N * K <= 4e8 else (dev(x, cuda).double() @ dev(w, cuda).double().T).to(torch.int32).cpu().numpy()
     assert np.array_equal(acc, want)
 
@@ -86,7 +82,7 @@ def test_prefetch_hint_changes_nothing(cuda):
 
 
 def test_constant_weights_promise_changes_nothing(cuda):
-    """zen_gemm_set_constant_weights: with the promise the kernels request weight tiles before their dependency
+    """ZEN_GEMM_CONST_WEIGHTS: with the promise the kernels request weight tiles before their dependency
     wait; results are the same, for one tile per CTA and for several, plain and fused with LayerNorm."""
     for (M, N, K) in [(200, 520, 256), (4096, 3072, 768), (128, 768, 64)]:
         x = dev(rng(1).integers(-128, 128, (M, K), dtype=np.int8), cuda)
@@ -97,17 +93,35 @@ def test_constant_weights_promise_changes_nothing(cuda):
         g = torch.ones(768, dtype=torch.float16, device=cuda)
         outs = []
         for on in (False, True):
-            ops.set_constant_weights(on)
-            try:
-                o = [ops.linear_int8(x, w, 0.02, ws, None, **kw), ops.linear_int8(x, w, 0.02, ws, None, out_dtype=torch.float16)]
-                if N == 768:
-                    o += list(ops.linear_int8_add_layernorm(x, w, 0.02, ws, None, res, g, g, 1e-5, out_scale=0.03))
-            finally:
-                ops.set_constant_weights(False)
+            o = [ops.linear_int8(x, w, 0.02, ws, None, constant_weights=on, **kw),
+                 ops.linear_int8(x, w, 0.02, ws, None, out_dtype=torch.float16, constant_weights=on)]
+            if N == 768:
+                o += list(ops.linear_int8_add_layernorm(x, w, 0.02, ws, None, res, g, g, 1e-5, out_scale=0.03,
+                                                        constant_weights=on))
             outs.append(o)
         for a, b in zip(*outs):
             assert torch.equal(a, b)
     assert _capi.device_status() == 0
+
+
+def test_weights_written_by_the_previous_kernel_in_the_stream(cuda):
+    """Without the constant-weights promise every operand is read after the dependency wait: a GEMM whose
+    weight matrix is the int8 output of the GEMM launched just before it (same stream, programmatic dependent
+    launch in between, no synchronisation) is still bit-exact.  Also after an encoder object exists: building
+    one switches nothing process-wide."""
+    from zenith_b200.encoder import EncoderConfig, Int8Encoder, Int8Scales, init_params  # noqa: F401
+    M, N, K = 512, 768, 256
+    a = rng(1).integers(-128, 128, (N, 512), dtype=np.int8)
+    b = rng(2).integers(-20, 20, (K, 512), dtype=np.int8)
+    x = rng(3).integers(-128, 128, (M, K), dtype=np.int8)
+    ad, bd, xd = dev(a, cuda), dev(b, cuda), dev(x, cuda)
+    want_w = O.linear_int8(a, b, 1e-3, None, None, "none", "s8", 0.7)  # [N, K] int8
+    want = O.gemm_s8(x, want_w)
+    for _ in range(20):  # back to back, so the second launch really overlaps the first one's tail
+        wq = ops.linear_int8(ad, bd, 1e-3, out_dtype=torch.int8, out_scale=0.7)
+        acc = ops.linear_int8(xd, wq, 1.0, out_dtype=torch.int32)
+    assert np.array_equal(wq.cpu().numpy(), want_w)
+    assert np.array_equal(acc.cpu().numpy(), want)
 
 
 def test_int8_epilogue_trunc_rounding_and_no_scale_no_bias(cuda):

@@ -14,8 +14,14 @@ OK, ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_LAUNCH, ERR_TIMEOUT, ERR_DRIVER, ERR_T
 DT_S32, DT_F32, DT_F16, DT_S8 = range(4)
 ACT_NONE, ACT_GELU, ACT_RELU = range(3)
 ROUND_NEAREST_EVEN, ROUND_TRUNC = range(2)
+GEMM_CONST_WEIGHTS = 0x1
 
-_p, _i, _f, _i64 = C.c_void_p, C.c_int, C.c_float, C.c_int64
+
+def gemm_tile_n(bn: int) -> int:
+    """``ZEN_GEMM_TILE_N(bn)``: the flag bits that force a GEMM tile width (0 = automatic)."""
+    return int(bn) << 8
+
+_p, _i, _f, _i64, _u = C.c_void_p, C.c_int, C.c_float, C.c_int64, C.c_uint
 
 # name -> argument types; every function returns int unless listed in _RESTYPES
 SIGNATURES = {
@@ -23,11 +29,16 @@ SIGNATURES = {
     "zen_status_string": [_i],
     "zen_device_status_read": [C.POINTER(C.c_int)],
     "zen_device_status_clear": [],
-    "zen_gemm_set_tile_n": [_i],
-    "zen_gemm_set_constant_weights": [_i],
+    "zen_selftest_wait_limit": [_p, _p],
     "zen_linear_i8": [_p, _i64, _p, _i64, _i, _i, _i, _f, _p, _p, _i, _i, _f, _i, _p, _i64, _p],
     "zen_linear_i8_prefetch": [_p, _i64, _p, _i64, _i, _i, _i, _f, _p, _p, _i, _i, _f, _i, _p, _i64, _p, C.c_size_t, _p,
                                C.c_size_t, _p],
+    "zen_linear_i8_ex": [_p, _i64, _p, _i64, _i, _i, _i, _f, _p, _p, _i, _i, _f, _i, _p, _i64, _p, C.c_size_t, _p, C.c_size_t,
+                         _u, _p],
+    "zen_linear_i8_add_layernorm_ex": [_p, _i64, _p, _i64, _i, _i, _i, _f, _p, _p, _p, _i64, _p, _p, _f, _p, _p, _f, _i, _u,
+                                       _p],
+    "zen_linear_f16_add_layernorm_ex": [_p, _i64, _p, _i64, _i, _i, _i, _p, _p, _i64, _p, _p, _f, _p, _p, _f, _i, _u, _p],
+    "zen_linear_f16_ex": [_p, _i64, _p, _i64, _i, _i, _i, _p, _i, _i, _p, _i64, _u, _p],
     "zen_linear_i8_add_layernorm": [_p, _i64, _p, _i64, _i, _i, _i, _f, _p, _p, _p, _i64, _p, _p, _f, _p, _p, _f, _i, _p],
     "zen_linear_f16_add_layernorm": [_p, _i64, _p, _i64, _i, _i, _i, _p, _p, _i64, _p, _p, _f, _p, _p, _f, _i, _p],
     "zen_linear_f16": [_p, _i64, _p, _i64, _i, _i, _i, _p, _i, _i, _p, _i64, _p],

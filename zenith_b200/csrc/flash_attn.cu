@@ -104,12 +104,13 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   const int h = blockIdx.y;
   const int b = blockIdx.z;
 
-  int kv_len = p.kv_lens ? p.kv_lens[b] : p.S;
-  kv_len = kv_len < 0 ? 0 : (kv_len > p.S ? p.S : kv_len);
-  int kv_end = kv_len;
-  if (p.causal && q0 + FA_BQ < kv_end) kv_end = q0 + FA_BQ;
-  const bool any_keys = kv_end > 0;
-  const int k_cols = ((min(kv_end, FA_BKV) + 15) / 16) * 16;  // columns of P the P V product reads
+  // The key length may be produced by the kernel ahead in the stream.  When this kernel family is launched
+  // with programmatic dependent launch it is therefore read after the dependency wait; otherwise the launch
+  // itself orders it and the load is issued here, where the set-up below hides its latency.
+  int kv_len = p.S;
+  if constexpr (!kAttentionLaunchesEarly) {
+    if (p.kv_lens) kv_len = p.kv_lens[b];
+  }
 
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tmap_q);
@@ -136,6 +137,14 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   const uint32_t tmem_o = tmem_s;
   grid_launch_dependents();
   grid_dependency_wait();  // Q, K, V and the output buffers may belong to the previous kernel until here
+  if constexpr (kAttentionLaunchesEarly) {
+    if (p.kv_lens) kv_len = p.kv_lens[b];
+  }
+  kv_len = kv_len < 0 ? 0 : (kv_len > p.S ? p.S : kv_len);
+  int kv_end = kv_len;
+  if (p.causal && q0 + FA_BQ < kv_end) kv_end = q0 + FA_BQ;
+  const bool any_keys = kv_end > 0;
+  const int k_cols = ((min(kv_end, FA_BKV) + 15) / 16) * 16;  // columns of P the P V product reads
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer

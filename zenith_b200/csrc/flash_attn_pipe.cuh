@@ -61,17 +61,11 @@ flash_attn_pipe_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
   const int h = blockIdx.y;
   const int b = blockIdx.z;
 
-  int kv_len = p.kv_lens ? p.kv_lens[b] : p.S;
-  kv_len = kv_len < 0 ? 0 : (kv_len > p.S ? p.S : kv_len);
-  // key blocks needed by each group (group B has no rows if the sequence ends before its tile)
-  int nblk[2];
-#pragma unroll
-  for (int g = 0; g < 2; ++g) {
-    int end = kv_len;
-    if (p.causal && q0 + g * 128 + 128 < end) end = q0 + g * 128 + 128;
-    nblk[g] = (q0 + g * 128 < p.S) ? (end + 127) / 128 : 0;
+  // see flash_attn_kernel: the key length is read after the dependency wait when this family launches early
+  int kv_len = p.S;
+  if constexpr (!kAttentionLaunchesEarly) {
+    if (p.kv_lens) kv_len = p.kv_lens[b];
   }
-  const int n_blocks = nblk[0] > nblk[1] ? nblk[0] : nblk[1];
 
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tmap_q);
@@ -102,6 +96,19 @@ flash_attn_pipe_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
   const uint32_t tmem_base = *tmem_slot;
   grid_launch_dependents();
   grid_dependency_wait();
+  if constexpr (kAttentionLaunchesEarly) {
+    if (p.kv_lens) kv_len = p.kv_lens[b];
+  }
+  kv_len = kv_len < 0 ? 0 : (kv_len > p.S ? p.S : kv_len);
+  // key blocks needed by each group (group B has no rows if the sequence ends before its tile)
+  int nblk[2];
+#pragma unroll
+  for (int g = 0; g < 2; ++g) {
+    int end = kv_len;
+    if (p.causal && q0 + g * 128 + 128 < end) end = q0 + g * 128 + 128;
+    nblk[g] = (q0 + g * 128 < p.S) ? (end + 127) / 128 : 0;
+  }
+  const int n_blocks = nblk[0] > nblk[1] ? nblk[0] : nblk[1];
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer

@@ -5,13 +5,13 @@
 
 namespace zen {
 
-static int g_tile_n_override = 0;
-
-// Smallest estimated time: waves of persistent CTAs x (tile width + fixed per-tile cost).
-static int pick_bn(int M, int N, const int* allowed, int n_allowed) {
-  if (g_tile_n_override) {
+// Smallest estimated time: waves of persistent CTAs x (tile width + fixed per-tile cost).  `flags` may carry a
+// forced width (ZEN_GEMM_TILE_N); a width the kernel family does not have is ignored.
+static int pick_bn(int M, int N, const int* allowed, int n_allowed, unsigned flags) {
+  const int forced = int((flags >> 8) & 0x3ffu);
+  if (forced) {
     for (int i = 0; i < n_allowed; ++i)
-      if (allowed[i] == g_tile_n_override) return g_tile_n_override;
+      if (allowed[i] == forced) return forced;
   }
   const int sms = num_sms();
   const int tiles_m = (M + GEMM_BM - 1) / GEMM_BM;
@@ -125,29 +125,32 @@ const char* zen_status_string(int s) {
   }
 }
 
-int zen_gemm_set_tile_n(int bn) {
-  if (bn != 0 && bn != 64 && bn != 128 && bn != 192 && bn != 256) return ZEN_ERR_INVALID_ARG;
-  g_tile_n_override = bn;
-  return ZEN_OK;
-}
-
-int zen_gemm_set_constant_weights(int on) {
-  constant_weights_flag().store(on ? 1 : 0, std::memory_order_relaxed);
-  return ZEN_OK;
+static bool flags_ok(unsigned flags) {
+  const unsigned bn = (flags >> 8) & 0x3ffu;
+  if (flags & ~(ZEN_GEMM_CONST_WEIGHTS | (0x3ffu << 8))) return false;
+  return bn == 0 || bn == 64 || bn == 128 || bn == 192 || bn == 256;
 }
 
 int zen_linear_i8(const int8_t* xq, int64_t ldx, const int8_t* wq, int64_t ldw, int M, int N, int K, float x_scale,
                   const float* w_scale, const float* bias, int act, int out_dtype, float out_scale, int round_mode,
                   void* out, int64_t ldo, void* stream) {
-  return zen_linear_i8_prefetch(xq, ldx, wq, ldw, M, N, K, x_scale, w_scale, bias, act, out_dtype, out_scale,
-                                round_mode, out, ldo, nullptr, 0, nullptr, 0, stream);
+  return zen_linear_i8_ex(xq, ldx, wq, ldw, M, N, K, x_scale, w_scale, bias, act, out_dtype, out_scale, round_mode, out,
+                          ldo, nullptr, 0, nullptr, 0, 0u, stream);
 }
 
 int zen_linear_i8_prefetch(const int8_t* xq, int64_t ldx, const int8_t* wq, int64_t ldw, int M, int N, int K,
                            float x_scale, const float* w_scale, const float* bias, int act, int out_dtype,
                            float out_scale, int round_mode, void* out, int64_t ldo, const void* next0,
                            size_t next0_bytes, const void* next1, size_t next1_bytes, void* stream) {
-  if (!xq || !wq || !out || M <= 0 || N <= 0 || K <= 0) return ZEN_ERR_INVALID_ARG;
+  return zen_linear_i8_ex(xq, ldx, wq, ldw, M, N, K, x_scale, w_scale, bias, act, out_dtype, out_scale, round_mode, out,
+                          ldo, next0, next0_bytes, next1, next1_bytes, 0u, stream);
+}
+
+int zen_linear_i8_ex(const int8_t* xq, int64_t ldx, const int8_t* wq, int64_t ldw, int M, int N, int K, float x_scale,
+                     const float* w_scale, const float* bias, int act, int out_dtype, float out_scale, int round_mode,
+                     void* out, int64_t ldo, const void* next0, size_t next0_bytes, const void* next1,
+                     size_t next1_bytes, unsigned flags, void* stream) {
+  if (!xq || !wq || !out || M <= 0 || N <= 0 || K <= 0 || !flags_ok(flags)) return ZEN_ERR_INVALID_ARG;
   if ((next0_bytes != 0 && !next0) || (next1_bytes != 0 && !next1)) return ZEN_ERR_INVALID_ARG;
   if (out_dtype < ZEN_DT_S32 || out_dtype > ZEN_DT_S8 || act < ZEN_ACT_NONE || act > ZEN_ACT_RELU)
     return ZEN_ERR_INVALID_ARG;
@@ -158,7 +161,7 @@ int zen_linear_i8_prefetch(const int8_t* xq, int64_t ldx, const int8_t* wq, int6
   p.M = M; p.N = N; p.K = K;
   p.out = out; p.ldo = ldo; p.out_dtype = out_dtype; p.act = act; p.round_mode = round_mode;
   p.x_scale = x_scale; p.out_scale = out_scale; p.w_scale = w_scale; p.bias = bias;
-  p.early_b = constant_weights_flag().load(std::memory_order_relaxed) ? 1 : 0;
+  p.early_b = (flags & ZEN_GEMM_CONST_WEIGHTS) ? 1 : 0;
   const void* next[2] = {next0, next1};
   const size_t next_bytes[2] = {next0_bytes, next1_bytes};
   for (int i = 0; i < 2; ++i) {
@@ -172,7 +175,7 @@ int zen_linear_i8_prefetch(const int8_t* xq, int64_t ldx, const int8_t* wq, int6
   }
   static const int allowed[] = {64, 128, 192, 256};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  switch (pick_bn(M, N, allowed, 4)) {
+  switch (pick_bn(M, N, allowed, 4, flags)) {
     case 64: return run_gemm<KIND_I8, 64, 7, false>(xq, ldx, wq, ldw, p, s);
     case 128: return run_gemm<KIND_I8, 128, 5, false>(xq, ldx, wq, ldw, p, s);
     case 192: return run_gemm<KIND_I8, 192, 4, false>(xq, ldx, wq, ldw, p, s);
@@ -182,7 +185,12 @@ int zen_linear_i8_prefetch(const int8_t* xq, int64_t ldx, const int8_t* wq, int6
 
 int zen_linear_f16(const void* x, int64_t ldx, const void* w, int64_t ldw, int M, int N, int K, const float* bias,
                    int act, int out_dtype, void* out, int64_t ldo, void* stream) {
-  if (!x || !w || !out || M <= 0 || N <= 0 || K <= 0) return ZEN_ERR_INVALID_ARG;
+  return zen_linear_f16_ex(x, ldx, w, ldw, M, N, K, bias, act, out_dtype, out, ldo, 0u, stream);
+}
+
+int zen_linear_f16_ex(const void* x, int64_t ldx, const void* w, int64_t ldw, int M, int N, int K, const float* bias,
+                      int act, int out_dtype, void* out, int64_t ldo, unsigned flags, void* stream) {
+  if (!x || !w || !out || M <= 0 || N <= 0 || K <= 0 || !flags_ok(flags)) return ZEN_ERR_INVALID_ARG;
   if ((out_dtype != ZEN_DT_F32 && out_dtype != ZEN_DT_F16) || act < ZEN_ACT_NONE || act > ZEN_ACT_RELU)
     return ZEN_ERR_INVALID_ARG;
   if (K % 8 || ldx % 8 || ldw % 8 || ldx < K || ldw < K || ldo < N) return ZEN_ERR_UNSUPPORTED;
@@ -190,9 +198,10 @@ int zen_linear_f16(const void* x, int64_t ldx, const void* w, int64_t ldw, int M
   p.M = M; p.N = N; p.K = K;
   p.out = out; p.ldo = ldo; p.out_dtype = out_dtype; p.act = act;
   p.x_scale = 1.0f; p.out_scale = 1.0f; p.w_scale = nullptr; p.bias = bias;
+  p.early_b = (flags & ZEN_GEMM_CONST_WEIGHTS) ? 1 : 0;
   static const int allowed[] = {64, 128, 192, 256};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  switch (pick_bn(M, N, allowed, 4)) {
+  switch (pick_bn(M, N, allowed, 4, flags)) {
     case 64: return run_gemm<KIND_F16, 64, 7, false>(x, ldx, w, ldw, p, s);
     case 128: return run_gemm<KIND_F16, 128, 5, false>(x, ldx, w, ldw, p, s);
     case 192: return run_gemm<KIND_F16, 192, 4, false>(x, ldx, w, ldw, p, s);
@@ -211,7 +220,7 @@ int zen_linear_f32(const float* x, int64_t ldx, const float* w, int64_t ldw, int
   p.x_scale = 1.0f; p.out_scale = 1.0f; p.w_scale = nullptr; p.bias = bias;
   static const int allowed[] = {64, 128, 256};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  switch (pick_bn(M, N, allowed, 3)) {
+  switch (pick_bn(M, N, allowed, 3, 0u)) {
     case 64: return run_gemm<KIND_TF32, 64, 7, false>(x, ldx, w, ldw, p, s);
     case 128: return run_gemm<KIND_TF32, 128, 5, false>(x, ldx, w, ldw, p, s);
     default: return run_gemm<KIND_TF32, 256, 3, false>(x, ldx, w, ldw, p, s);
@@ -227,7 +236,7 @@ int zen_wmma_matmul_f16(const void* A, const void* B, float* C, int M, int N, in
   p.x_scale = 1.0f; p.out_scale = 1.0f;
   static const int allowed[] = {64, 128, 256};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  switch (pick_bn(M, N, allowed, 3)) {
+  switch (pick_bn(M, N, allowed, 3, 0u)) {
     case 64: return run_gemm<KIND_F16, 64, 7, true>(A, K, B, N, p, s);
     case 128: return run_gemm<KIND_F16, 128, 5, true>(A, K, B, N, p, s);
     default: return run_gemm<KIND_F16, 256, 3, true>(A, K, B, N, p, s);

@@ -543,11 +543,12 @@ template <int KIND>
 static int run_linear_add_layernorm(const void* x, int64_t ldx, const void* w, int64_t ldw, int M, int N, int K, float x_scale,
                                     const float* w_scale, const float* bias, const void* residual, int64_t ldr,
                                     const void* gamma, const void* beta, float eps, void* y, int8_t* yq, float out_scale,
-                                    int round_mode, void* stream) {
+                                    int round_mode, unsigned flags, void* stream) {
   constexpr int ELEM = GemmKind<KIND>::ELEM;  // bytes per operand element
   constexpr int KA = 16 / ELEM;               // elements per 16 bytes: the unit K and the row strides must be a multiple of
   if (!x || !w || !residual || !gamma || !beta || !y || M <= 0 || N <= 0 || K <= 0) return ZEN_ERR_INVALID_ARG;
   if (round_mode != ZEN_ROUND_NEAREST_EVEN && round_mode != ZEN_ROUND_TRUNC) return ZEN_ERR_INVALID_ARG;
+  if (flags & ~unsigned(ZEN_GEMM_CONST_WEIGHTS)) return ZEN_ERR_INVALID_ARG;
   if (yq && !(out_scale > 0.0f)) return ZEN_ERR_INVALID_ARG;
   if (N != 768 && N != 1024) return ZEN_ERR_UNSUPPORTED;  // four CTAs x 192 (or 256) columns hold one row
   if (K % KA || ldx % KA || ldw % KA || ldx < K || ldw < K || ldr % 8 || ldr < N) return ZEN_ERR_UNSUPPORTED;
@@ -565,7 +566,7 @@ static int run_linear_add_layernorm(const void* x, int64_t ldx, const void* w, i
   p.residual = static_cast<const __half*>(residual); p.ldr = ldr;
   p.gamma = static_cast<const __half*>(gamma); p.beta = static_cast<const __half*>(beta);
   p.emit_q = yq ? 1 : 0;
-  p.early_b = constant_weights_flag().load(std::memory_order_relaxed) ? 1 : 0;
+  p.early_b = (flags & ZEN_GEMM_CONST_WEIGHTS) ? 1 : 0;
   const CUtensorMapDataType dt = KIND == KIND_I8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   CUtensorMap ta, tb, ty, tq, tr;
   int st = encode_tmap_2d(&ta, dt, x, uint64_t(K), uint64_t(M), uint64_t(ldx) * ELEM, BK, GEMM_BM);
@@ -585,13 +586,30 @@ static int run_linear_add_layernorm(const void* x, int64_t ldx, const void* w, i
   return launch_gemm_ln<KIND, 256, 2>(ta, tb, ty, tq, tr, p, static_cast<cudaStream_t>(stream));
 }
 
+extern "C" int zen_linear_i8_add_layernorm_ex(const int8_t* xq, int64_t ldx, const int8_t* wq, int64_t ldw, int M, int N,
+                                              int K, float x_scale, const float* w_scale, const float* bias,
+                                              const void* residual, int64_t ldr, const void* gamma, const void* beta,
+                                              float eps, void* y, int8_t* yq, float out_scale, int round_mode,
+                                              unsigned flags, void* stream) {
+  return run_linear_add_layernorm<KIND_I8>(xq, ldx, wq, ldw, M, N, K, x_scale, w_scale, bias, residual, ldr, gamma, beta, eps,
+                                           y, yq, out_scale, round_mode, flags, stream);
+}
+
 extern "C" int zen_linear_i8_add_layernorm(const int8_t* xq, int64_t ldx, const int8_t* wq, int64_t ldw, int M, int N,
                                            int K, float x_scale, const float* w_scale, const float* bias,
                                            const void* residual, int64_t ldr, const void* gamma, const void* beta,
                                            float eps, void* y, int8_t* yq, float out_scale, int round_mode,
                                            void* stream) {
   return run_linear_add_layernorm<KIND_I8>(xq, ldx, wq, ldw, M, N, K, x_scale, w_scale, bias, residual, ldr, gamma, beta, eps,
-                                           y, yq, out_scale, round_mode, stream);
+                                           y, yq, out_scale, round_mode, 0u, stream);
+}
+
+extern "C" int zen_linear_f16_add_layernorm_ex(const void* x, int64_t ldx, const void* w, int64_t ldw, int M, int N, int K,
+                                               const float* bias, const void* residual, int64_t ldr, const void* gamma,
+                                               const void* beta, float eps, void* y, int8_t* yq, float out_scale,
+                                               int round_mode, unsigned flags, void* stream) {
+  return run_linear_add_layernorm<KIND_F16>(x, ldx, w, ldw, M, N, K, 1.0f, nullptr, bias, residual, ldr, gamma, beta, eps, y,
+                                            yq, out_scale, round_mode, flags, stream);
 }
 
 extern "C" int zen_linear_f16_add_layernorm(const void* x, int64_t ldx, const void* w, int64_t ldw, int M, int N, int K,
@@ -599,5 +617,5 @@ extern "C" int zen_linear_f16_add_layernorm(const void* x, int64_t ldx, const vo
                                             const void* beta, float eps, void* y, int8_t* yq, float out_scale,
                                             int round_mode, void* stream) {
   return run_linear_add_layernorm<KIND_F16>(x, ldx, w, ldw, M, N, K, 1.0f, nullptr, bias, residual, ldr, gamma, beta, eps, y,
-                                            yq, out_scale, round_mode, stream);
+                                            yq, out_scale, round_mode, 0u, stream);
 }

@@ -6,11 +6,12 @@ int zen_tu_status_gemm(int* out, int clear);
 int zen_tu_status_rowwise(int* out, int clear);
 int zen_tu_status_flash_attn(int* out, int clear);
 int zen_tu_status_gemm_ln(int* out, int clear);
+int zen_tu_status_selftest(int* out, int clear);
 }
 
 typedef int (*TuStatusFn)(int*, int);
 static const TuStatusFn kTuStatus[] = {zen_tu_status_gemm, zen_tu_status_rowwise, zen_tu_status_flash_attn,
-                                        zen_tu_status_gemm_ln};
+                                        zen_tu_status_gemm_ln, zen_tu_status_selftest};
 
 static int fold_status(int* out, int clear) {
   if (cudaDeviceSynchronize() != cudaSuccess) {

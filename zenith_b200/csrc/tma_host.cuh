@@ -2,15 +2,14 @@
 // CUDA runtime so that the library links against cudart only and loads on a machine without
 // a driver (where every compute entry point then fails with ZEN_ERR_DRIVER / ZEN_ERR_LAUNCH).
 #pragma once
-#include <atomic>
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
-#include <stdlib.h>
 #include <utility>
 #include <mutex>
 #include <set>
 #include "../../include/zenith_b200.h"
+#include "zen_common.cuh"
 
 namespace zen {
 
@@ -65,27 +64,13 @@ inline int encode_tmap_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* 
   return encode_tmap(map, dt, 2, base, dims, str, box, swizzle);
 }
 
-// Promise of the host (zen_gemm_set_constant_weights): the weight operand of the int8 linear entry points is
-// never written by work that may still be running when they are launched, so a kernel may request its
-// first weight tiles before it waits for its predecessor.  One flag for the whole library.
-inline std::atomic<int>& constant_weights_flag() {
-  static std::atomic<int> flag{0};
-  return flag;
-}
-
 // Launch with the programmatic-stream-serialization attribute (see grid_dependency_wait()).  Only for
-// kernels that execute grid_dependency_wait() before touching global data.  `family` selects the bit
-// of ZEN_PDL_MASK (environment, default: GEMM only) that enables the attribute: 1 = GEMM, 2 = attention,
-// 4 = row kernels.  Early launch pays off for the GEMMs (long set-up, one CTA per SM); for the short
-// row kernels the early-resident CTAs only got in the way (measured: 7.1 vs 5.9 us per LayerNorm).
-enum { PDL_GEMM = 1, PDL_ATTENTION = 2, PDL_ROW = 4 };
-inline int pdl_mask() {
-  static int mask = []() {
-    const char* e = getenv("ZEN_PDL_MASK");
-    return e ? atoi(e) : int(PDL_GEMM);
-  }();
-  return mask;
-}
+// kernels that execute grid_dependency_wait() before touching global data.  `family` is tested against
+// ZEN_PDL_FAMILIES, a build-time constant (1 = GEMM, 2 = attention, 4 = row kernels; default: GEMM only).
+// Early launch pays off for the GEMMs (long set-up, one CTA per SM); for the short row kernels the
+// early-resident CTAs only got in the way (measured: 7.1 vs 5.9 us per LayerNorm).
+// (the constant and the family bits live in zen_common.cuh, where the kernels see them too)
+constexpr int pdl_mask() { return ZEN_PDL_FAMILIES; }
 
 template <typename... KArgs, typename... Args>
 inline int launch_pdl(int family, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,

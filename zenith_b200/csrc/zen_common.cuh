@@ -73,6 +73,13 @@ __device__ __forceinline__ bool elect_one() {
 // returns once the predecessor has completed and its writes are visible; nothing that reads or
 // writes global data shared with the predecessor may precede it.
 // ---------------------------------------------------------------------------
+// Kernel families launched with the programmatic-stream-serialization attribute: a build-time constant.
+enum { PDL_GEMM = 1, PDL_ATTENTION = 2, PDL_ROW = 4 };
+#ifndef ZEN_PDL_FAMILIES
+#define ZEN_PDL_FAMILIES 1
+#endif
+constexpr bool kAttentionLaunchesEarly = (ZEN_PDL_FAMILIES & PDL_ATTENTION) != 0;
+
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 

@@ -27,7 +27,7 @@ import numpy as np
 import torch
 
 from . import _capi, ops
-from ._capi import ACT_GELU, ACT_NONE, DT_F16, DT_S8, ROUND_NEAREST_EVEN
+from ._capi import ACT_GELU, ACT_NONE, DT_F16, DT_S8, GEMM_CONST_WEIGHTS, ROUND_NEAREST_EVEN
 
 
 @dataclass
@@ -223,7 +223,6 @@ class Fp16Encoder(_EncoderBase):
         if self.fuse_layernorm and cfg.hidden not in (768, 1024):
             raise RuntimeError("the fused GEMM + LayerNorm kernel needs hidden == 768 or 1024")
         self.launches_per_layer = 5 if self.fuse_layernorm else 7
-        ops.set_constant_weights(True)  # the weights below are written once, here
         d = self.device
         self.layers = []
         for lp in params["layers"]:
@@ -252,6 +251,9 @@ class Fp16Encoder(_EncoderBase):
         T, H, F, nh, hd = B * S, cfg.hidden, cfg.ffn, cfg.heads, cfg.head_dim
         r0 = b0 * S
         P = lambda t: _row_ptr(t, r0)
+        # the weights of this object are written once, in __init__: every GEMM of the launch list carries the
+        # constant-weights promise for its own call (nothing process-wide is switched)
+        CW = GEMM_CONST_WEIGHTS
         self._add("zen_embed_layernorm_f16", P(self.ids), None, self.word.data_ptr(), self.pos.data_ptr(),
                   self.type.data_ptr(), self.emb_g.data_ptr(), self.emb_b.data_ptr(), P(self.x[0]), None, 1.0,
                   ROUND_NEAREST_EVEN, T, S, H, cfg.vocab, cfg.eps)
@@ -261,28 +263,28 @@ class Fp16Encoder(_EncoderBase):
         cur = 0
         for L in self.layers:
             x, xn = self.x[cur], self.x[cur ^ 1]
-            self._add("zen_linear_f16", P(x), H, L["wqkv"].data_ptr(), H, T, 3 * H, H, L["bqkv"].data_ptr(),
-                      ACT_NONE, DT_F16, P(self.qkv), 3 * H)
+            self._add("zen_linear_f16_ex", P(x), H, L["wqkv"].data_ptr(), H, T, 3 * H, H, L["bqkv"].data_ptr(),
+                      ACT_NONE, DT_F16, P(self.qkv), 3 * H, CW)
             self._add("zen_flash_attention_f16", P(self.qkv), P(self.qkv) + 2 * H, P(self.qkv) + 4 * H, P(self.ctx), None,
                       1.0, B, nh, S, hd, *qs, *qs, *qs, *os_, kv, 0, 1.0 / math.sqrt(hd))
             if self.fuse_layernorm:
-                self._add("zen_linear_f16_add_layernorm", P(self.ctx), H, L["wo"].data_ptr(), H, T, H, H, L["bo"].data_ptr(),
-                          P(x), H, L["ln1_g"].data_ptr(), L["ln1_b"].data_ptr(), cfg.eps, P(self.h1), None, 1.0,
-                          ROUND_NEAREST_EVEN)
+                self._add("zen_linear_f16_add_layernorm_ex", P(self.ctx), H, L["wo"].data_ptr(), H, T, H, H,
+                          L["bo"].data_ptr(), P(x), H, L["ln1_g"].data_ptr(), L["ln1_b"].data_ptr(), cfg.eps, P(self.h1),
+                          None, 1.0, ROUND_NEAREST_EVEN, CW)
             else:
-                self._add("zen_linear_f16", P(self.ctx), H, L["wo"].data_ptr(), H, T, H, H, L["bo"].data_ptr(),
-                          ACT_NONE, DT_F16, P(self.ao), H)
+                self._add("zen_linear_f16_ex", P(self.ctx), H, L["wo"].data_ptr(), H, T, H, H, L["bo"].data_ptr(),
+                          ACT_NONE, DT_F16, P(self.ao), H, CW)
                 self._add("zen_add_layernorm_f16", P(self.ao), P(x), L["ln1_g"].data_ptr(), L["ln1_b"].data_ptr(),
                           P(self.h1), None, 1.0, ROUND_NEAREST_EVEN, T, H, cfg.eps)
-            self._add("zen_linear_f16", P(self.h1), H, L["w1"].data_ptr(), H, T, F, H, L["b1"].data_ptr(),
-                      ACT_GELU, DT_F16, P(self.g), F)
+            self._add("zen_linear_f16_ex", P(self.h1), H, L["w1"].data_ptr(), H, T, F, H, L["b1"].data_ptr(),
+                      ACT_GELU, DT_F16, P(self.g), F, CW)
             if self.fuse_layernorm:
-                self._add("zen_linear_f16_add_layernorm", P(self.g), F, L["w2"].data_ptr(), F, T, H, F, L["b2"].data_ptr(),
-                          P(self.h1), H, L["ln2_g"].data_ptr(), L["ln2_b"].data_ptr(), cfg.eps, P(xn), None, 1.0,
-                          ROUND_NEAREST_EVEN)
+                self._add("zen_linear_f16_add_layernorm_ex", P(self.g), F, L["w2"].data_ptr(), F, T, H, F,
+                          L["b2"].data_ptr(), P(self.h1), H, L["ln2_g"].data_ptr(), L["ln2_b"].data_ptr(), cfg.eps, P(xn),
+                          None, 1.0, ROUND_NEAREST_EVEN, CW)
             else:
-                self._add("zen_linear_f16", P(self.g), F, L["w2"].data_ptr(), F, T, H, F, L["b2"].data_ptr(),
-                          ACT_NONE, DT_F16, P(self.o), H)
+                self._add("zen_linear_f16_ex", P(self.g), F, L["w2"].data_ptr(), F, T, H, F, L["b2"].data_ptr(),
+                          ACT_NONE, DT_F16, P(self.o), H, CW)
                 self._add("zen_add_layernorm_f16", P(self.o), P(self.h1), L["ln2_g"].data_ptr(), L["ln2_b"].data_ptr(),
                           P(xn), None, 1.0, ROUND_NEAREST_EVEN, T, H, cfg.eps)
             cur ^= 1
@@ -370,8 +372,6 @@ class Int8Encoder(_EncoderBase):
         # next layer's QKV weights (zen_linear_i8_prefetch): a pass's weights do not stay in L2 beside
         # the activations, and a GEMM that starts on HBM-cold weights loses about a microsecond.
         self.prefetch_weights = bool(prefetch_weights)
-        # the int8 weights below are written once, here: the GEMMs may fetch them ahead of their dependency wait
-        ops.set_constant_weights(True)
         d = self.device
         self.act_scales = scales.act
         self.layers = []
@@ -407,6 +407,9 @@ class Int8Encoder(_EncoderBase):
         T, H, F, nh, hd = B * S, cfg.hidden, cfg.ffn, cfg.heads, cfg.head_dim
         r0 = b0 * S
         P = lambda t: _row_ptr(t, r0)
+        # the weights of this object are written once, in __init__: every GEMM of the launch list carries the
+        # constant-weights promise for its own call (nothing process-wide is switched)
+        CW = GEMM_CONST_WEIGHTS
         sc = self.act_scales
         self._add("zen_embed_layernorm_f16", P(self.ids), None, self.word.data_ptr(), self.pos.data_ptr(),
                   self.type.data_ptr(), self.emb_g.data_ptr(), self.emb_b.data_ptr(), P(self.x[0]), P(self.xq[0]),
@@ -423,33 +426,33 @@ class Int8Encoder(_EncoderBase):
             nbytes = lambda t: t.numel() * t.element_size()
             pf = lambda *ts: [v for t in ts for v in ((t.data_ptr(), nbytes(t)) if self.prefetch_weights and t is not None
                                                        else (None, 0))]
-            self._add("zen_linear_i8_prefetch", P(xq), H, L["wqkv"].data_ptr(), H, T, 3 * H, H, a["x"],
+            self._add("zen_linear_i8_ex", P(xq), H, L["wqkv"].data_ptr(), H, T, 3 * H, H, a["x"],
                       L["wqkv_s"].data_ptr(), L["bqkv"].data_ptr(), ACT_NONE, DT_F16, 1.0, ROUND_NEAREST_EVEN,
-                      P(self.qkv), 3 * H, *pf(L["wo"], L["w1"]))
+                      P(self.qkv), 3 * H, *pf(L["wo"], L["w1"]), CW)
             self._add("zen_flash_attention_f16", P(self.qkv), P(self.qkv) + 2 * H, P(self.qkv) + 4 * H, P(self.ctx),
                       P(self.ctxq), a["ctx"], B, nh, S, hd, *qs, *qs, *qs, *os_, kv, 0, 1.0 / math.sqrt(hd))
             if self.fuse_layernorm:
-                self._add("zen_linear_i8_add_layernorm", P(self.ctxq), H, L["wo"].data_ptr(), H, T, H, H, a["ctx"],
+                self._add("zen_linear_i8_add_layernorm_ex", P(self.ctxq), H, L["wo"].data_ptr(), H, T, H, H, a["ctx"],
                           L["wo_s"].data_ptr(), L["bo"].data_ptr(), P(x), H, L["ln1_g"].data_ptr(), L["ln1_b"].data_ptr(),
-                          cfg.eps, P(self.h1), P(self.h1q), a["h1"], ROUND_NEAREST_EVEN)
+                          cfg.eps, P(self.h1), P(self.h1q), a["h1"], ROUND_NEAREST_EVEN, CW)
             else:
-                self._add("zen_linear_i8", P(self.ctxq), H, L["wo"].data_ptr(), H, T, H, H, a["ctx"],
+                self._add("zen_linear_i8_ex", P(self.ctxq), H, L["wo"].data_ptr(), H, T, H, H, a["ctx"],
                           L["wo_s"].data_ptr(), L["bo"].data_ptr(), ACT_NONE, DT_F16, 1.0, ROUND_NEAREST_EVEN,
-                          P(self.ao), H)
+                          P(self.ao), H, None, 0, None, 0, CW)
                 self._add("zen_add_layernorm_f16", P(self.ao), P(x), L["ln1_g"].data_ptr(), L["ln1_b"].data_ptr(),
                           P(self.h1), P(self.h1q), a["h1"], ROUND_NEAREST_EVEN, T, H, cfg.eps)
-            self._add("zen_linear_i8_prefetch", P(self.h1q), H, L["w1"].data_ptr(), H, T, F, H, a["h1"],
+            self._add("zen_linear_i8_ex", P(self.h1q), H, L["w1"].data_ptr(), H, T, F, H, a["h1"],
                       L["w1_s"].data_ptr(), L["b1"].data_ptr(), ACT_GELU, DT_S8, a["gelu"], ROUND_NEAREST_EVEN,
-                      P(self.gq), F, *pf(L["w2"], None if last else self.layers[li + 1]["wqkv"]))
+                      P(self.gq), F, *pf(L["w2"], None if last else self.layers[li + 1]["wqkv"]), CW)
             if self.fuse_layernorm:
-                self._add("zen_linear_i8_add_layernorm", P(self.gq), F, L["w2"].data_ptr(), F, T, H, F, a["gelu"],
+                self._add("zen_linear_i8_add_layernorm_ex", P(self.gq), F, L["w2"].data_ptr(), F, T, H, F, a["gelu"],
                           L["w2_s"].data_ptr(), L["b2"].data_ptr(), P(self.h1), H, L["ln2_g"].data_ptr(),
                           L["ln2_b"].data_ptr(), cfg.eps, P(xn), None if last else P(xqn),
-                          1.0 if last else sc[li + 1]["x"], ROUND_NEAREST_EVEN)
+                          1.0 if last else sc[li + 1]["x"], ROUND_NEAREST_EVEN, CW)
             else:
-                self._add("zen_linear_i8", P(self.gq), F, L["w2"].data_ptr(), F, T, H, F, a["gelu"],
+                self._add("zen_linear_i8_ex", P(self.gq), F, L["w2"].data_ptr(), F, T, H, F, a["gelu"],
                           L["w2_s"].data_ptr(), L["b2"].data_ptr(), ACT_NONE, DT_F16, 1.0, ROUND_NEAREST_EVEN,
-                          P(self.o), H)
+                          P(self.o), H, None, 0, None, 0, CW)
                 self._add("zen_add_layernorm_f16", P(self.o), P(self.h1), L["ln2_g"].data_ptr(), L["ln2_b"].data_ptr(),
                           P(xn), None if last else P(xqn), 1.0 if last else sc[li + 1]["x"], ROUND_NEAREST_EVEN, T, H,
                           cfg.eps)

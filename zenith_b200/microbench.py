@@ -69,8 +69,7 @@ def main() -> None:
               "gelu_s8": dict(act="gelu", out_dtype=torch.int8, out_scale=0.05),
               "gelu_f16": dict(act="gelu", out_dtype=torch.float16)}[a.epilogue]
         y = torch.empty((a.m, a.n), dtype=kw["out_dtype"], device=dev)
-        ops.set_gemm_tile_n(a.tile_n)
-        med, best = _time(lambda: ops.linear_int8(x, w, 0.02, ws, b, out=y, **kw), a.iters, flush)
+        med, best = _time(lambda: ops.linear_int8(x, w, 0.02, ws, b, out=y, tile_n=a.tile_n, **kw), a.iters, flush)
         out.update(m=a.m, n=a.n, k=a.k, epilogue=a.epilogue, tile_n=a.tile_n, us=med, us_min=best,
                    tops=2.0 * a.m * a.n * a.k / med / 1e6)
     elif a.case == "gemm_i8_ln":
@@ -90,8 +89,7 @@ def main() -> None:
         w = torch.randn(a.n, a.k, device=dev, dtype=torch.float16)
         b = torch.randn(a.n, device=dev)
         y = torch.empty((a.m, a.n), dtype=torch.float16, device=dev)
-        ops.set_gemm_tile_n(a.tile_n)
-        med, best = _time(lambda: ops.linear_fp16(x, w, b, out=y), a.iters, flush)
+        med, best = _time(lambda: ops.linear_fp16(x, w, b, out=y, tile_n=a.tile_n), a.iters, flush)
         out.update(m=a.m, n=a.n, k=a.k, tile_n=a.tile_n, us=med, us_min=best, tflops=2.0 * a.m * a.n * a.k / med / 1e6)
     elif a.case == "add_ln":
         x = torch.randn(a.rows, a.hidden, device=dev, dtype=torch.float16)

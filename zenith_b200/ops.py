@@ -58,7 +58,8 @@ def _call(fn: str, *args) -> None:
 # GEMMs
 # --------------------------------------------------------------------------------------------
 def linear_int8(xq, wq, x_scale: float, w_scale=None, bias=None, *, act="none", out_dtype=torch.float32,
-                out_scale: float | None = None, round="nearest_even", out=None, prefetch=()):
+                out_scale: float | None = None, round="nearest_even", out=None, prefetch=(), constant_weights=False,
+                tile_n: int = 0):
     """W8A8 Linear: ``acc = xq @ wq.T`` in int32, then the fused epilogue.
 
     ``out_dtype=torch.int32`` returns the raw accumulators.  Otherwise
@@ -69,6 +70,8 @@ def linear_int8(xq, wq, x_scale: float, w_scale=None, bias=None, *, act="none", 
 
     ``prefetch``: up to two CUDA tensors (e.g. the weights of the GEMMs that follow) that the kernel
     hints into L2 while it runs; they are not read and the result does not depend on them.
+    ``constant_weights``: promise that ``wq`` is not being written by work still queued on the device
+    (``ZEN_GEMM_CONST_WEIGHTS``, for this call only); ``tile_n`` forces the tile width (benchmark hook).
     """
     _require(xq, "xq", torch.int8, 2)
     _require(wq, "wq", torch.int8, 2)
@@ -97,14 +100,15 @@ def linear_int8(xq, wq, x_scale: float, w_scale=None, bias=None, *, act="none", 
     if M == 0 or N == 0:
         return out
     hint = [v for t in prefetch for v in (t.data_ptr(), t.numel() * t.element_size())] + [None, 0] * (2 - len(prefetch))
-    _call("zen_linear_i8_prefetch", xq.data_ptr(), K, wq.data_ptr(), K, M, N, K, float(x_scale), _ptr(w_scale),
+    flags = (_capi.GEMM_CONST_WEIGHTS if constant_weights else 0) | _capi.gemm_tile_n(tile_n)
+    _call("zen_linear_i8_ex", xq.data_ptr(), K, wq.data_ptr(), K, M, N, K, float(x_scale), _ptr(w_scale),
           _ptr(bias), _ACT[act], _OUT[out_dtype], float(out_scale if out_scale is not None else 1.0), _ROUND[round],
-          out.data_ptr(), out.stride(0), *hint, _stream())
+          out.data_ptr(), out.stride(0), *hint, flags, _stream())
     return out
 
 
 def linear_int8_add_layernorm(xq, wq, x_scale: float, w_scale, bias, residual, gamma, beta, eps: float, *,
-                              out_scale: float | None = None, round="nearest_even"):
+                              out_scale: float | None = None, round="nearest_even", constant_weights=False):
     """``LayerNorm(dequant(xq @ wq.T) + bias + residual) * gamma + beta`` in one kernel (hidden size 768).
 
     Returns fp16 ``y`` and, with ``out_scale``, also the int8 copy ``quantize(y, out_scale)``.
@@ -125,14 +129,14 @@ def linear_int8_add_layernorm(xq, wq, x_scale: float, w_scale, bias, residual, g
     y = torch.empty((M, N), dtype=torch.float16, device=xq.device)
     yq = torch.empty((M, N), dtype=torch.int8, device=xq.device) if out_scale is not None else None
     if M:
-        _call("zen_linear_i8_add_layernorm", xq.data_ptr(), K, wq.data_ptr(), K, M, N, K, float(x_scale), _ptr(w_scale),
+        _call("zen_linear_i8_add_layernorm_ex", xq.data_ptr(), K, wq.data_ptr(), K, M, N, K, float(x_scale), _ptr(w_scale),
               _ptr(bias), residual.data_ptr(), N, gamma.data_ptr(), beta.data_ptr(), float(eps), y.data_ptr(), _ptr(yq),
-              float(out_scale or 1.0), _ROUND[round], _stream())
+              float(out_scale or 1.0), _ROUND[round], _capi.GEMM_CONST_WEIGHTS if constant_weights else 0, _stream())
     return y if yq is None else (y, yq)
 
 
 def linear_fp16_add_layernorm(x, w, bias, residual, gamma, beta, eps: float, *, out_scale: float | None = None,
-                              round="nearest_even"):
+                              round="nearest_even", constant_weights=False):
     """``LayerNorm(x @ w.T + bias + residual) * gamma + beta`` with fp16 operands in one kernel (hidden 768 or
     1024).  Returns fp16 ``y`` and, with ``out_scale``, also ``quantize(y, out_scale)``."""
     _require(x, "x", torch.float16, 2)
@@ -149,13 +153,13 @@ def linear_fp16_add_layernorm(x, w, bias, residual, gamma, beta, eps: float, *, 
     y = torch.empty((M, N), dtype=torch.float16, device=x.device)
     yq = torch.empty((M, N), dtype=torch.int8, device=x.device) if out_scale is not None else None
     if M:
-        _call("zen_linear_f16_add_layernorm", x.data_ptr(), K, w.data_ptr(), K, M, N, K, _ptr(bias), residual.data_ptr(), N,
+        _call("zen_linear_f16_add_layernorm_ex", x.data_ptr(), K, w.data_ptr(), K, M, N, K, _ptr(bias), residual.data_ptr(), N,
               gamma.data_ptr(), beta.data_ptr(), float(eps), y.data_ptr(), _ptr(yq), float(out_scale or 1.0), _ROUND[round],
-              _stream())
+              _capi.GEMM_CONST_WEIGHTS if constant_weights else 0, _stream())
     return y if yq is None else (y, yq)
 
 
-def linear_fp16(x, w, bias=None, *, act="none", out_dtype=torch.float16, out=None):
+def linear_fp16(x, w, bias=None, *, act="none", out_dtype=torch.float16, out=None, tile_n: int = 0):
     """``act(x @ w.T + bias)`` with fp16 operands, fp32 accumulation (core/src/fp16_kernels.cu:92-122)."""
     _require(x, "x", torch.float16, 2)
     _require(w, "w", torch.float16, 2)
@@ -171,8 +175,8 @@ def linear_fp16(x, w, bias=None, *, act="none", out_dtype=torch.float16, out=Non
         out = torch.empty((M, N), dtype=out_dtype, device=x.device)
     if M == 0 or N == 0:
         return out
-    _call("zen_linear_f16", x.data_ptr(), K, w.data_ptr(), K, M, N, K, _ptr(bias), _ACT[act], _OUT[out_dtype],
-          out.data_ptr(), out.stride(0), _stream())
+    _call("zen_linear_f16_ex", x.data_ptr(), K, w.data_ptr(), K, M, N, K, _ptr(bias), _ACT[act], _OUT[out_dtype],
+          out.data_ptr(), out.stride(0), _capi.gemm_tile_n(tile_n), _stream())
     return out
 
 
@@ -472,15 +476,3 @@ def embed_layernorm(ids, type_ids, word, pos, typ, gamma, beta, eps: float, seq:
               typ.data_ptr(), gamma.data_ptr(), beta.data_ptr(), y.data_ptr(), _ptr(yq), float(out_scale or 1.0),
               _ROUND[round], tokens, int(seq), hidden, word.shape[0], float(eps), _stream())
     return y if yq is None else (y, yq)
-
-
-def set_constant_weights(on: bool) -> None:
-    """Promise that int8 weight tensors are never written while a GEMM that reads them may be queued
-    (``zen_gemm_set_constant_weights``): the GEMMs then fetch their first weight tiles ahead of the
-    dependency wait.  The encoder drivers make the promise for their own (immutable) weights."""
-    _capi.check("zen_gemm_set_constant_weights", _capi.lib().zen_gemm_set_constant_weights(1 if on else 0))
-
-
-def set_gemm_tile_n(tile_n: int) -> None:
-    """Force the GEMM tile width (0 = automatic).  Benchmark hook."""
-    _capi.call("zen_gemm_set_tile_n", int(tile_n))
