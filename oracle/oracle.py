@@ -148,6 +148,19 @@ def attention(q, k, v, kv_lens=None, causal=False, scale=None):
     return o
 
 
+def attention_rows(q, k, v, rows, kv_lens=None, causal=False, scale=None):
+    """Rows ``rows`` (query indices) of ``attention(q, k, v, ...)``: ``[B, H, len(rows), D]``."""
+    q, k, v = _c(q, np.float32), _c(k, np.float32), _c(v, np.float32)
+    B, H, S, D = q.shape
+    scale = 1.0 / np.sqrt(D) if scale is None else scale
+    kl = _c(kv_lens, np.int32) if kv_lens is not None else None
+    rows = _c(rows, np.int32)
+    o = np.empty((B, H, rows.size, D), np.float32)
+    _load().orc_attention_rows_f32(_p(q), _p(k), _p(v), _p(o), B, H, S, D, _p(kl), 1 if causal else 0, C.c_float(scale),
+                                   _p(rows), int(rows.size))
+    return o
+
+
 def gemm_f32_nt(a, w):
     """``a[M,K] @ w[N,K].T`` with double accumulation."""
     a, w = _c(a, np.float32), _c(w, np.float32)

@@ -140,6 +140,45 @@ void orc_attention_f32(const float* Q, const float* K, const float* V, float* O,
   free(p);
 }
 
+/* orc_attention_f32 for a subset of the query rows: O_rows[b,h,r,:] is row rows[r] of the full result (the same
+ * arithmetic, same reference lines); lets a test check long sequences on sampled rows in seconds. */
+void orc_attention_rows_f32(const float* Q, const float* K, const float* V, float* O_rows, int B, int H, int S, int D,
+                            const int32_t* kv_lens, int causal, float scale, const int32_t* rows, int n_rows) {
+  double* p = (double*)malloc(sizeof(double) * (size_t)S);
+  for (int b = 0; b < B; ++b) {
+    int kvl = kv_lens ? kv_lens[b] : S;
+    if (kvl < 0) kvl = 0;
+    if (kvl > S) kvl = S;
+    for (int h = 0; h < H; ++h) {
+      const size_t base = ((size_t)b * H + h) * (size_t)S * D;
+      for (int r = 0; r < n_rows; ++r) {
+        const int i = rows[r];
+        int lim = kvl;
+        if (causal && i + 1 < lim) lim = i + 1;
+        double mx = -INFINITY;
+        for (int j = 0; j < lim; ++j) {
+          double s = 0.0;
+          for (int d = 0; d < D; ++d) s += (double)Q[base + (size_t)i * D + d] * (double)K[base + (size_t)j * D + d];
+          p[j] = s * (double)scale;
+          if (p[j] > mx) mx = p[j];
+        }
+        double l = 0.0;
+        for (int j = 0; j < lim; ++j) {
+          p[j] = exp(p[j] - mx);
+          l += p[j];
+        }
+        float* out = O_rows + (((size_t)b * H + h) * (size_t)n_rows + (size_t)r) * D;
+        for (int d = 0; d < D; ++d) {
+          double o = 0.0;
+          for (int j = 0; j < lim; ++j) o += p[j] * (double)V[base + (size_t)j * D + d];
+          out[d] = l > 0.0 ? (float)(o / l) : 0.0f;
+        }
+      }
+    }
+  }
+  free(p);
+}
+
 /* C[M,N] = A[M,K] . W[N,K]^T in fp32 with double accumulation (checker for the fp16 / TF32 GEMMs). */
 void orc_gemm_f32_nt(const float* A, const float* W, float* C, int M, int N, int K) {
   for (int m = 0; m < M; ++m)

@@ -131,3 +131,12 @@ def test_int8_encoder_oracle_tracks_fp32_encoder():
     fq = ER.encoder_fake_quant(cfg, params, scales, ids, lens)
     assert np.max(np.abs(q8 - ref)) < 0.15 and np.mean(np.abs(q8 - ref)) < 0.02
     assert np.max(np.abs(fq - ref)) < 0.15
+
+
+def test_attention_rows_is_a_row_subset_of_attention():
+    r = np.random.default_rng(0)
+    q, k, v = (r.standard_normal((2, 2, 70, 16)).astype(np.float32) for _ in range(3))
+    rows = np.array([0, 3, 69, 17])
+    for causal in (False, True):
+        full = O.attention(q, k, v, [70, 33], causal)
+        assert np.array_equal(full[:, :, rows], O.attention_rows(q, k, v, rows, [70, 33], causal))

@@ -1,0 +1,272 @@
+"""Parity with the CPU oracle AT THE BENCHMARK'S OWN SIZES (BASELINE.json configs 2-5), through the C ABI.
+
+The small-shape tests elsewhere never give a persistent CTA more than one tile, a cluster more than one row
+block, or the attention kernel more than eight key blocks.  Here every kernel runs the code path the headline
+number runs on:
+
+* int8 GEMMs of BERT-base at 4096 tokens (QKV -> fp16, FFN1 + GELU -> int8): whole output, bit-exact;
+* GEMM + residual + LayerNorm with 2-3 row blocks per cluster (M = 8192 and 12288, both hidden sizes);
+* one whole BERT-base pass (12 layers, batch 32, seq 128, the benchmark's seeds), every kernel checked on the
+  inputs the device really gave it, int8 results bit-exact, fp16 results within 1e-2;
+* attention at S = 2048 and 8192 on sampled query rows, head sizes 64 and 128, causal and not, plus large
+  logits and a slowly creeping row maximum (the lazy-rescale path).
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import encoder_ref as ER
+from oracle import oracle as O
+from zenith_b200 import _capi, ops
+from zenith_b200.calibrate import calibrate
+from zenith_b200.encoder import BERT_BASE, Fp16Encoder, Int8Encoder, init_params
+
+pytestmark = pytest.mark.gpu
+
+BATCH, SEQ, MASTER_SEED, CALIB_BATCHES = 32, 128, 1234, 16  # as bench.py
+
+
+def rng(seed):
+    return np.random.default_rng(seed)
+
+
+def dev(a, cuda):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(cuda)
+
+
+def make_batch(seed, vocab, batch=BATCH, seq=SEQ):
+    r = rng(seed)
+    ids = r.integers(0, vocab, (batch, seq)).astype(np.int32)
+    lens = (seq - r.integers(0, 33, batch)).astype(np.int32)
+    return ids, lens
+
+
+# ------------------------------------------------------------------------------------------------------------
+# (a) the two plain int8 GEMMs of a BERT-base layer at 4096 tokens: 2 and 2.6 tiles per persistent CTA
+# ------------------------------------------------------------------------------------------------------------
+def _gemm_inputs(N, K, M=4096):
+    x = rng(N).integers(-128, 128, (M, K), dtype=np.int8)
+    w = rng(K + 1).integers(-128, 128, (N, K), dtype=np.int8)
+    ws = ((rng(3).random(N) + 0.5) * 4e-4).astype(np.float32)
+    b = (rng(4).standard_normal(N) * 0.1).astype(np.float32)
+    return x, w, ws, b
+
+
+@pytest.mark.parametrize("tile", [0, 128, 192])
+def test_qkv_gemm_fp16_whole_output_bit_exact(cuda, tile):
+    x, w, ws, b = _gemm_inputs(2304, 768)
+    got = ops.linear_int8(dev(x, cuda), dev(w, cuda), 0.02, dev(ws, cuda), dev(b, cuda), out_dtype=torch.float16,
+                          constant_weights=True, tile_n=tile).cpu().numpy()
+    want = O.linear_int8(x, w, 0.02, ws, b, "none", "f16")
+    assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
+    assert _capi.device_status() == 0
+
+
+@pytest.mark.parametrize("tile", [0, 128])
+def test_ffn1_gemm_gelu_requant_whole_output_bit_exact(cuda, tile):
+    x, w, ws, b = _gemm_inputs(3072, 768)
+    got = ops.linear_int8(dev(x, cuda), dev(w, cuda), 0.02, dev(ws, cuda), dev(b, cuda), act="gelu",
+                          out_dtype=torch.int8, out_scale=0.05, constant_weights=True, tile_n=tile).cpu().numpy()
+    acc = O.gemm_s8(x, w)
+    want = O.quantize(O.epilogue(acc, 0.02, ws, b, "gelu"), 0.05)
+    assert np.array_equal(got, want)
+    assert len(np.unique(got)) > 100  # the requantised values use the int8 range
+    # How much would a libm-based checker disagree?  GELU with libm tanhf instead of the deterministic tanh of
+    # det_math.h: the int8 outputs may differ by one step on a small fraction of the elements.
+    y = O.epilogue(acc, 0.02, ws, b, "none")
+    libm = O.quantize(O.gelu_libm(y), 0.05)
+    diff = np.abs(got.astype(np.int32) - libm.astype(np.int32))
+    rate = float(np.mean(diff != 0))
+    print(f"\nFFN1 int8 output vs libm-GELU oracle: {rate:.2e} of {got.size} elements differ, max |diff| {diff.max()}")
+    assert diff.max() <= 1 and rate < 1e-4
+    assert _capi.device_status() == 0
+
+
+# ------------------------------------------------------------------------------------------------------------
+# (b) GEMM + residual + LayerNorm with several row blocks per cluster (37 clusters: 64 / 96 row blocks)
+# ------------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("M,K,N", [(8192, 768, 768), (8192, 3072, 768), (12288, 1024, 1024), (12288, 4096, 1024),
+                                   (12200, 1024, 1024)])
+def test_linear_add_layernorm_many_row_blocks_per_cluster(cuda, M, K, N):
+    x = rng(M).integers(-128, 128, (M, K), dtype=np.int8)
+    w = rng(K).integers(-128, 128, (N, K), dtype=np.int8)
+    ws = ((rng(1).random(N) + 0.5) * 2e-4).astype(np.float32)
+    b = (rng(2).standard_normal(N) * 0.1).astype(np.float32)
+    res = rng(3).standard_normal((M, N)).astype(np.float16)
+    g = (1 + 0.1 * rng(4).standard_normal(N)).astype(np.float16)
+    be = (0.1 * rng(5).standard_normal(N)).astype(np.float16)
+    y, yq = ops.linear_int8_add_layernorm(dev(x, cuda), dev(w, cuda), 0.02, dev(ws, cuda), dev(b, cuda), dev(res, cuda),
+                                          dev(g, cuda), dev(be, cuda), 1e-12, out_scale=0.03, constant_weights=True)
+    got = y.float().cpu().numpy()
+    assert not np.isnan(got).any()
+    # every 11th row: all row blocks, all four TMEM lane quadrants and every cluster iteration are sampled
+    rows = np.arange(0, M, 11)
+    t = O.linear_int8(x[rows], w, 0.02, ws, b, "none", "f32") + res[rows].astype(np.float32)
+    want = O.layernorm(t, g.astype(np.float32), be.astype(np.float32), 1e-12)
+    assert np.max(np.abs(got[rows] - want)) < 1e-2 and np.mean(np.abs(got[rows] - want)) < 5e-4
+    # the int8 copy is exactly the quantization of the fp16 tensor, over the whole output
+    assert np.array_equal(yq.cpu().numpy(), O.quantize(got, 0.03))
+    # row statistics over the WHOLE output: a mixed-up statistics exchange would show as a wrong mean / variance
+    z = (got - be.astype(np.float32)) / g.astype(np.float32)
+    assert np.max(np.abs(z.mean(axis=1))) < 2e-2 and np.max(np.abs(z.var(axis=1) - 1.0)) < 5e-2
+    assert _capi.device_status() == 0
+
+
+@pytest.mark.parametrize("M,K,N", [(8192, 768, 768), (12288, 1024, 1024)])
+def test_fp16_linear_add_layernorm_many_row_blocks_per_cluster(cuda, M, K, N):
+    x = (rng(M).standard_normal((M, K)) * 0.5).astype(np.float16)
+    w = (rng(K).standard_normal((N, K)) * 0.05).astype(np.float16)
+    b = (rng(2).standard_normal(N) * 0.1).astype(np.float32)
+    res = rng(3).standard_normal((M, N)).astype(np.float16)
+    g = (1 + 0.1 * rng(4).standard_normal(N)).astype(np.float16)
+    be = (0.1 * rng(5).standard_normal(N)).astype(np.float16)
+    y, yq = ops.linear_fp16_add_layernorm(dev(x, cuda), dev(w, cuda), dev(b, cuda), dev(res, cuda), dev(g, cuda),
+                                          dev(be, cuda), 1e-12, out_scale=0.03)
+    got = y.float().cpu().numpy()
+    rows = np.arange(0, M, 11)
+    t = O.gemm_f32_nt(x[rows].astype(np.float32), w.astype(np.float32)) + b + res[rows].astype(np.float32)
+    want = O.layernorm(t, g.astype(np.float32), be.astype(np.float32), 1e-12)
+    assert np.max(np.abs(got[rows] - want)) < 1e-2 and np.mean(np.abs(got[rows] - want)) < 5e-4
+    assert np.array_equal(yq.cpu().numpy(), O.quantize(got, 0.03))
+    assert _capi.device_status() == 0
+
+
+# ------------------------------------------------------------------------------------------------------------
+# (c) the benchmark's own pass: BERT-base, 12 layers, batch 32, seq 128, the benchmark's seeds and calibration
+# ------------------------------------------------------------------------------------------------------------
+@pytest.fixture(scope="module")
+def bert_base(cuda):
+    cfg = BERT_BASE
+    params = init_params(cfg, MASTER_SEED)
+    calib = [make_batch(MASTER_SEED + 1 + i, cfg.vocab) for i in range(CALIB_BATCHES)]
+    scales = calibrate(cfg, params, [(dev(i, cuda), dev(l, cuda)) for i, l in calib], cuda)
+    return cfg, params, scales
+
+
+def test_bert_base_int8_pass_every_kernel_against_the_oracle(cuda, bert_base):
+    cfg, params, scales = bert_base
+    H, nh, hd = cfg.hidden, cfg.heads, cfg.head_dim
+    enc = Int8Encoder(cfg, params, scales, cuda)
+    assert enc.launches_per_layer == 5
+    ids, lens = make_batch(MASTER_SEED + 1000, cfg.vocab)
+    np_ = lambda t: t.cpu().numpy()
+    rows = np.arange(0, BATCH * SEQ, 7)  # all 32 row blocks, every TMEM quadrant, each CTA's 1st / 2nd / 3rd tile
+    seqs = [0, 13, 31]                   # sequences whose attention is recomputed on the CPU
+    for li, buf in enc.forward_layerwise(dev(ids, cuda), dev(lens, cuda)):
+        a, wq, lp = scales.act[li], scales.weights[li], params["layers"][li]
+        f16 = lambda k: lp[k].astype(np.float16).astype(np.float32)
+        xq, qkv, ctx, ctxq, h1, h1q, gq = (np_(buf[k]) for k in ("xq", "qkv", "ctx", "ctxq", "h1", "h1q", "gq"))
+        x32, x_next = np_(buf["x"].float()), np_(buf["x_next"].float())
+        # int8 copies are the exact quantization of the fp16 tensors beside them (whole tensors)
+        assert np.array_equal(xq, O.quantize(x32, a["x"])), f"layer {li}: x_q"
+        assert np.array_equal(ctxq, O.quantize(ctx.astype(np.float32), a["ctx"])), f"layer {li}: ctx_q"
+        assert np.array_equal(h1q, O.quantize(h1.astype(np.float32), a["h1"])), f"layer {li}: h1_q"
+        # QKV: fp16 output bit-exact
+        want = O.linear_int8(xq[rows], wq["wqkv"][0], a["x"], wq["wqkv"][1], lp["bqkv"], "none", "f16")
+        assert np.array_equal(qkv[rows].view(np.uint16), want.view(np.uint16)), f"layer {li}: QKV"
+        # attention with the key-padding mask, on the device's own Q, K, V
+        for b in seqs:
+            blk = qkv[b * SEQ:(b + 1) * SEQ].astype(np.float32)
+            split = lambda m: np.ascontiguousarray(m.reshape(1, SEQ, nh, hd).transpose(0, 2, 1, 3))
+            o = O.attention(split(blk[:, :H]), split(blk[:, H:2 * H]), split(blk[:, 2 * H:]), lens[b:b + 1])
+            o = o.transpose(0, 2, 1, 3).reshape(SEQ, H)
+            assert np.max(np.abs(ctx[b * SEQ:(b + 1) * SEQ].astype(np.float32) - o)) < 1e-2, f"layer {li}: attention"
+        # attention-out + residual + LayerNorm (fused kernel)
+        t = O.linear_int8(ctxq[rows], wq["wo"][0], a["ctx"], wq["wo"][1], lp["bo"], "none", "f32") + x32[rows]
+        want = O.layernorm(t, f16("ln1_g"), f16("ln1_b"), cfg.eps)
+        assert np.max(np.abs(h1[rows].astype(np.float32) - want)) < 1e-2, f"layer {li}: attention-out + LN"
+        # FFN1 + GELU + requant: int8 output bit-exact
+        want = O.linear_int8(h1q[rows], wq["w1"][0], a["h1"], wq["w1"][1], lp["b1"], "gelu", "s8", a["gelu"])
+        assert np.array_equal(gq[rows], want), f"layer {li}: FFN1"
+        # FFN2 + residual + LayerNorm
+        t = O.linear_int8(gq[rows], wq["w2"][0], a["gelu"], wq["w2"][1], lp["b2"], "none", "f32") + h1[rows].astype(np.float32)
+        want = O.layernorm(t, f16("ln2_g"), f16("ln2_b"), cfg.eps)
+        assert np.max(np.abs(x_next[rows] - want)) < 1e-2, f"layer {li}: FFN2 + LN"
+    eager = enc.out.clone()
+    assert not torch.isnan(eager.float()).any()
+    # what the benchmark times: the CUDA-graph replay of the same 61 launches
+    enc.capture(BATCH, SEQ)
+    enc.set_inputs(dev(ids, cuda), dev(lens, cuda))
+    assert torch.equal(enc.replay(), eager)
+    assert _capi.device_status() == 0
+
+
+def test_bert_base_fp16_pass_tracks_the_fp32_reference_path(cuda, bert_base):
+    """BASELINE config 2: the fp16 encoder against the oracle's fp32 encoder on the same weights and batch.
+    The reference states < 0.1 (absolute) for its own 12-layer fp16 path against fp32
+    (benchmarks/bert_fp16_full.py:210-229); LayerNorm outputs are O(1), so 1e-2 relative to the largest
+    activation is the tighter of the two and is what is asserted, on four sequences."""
+    cfg, params, _ = bert_base
+    ids, lens = make_batch(MASTER_SEED + 1000, cfg.vocab)
+    enc = Fp16Encoder(cfg, params, cuda)
+    got = enc.forward(dev(ids, cuda), dev(lens, cuda)).float().cpu().numpy()
+    sel = [0, 9, 20, 31]
+    want = ER.encoder_fp32(cfg, params, ids[sel], lens[sel])
+    got_sel = np.concatenate([got[b * SEQ:(b + 1) * SEQ] for b in sel])
+    err = np.abs(got_sel - want)
+    assert err.max() < 1e-2 * np.abs(want).max() and err.max() < 0.1 and err.mean() < 2e-3
+    eager = enc.out.clone()
+    enc.capture(BATCH, SEQ)
+    enc.set_inputs(dev(ids, cuda), dev(lens, cuda))
+    assert torch.equal(enc.replay(), eager)
+    assert _capi.device_status() == 0
+
+
+# ------------------------------------------------------------------------------------------------------------
+# (d) attention at the sweep's long sequences (BASELINE config 4), on sampled query rows
+# ------------------------------------------------------------------------------------------------------------
+def _attention_case(cuda, S, D, causal, q, k, v, lens=None, tol=1e-2):
+    B, H = q.shape[:2]
+    kl = None if lens is None else np.array(lens, np.int32)
+    o = ops.flash_attention(dev(q, cuda), dev(k, cuda), dev(v, cuda), causal=causal,
+                            kv_lens=None if kl is None else dev(kl, cuda)).float().cpu().numpy()
+    assert not np.isnan(o).any()
+    # rows at both ends, around every 128- / 256-row tile edge of a few tiles, and a random sample
+    edges = [e + d for e in (0, 128, 256, 1024, S // 2, S - 256) for d in (-1, 0, 1, 127)]
+    rows = np.unique(np.clip(np.concatenate([edges, [S - 1], rng(S + D).integers(0, S, 160)]), 0, S - 1)).astype(np.int32)
+    f = lambda t: t.astype(np.float32)
+    want = O.attention_rows(f(q), f(k), f(v), rows, kl, causal)
+    err = np.abs(o[:, :, rows] - want)
+    assert err.max() < tol * max(1.0, np.abs(want).max()), f"max |diff| {err.max()}"
+    assert err.mean() < 1e-3 * max(1.0, np.abs(want).max())
+    return o
+
+
+@pytest.mark.parametrize("S", [2048, 8192])
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("causal", [False, True])
+def test_attention_long_sequences(cuda, S, D, causal):
+    q, k, v = (rng(S + D + i).standard_normal((1, 2, S, D)).astype(np.float16) for i in range(3))
+    _attention_case(cuda, S, D, causal, q, k, v)
+    assert _capi.device_status() == 0
+
+
+@pytest.mark.parametrize("D", [64, 128])
+def test_attention_long_sequence_with_key_lengths(cuda, D):
+    S = 2048
+    q, k, v = (rng(7 + D + i).standard_normal((2, 2, S, D)).astype(np.float16) for i in range(3))
+    _attention_case(cuda, S, D, False, q, k, v, lens=[S - 37, 1000])
+    _attention_case(cuda, S, D, True, q, k, v, lens=[S - 37, 1000])
+
+
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("causal", [False, True])
+def test_attention_large_logits(cuda, D, causal):
+    """Logits four times the usual spread (|s| up to ~20): rows dominated by one or two keys."""
+    S = 2048
+    q, k, v = (rng(11 + D + i).standard_normal((1, 2, S, D)).astype(np.float16) for i in range(3))
+    _attention_case(cuda, S, D, causal, (q * 4).astype(np.float16), k, v)
+
+
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("causal", [False, True])
+def test_attention_slowly_rising_row_maximum(cuda, D, causal):
+    """Every key block raises the row maximum a little (about 5 in the base-2 exponent per 128 keys, below the
+    2^8 step at which the kernel moves its reference maximum), so the accumulated O and row sum run far
+    from the current maximum for many blocks before a rescale happens."""
+    S = 2048
+    q, k, v = (rng(21 + D + i).standard_normal((1, 2, S, D)).astype(np.float16) for i in range(3))
+    q[..., 0] = np.float16(np.sqrt(D))                                        # scale * q0 == 1
+    k[..., 0] = (np.arange(S, dtype=np.float32) * (3.5 / 128)).astype(np.float16)  # logit += 3.5 nats per block
+    _attention_case(cuda, S, D, causal, q, k, v)
+    assert _capi.device_status() == 0
