@@ -125,8 +125,12 @@ int zen_linear_f16_add_layernorm(const void* x, int64_t ldx, const void* w, int6
  *                           the fp16 forms alike.
  *   ZEN_GEMM_TILE_N(bn)     force the tile width (64, 128, 192 or 256; a width the kernel family lacks is ignored);
  *                           a tuning hook for benchmarks.  Not accepted by the *_add_layernorm_ex forms.
+ *   ZEN_GEMM_PAIR / _NO_PAIR force or forbid the CTA-pair kernel, which the library otherwise chooses by shape;
+ *                           results are identical either way.  Tuning / test hook.
  * None of this has a counterpart in the reference. */
 #define ZEN_GEMM_CONST_WEIGHTS 0x1u
+#define ZEN_GEMM_NO_PAIR 0x2u /* never run this GEMM on CTA pairs (one CTA per 128-row tile) */
+#define ZEN_GEMM_PAIR 0x4u    /* always run it on CTA pairs (two CTAs per 256-row tile, tcgen05 cta_group::2) */
 #define ZEN_GEMM_TILE_N(bn) ((unsigned)(bn) << 8)
 
 /* zen_linear_i8_prefetch with per-call options. */

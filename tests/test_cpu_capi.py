@@ -50,7 +50,8 @@ def test_argument_validation_needs_no_device():
     assert lib.zen_layernorm_f32(z, z, z, z, 4, 8, 1e-5, z) == _capi.ERR_INVALID_ARG
     # per-call options: an unknown flag bit or tile width is rejected
     ex = lambda flags: lib.zen_linear_i8_ex(one, 16, one, 16, 4, 4, 16, 1.0, z, z, 0, 0, 1.0, 0, one, 4, z, 0, z, 0, flags, z)
-    assert ex(0x2) == _capi.ERR_INVALID_ARG and ex(_capi.gemm_tile_n(100)) == _capi.ERR_INVALID_ARG
+    assert ex(0x80) == _capi.ERR_INVALID_ARG and ex(_capi.gemm_tile_n(100)) == _capi.ERR_INVALID_ARG
+    assert ex(_capi.GEMM_PAIR | _capi.GEMM_NO_PAIR) == _capi.ERR_INVALID_ARG
     # zero-sized work is a no-op, not an error
     assert lib.zen_gelu_f32(z, z, 0, z) == 0 and lib.zen_layernorm_f16(z, z, z, z, 0, 8, 1e-5, z) == 0
 

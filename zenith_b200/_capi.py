@@ -14,7 +14,7 @@ OK, ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_LAUNCH, ERR_TIMEOUT, ERR_DRIVER, ERR_T
 DT_S32, DT_F32, DT_F16, DT_S8 = range(4)
 ACT_NONE, ACT_GELU, ACT_RELU = range(3)
 ROUND_NEAREST_EVEN, ROUND_TRUNC = range(2)
-GEMM_CONST_WEIGHTS = 0x1
+GEMM_CONST_WEIGHTS, GEMM_NO_PAIR, GEMM_PAIR = 0x1, 0x2, 0x4
 
 
 def gemm_tile_n(bn: int) -> int:

@@ -1,6 +1,8 @@
 // Host side of the tcgen05 GEMMs: tile selection, tensor maps, launches, C ABI.
 #include "gemm_tc.cuh"
+#include "gemm_pair.cuh"
 #include "tma_host.cuh"
+#include <map>
 #include <mutex>
 
 namespace zen {
@@ -43,6 +45,71 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
   return launch_pdl(PDL_GEMM, kernel, dim3(grid), dim3(GEMM_THREADS), smem, stream, ta, tb, tc, p);
 }
 
+// Pairs of CTAs that can be resident at once for a pair kernel (SMs of a GPC come in odd numbers on some
+// parts, so this may be below half the SM count); asked of the runtime once per (kernel, device).
+static int max_resident_pairs(const void* kernel, size_t smem) {
+  static std::mutex mu;
+  static std::map<std::pair<const void*, int>, int> cache;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) {
+    cudaGetLastError();
+    return num_sms() / 2;
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find({kernel, dev});
+  if (it != cache.end()) return it->second;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(unsigned(num_sms() / 2 * 2));
+  cfg.blockDim = dim3(GEMM_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n <= 0) {
+    cudaGetLastError();
+    n = num_sms() / 2;
+  }
+  cache[{kernel, dev}] = n;
+  return n;
+}
+
+template <int KIND, int BN, int STAGES>
+static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, GemmParams p,
+                            cudaStream_t stream) {
+  auto kernel = gemm_pair_kernel<KIND, BN, STAGES>;
+  constexpr size_t smem = gemm_pair_smem_bytes<BN, STAGES>();
+  if (int st = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), smem); st != ZEN_OK) return st;
+  p.tiles_m = (p.M + 2 * GEMM_BM - 1) / (2 * GEMM_BM);  // 256-row blocks
+  p.tiles_n = (p.N + BN - 1) / BN;
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int resident = max_resident_pairs(reinterpret_cast<const void*>(kernel), smem);
+  const int pairs = tiles < resident ? tiles : resident;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(unsigned(2 * pairs));
+  cfg.blockDim = dim3(GEMM_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = (pdl_mask() & PDL_GEMM) ? 2 : 1;
+  if (cudaLaunchKernelEx(&cfg, kernel, ta, tb, tc, p) != cudaSuccess) {
+    cudaGetLastError();
+    return ZEN_ERR_LAUNCH;
+  }
+  return ZEN_OK;
+}
+
 template <int KIND>
 static CUtensorMapDataType tmap_dtype() {
   return KIND == KIND_I8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
@@ -51,14 +118,16 @@ static CUtensorMapDataType tmap_dtype() {
 }
 
 // A [M,K] (row stride lda elements); B K-major [N,K] (ldb) or MN-major [K,N] (ldb).
-template <int KIND, int BN, int STAGES, bool B_MN>
+// PAIR: the CTA-pair kernel (gemm_pair.cuh); each CTA then copies BN / 2 rows of B per k-block.
+template <int KIND, int BN, int STAGES, bool B_MN, bool PAIR = false>
 static int run_gemm(const void* A, int64_t lda, const void* B, int64_t ldb, GemmParams p, cudaStream_t stream) {
+  static_assert(!(PAIR && B_MN), "the pair kernel takes K-major B only");
   constexpr int ELEM = GemmKind<KIND>::ELEM;
   constexpr int BK = 128 / ELEM;
   CUtensorMap ta, tb;
   int st = encode_tmap_2d(&ta, tmap_dtype<KIND>(), A, uint64_t(p.K), uint64_t(p.M), uint64_t(lda) * ELEM, BK, GEMM_BM);
   if (st != ZEN_OK) return st;
-  if (!B_MN) st = encode_tmap_2d(&tb, tmap_dtype<KIND>(), B, uint64_t(p.K), uint64_t(p.N), uint64_t(ldb) * ELEM, BK, BN);
+  if (!B_MN) st = encode_tmap_2d(&tb, tmap_dtype<KIND>(), B, uint64_t(p.K), uint64_t(p.N), uint64_t(ldb) * ELEM, BK, PAIR ? BN / 2 : BN);
   else st = encode_tmap_2d(&tb, tmap_dtype<KIND>(), B, uint64_t(p.N), uint64_t(p.K), uint64_t(ldb) * ELEM, BK, BK);
   if (st != ZEN_OK) return st;
   p.num_k_blocks = (p.K + BK - 1) / BK;
@@ -75,7 +144,37 @@ static int run_gemm(const void* A, int64_t lda, const void* B, int64_t ldb, Gemm
     if (st != ZEN_OK) return st;
     p.staged_store = 1;
   }
-  return launch_gemm<KIND, BN, STAGES, B_MN>(ta, tb, tc, p, stream);
+  if constexpr (PAIR) return launch_gemm_pair<KIND, BN, STAGES>(ta, tb, tc, p, stream);
+  else return launch_gemm<KIND, BN, STAGES, B_MN>(ta, tb, tc, p, stream);
+}
+
+// Whether a GEMM of this shape runs on CTA pairs.  ZEN_GEMM_PAIR / ZEN_GEMM_NO_PAIR force the choice.
+static bool use_pair(int M, unsigned flags) {
+  if (flags & ZEN_GEMM_NO_PAIR) return false;
+  if (flags & ZEN_GEMM_PAIR) return true;
+  return false;
+}
+
+// Pair tile width: fewest rounds of the resident pairs, wider tiles preferred on a tie (less traffic per operation).
+static int pick_bn_pair(int M, int N, unsigned flags) {
+  static const int allowed[] = {256, 192, 128};
+  const int forced = int((flags >> 8) & 0x3ffu);
+  for (int bn : allowed)
+    if (bn == forced) return bn;
+  const int pairs = num_sms() / 2;
+  const int tiles_m = (M + 2 * GEMM_BM - 1) / (2 * GEMM_BM);
+  long best_cost = -1;
+  int best = allowed[0];
+  for (int bn : allowed) {
+    const long tiles = long(tiles_m) * ((N + bn - 1) / bn);
+    const long rounds = (tiles + pairs - 1) / pairs;
+    const long cost = rounds * (bn + 24);
+    if (best_cost < 0 || cost < best_cost) {
+      best_cost = cost;
+      best = bn;
+    }
+  }
+  return best;
 }
 
 // out[c, r] = in[r, c] for a row-major [rows, cols] fp32 matrix, 32 x 32 tiles through shared memory.
@@ -127,7 +226,8 @@ const char* zen_status_string(int s) {
 
 static bool flags_ok(unsigned flags) {
   const unsigned bn = (flags >> 8) & 0x3ffu;
-  if (flags & ~(ZEN_GEMM_CONST_WEIGHTS | (0x3ffu << 8))) return false;
+  if (flags & ~(ZEN_GEMM_CONST_WEIGHTS | ZEN_GEMM_PAIR | ZEN_GEMM_NO_PAIR | (0x3ffu << 8))) return false;
+  if ((flags & ZEN_GEMM_PAIR) && (flags & ZEN_GEMM_NO_PAIR)) return false;
   return bn == 0 || bn == 64 || bn == 128 || bn == 192 || bn == 256;
 }
 
@@ -175,6 +275,13 @@ int zen_linear_i8_ex(const int8_t* xq, int64_t ldx, const int8_t* wq, int64_t ld
   }
   static const int allowed[] = {64, 128, 192, 256};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (use_pair(M, flags)) {
+    switch (pick_bn_pair(M, N, flags)) {
+      case 128: return run_gemm<KIND_I8, 128, 6, false, true>(xq, ldx, wq, ldw, p, s);
+      case 192: return run_gemm<KIND_I8, 192, 5, false, true>(xq, ldx, wq, ldw, p, s);
+      default: return run_gemm<KIND_I8, 256, 4, false, true>(xq, ldx, wq, ldw, p, s);
+    }
+  }
   switch (pick_bn(M, N, allowed, 4, flags)) {
     case 64: return run_gemm<KIND_I8, 64, 7, false>(xq, ldx, wq, ldw, p, s);
     case 128: return run_gemm<KIND_I8, 128, 5, false>(xq, ldx, wq, ldw, p, s);
@@ -201,6 +308,13 @@ int zen_linear_f16_ex(const void* x, int64_t ldx, const void* w, int64_t ldw, in
   p.early_b = (flags & ZEN_GEMM_CONST_WEIGHTS) ? 1 : 0;
   static const int allowed[] = {64, 128, 192, 256};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (use_pair(M, flags)) {
+    switch (pick_bn_pair(M, N, flags)) {
+      case 128: return run_gemm<KIND_F16, 128, 6, false, true>(x, ldx, w, ldw, p, s);
+      case 192: return run_gemm<KIND_F16, 192, 5, false, true>(x, ldx, w, ldw, p, s);
+      default: return run_gemm<KIND_F16, 256, 4, false, true>(x, ldx, w, ldw, p, s);
+    }
+  }
   switch (pick_bn(M, N, allowed, 4, flags)) {
     case 64: return run_gemm<KIND_F16, 64, 7, false>(x, ldx, w, ldw, p, s);
     case 128: return run_gemm<KIND_F16, 128, 5, false>(x, ldx, w, ldw, p, s);

@@ -408,6 +408,160 @@ __device__ __forceinline__ void epilogue_chunk_act(const uint32_t (&r)[GEMM_CW],
     epilogue_chunk<KIND, OUT, ZEN_ACT_NONE>(r, sc, bi, p, row, col0, full, inv_scale, stage, lane, istep);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Epilogue role of the persistent GEMM kernels (warps 2..17 of a CTA), shared by the one-CTA kernel below and
+// the CTA-pair kernel of gemm_pair.cuh.  The calling CTA owns 128 rows of every tile it works on:
+//   tile t (t = first_tile, first_tile + tile_step, ...) covers rows (t % p.tiles_m) * TILE_M + row_off .. + 127
+//   and columns (t / p.tiles_m) * BN .. + BN - 1,
+// with TILE_M = 128 (one CTA per tile, row_off = 0) or 256 (a CTA pair per tile, row_off = 128 * rank).
+// `tempty` releases an accumulator to the MMA issuer: a local barrier on which every epilogue thread arrives
+// (one CTA), or the cluster address of the leader CTA's barrier on which one lane per warp arrives (pair).
+// ---------------------------------------------------------------------------------------------
+struct TmemEmptySignal {
+  uint64_t* local;        // one-CTA kernel: tempty_bar[2] of this CTA (count = epilogue threads)
+  uint32_t cluster_addr;  // pair kernel: shared::cluster address of the leader's tempty_bar[0] (count = warps of both CTAs)
+};
+
+template <bool PAIR>
+__device__ __forceinline__ void release_accumulator(const TmemEmptySignal& sig, int acc, int lane) {
+  if constexpr (PAIR) {
+    __syncwarp();
+    if (lane == 0) mbar_arrive_remote(sig.cluster_addr + uint32_t(acc) * 8u);
+  } else {
+    mbar_arrive(&sig.local[acc]);
+  }
+}
+
+template <int KIND, int BN, bool PAIR>
+__device__ __forceinline__ void gemm_epilogue_role(const GemmParams& p, const CUtensorMap& tmap_c, uint32_t tmem_base,
+                                                   uint8_t* out_stage, float* epi_rows, uint64_t* tfull_bar,
+                                                   const TmemEmptySignal& tempty, volatile int* abort_flag, int warp,
+                                                   int lane, int first_tile, int tile_step, int num_tiles, int row_off) {
+  constexpr int TILE_M = PAIR ? 2 * GEMM_BM : GEMM_BM;
+  const int quad = warp & 3;        // TMEM lane quadrant this warp may read: rows quad*32 .. +31 of the CTA's 128
+  const int sub = (warp - 2) >> 2;  // 64-column slab of the tile owned by this warp
+  constexpr int STEPS = 64 / GEMM_CW;
+  if (sub * 64 < BN) {
+    float* s_scale = epi_rows + (warp - 2) * 2 * 64;
+    float* s_bias = s_scale + 64;
+    const int slab_cols = (BN - sub * 64) < 64 ? (BN - sub * 64) : 64;
+    const int elem = p.out_dtype == ZEN_DT_S8 ? 1 : p.out_dtype == ZEN_DT_F16 ? 2 : 4;
+    const bool vec_ok = (reinterpret_cast<uintptr_t>(p.out) % 16 == 0) && ((p.ldo * elem) % 16 == 0);
+    const bool staged = p.staged_store != 0;
+    uint8_t* stage = staged ? out_stage + size_t(sub * 4 + quad) * 4096 : nullptr;
+    const float inv_scale = ZEN_DIV(1.0f, p.out_scale);
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    // Per-column scale and bias of the slab: lane l holds columns l and l + 32.  The values of the
+    // next tile are fetched while the current tile's steps run, so that no tile starts on a global load.
+    auto fetch_cols = [&](int tile, float (&sv)[2], float (&bv)[2]) {
+      const int nn = (tile / p.tiles_m) * BN + sub * 64;
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int col = nn + lane + 32 * u;
+        // predicated loads with no dependent instruction behind them: the warp issues in order and
+        // would otherwise sit on the load until it returns
+        sv[u] = 1.0f;
+        bv[u] = 0.0f;
+        if (p.w_scale != nullptr && col < p.N) sv[u] = __ldg(p.w_scale + col);
+        if (p.bias != nullptr && col < p.N) bv[u] = __ldg(p.bias + col);
+      }
+    };
+    float sv[2] = {1.0f, 1.0f}, bv[2] = {0.0f, 0.0f};
+    if (first_tile < num_tiles) fetch_cols(first_tile, sv, bv);
+    for (int tile = first_tile; tile < num_tiles; tile += tile_step) {
+      const int m0 = (tile % p.tiles_m) * TILE_M + row_off;
+      const int n0 = (tile / p.tiles_m) * BN + sub * 64;
+      __syncwarp();
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        s_scale[lane + 32 * u] = sv[u];
+        s_bias[lane + 32 * u] = bv[u];
+      }
+      if (tile + tile_step < num_tiles) fetch_cols(tile + tile_step, sv, bv);
+      if (staged) {
+        if (lane == 0) tma_store_wait_read();  // the previous tile's store has finished reading the block
+      }
+      __syncwarp();
+      if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag)) break;
+      tc_fence_after_sync();
+      const int row = m0 + quad * 32 + lane;
+      const bool row_ok = row < p.M;
+      const uint32_t tacc = tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * BN + sub * 64);
+      // The loop is kept rolled: the step body (above all the GELU + requant one) is large, and
+      // unrolling it made instruction fetch the bottleneck.  (Requesting the columns of step i + 1
+      // before working on step i was tried twice and lost both times: 16 more live registers.)
+#pragma unroll 1
+      for (int i = 0; i < STEPS; ++i) {
+        if (i * GEMM_CW >= slab_cols) break;
+        uint32_t r[GEMM_CW];
+        __syncwarp();
+        tmem_ld_32x16(tacc + uint32_t(i * GEMM_CW), r);
+        tmem_wait_ld();
+        const int col0 = n0 + i * GEMM_CW;
+        if constexpr (KIND == KIND_I8) {
+          if (p.out_dtype == ZEN_DT_S8 && p.round_mode == 0) {
+            const float* sc = s_scale + i * GEMM_CW;
+            const float* bi = s_bias + i * GEMM_CW;
+            const uint32_t ta = tacc + uint32_t(i * GEMM_CW);
+            if (p.act == ZEN_ACT_GELU)
+              epilogue_step_s8<ZEN_ACT_GELU>(r, ta, sc, bi, p, row, col0, row_ok, vec_ok, inv_scale, stage, lane, i);
+            else if (p.act == ZEN_ACT_RELU)
+              epilogue_step_s8<ZEN_ACT_RELU>(r, ta, sc, bi, p, row, col0, row_ok, vec_ok, inv_scale, stage, lane, i);
+            else
+              epilogue_step_s8<ZEN_ACT_NONE>(r, ta, sc, bi, p, row, col0, row_ok, vec_ok, inv_scale, stage, lane, i);
+            continue;
+          }
+        }
+        if (!staged && (!row_ok || col0 >= p.N)) continue;
+        const bool full = vec_ok && (col0 + GEMM_CW <= p.N);
+        const float* sc = s_scale + i * GEMM_CW;
+        const float* bi = s_bias + i * GEMM_CW;
+        if constexpr (KIND == KIND_I8) {
+          switch (p.out_dtype) {
+            case ZEN_DT_S32:
+              epilogue_chunk<KIND, ZEN_DT_S32, ZEN_ACT_NONE>(r, sc, bi, p, row, col0, full, inv_scale, stage, lane, i);
+              break;
+            case ZEN_DT_F32: epilogue_chunk_act<KIND, ZEN_DT_F32>(r, sc, bi, p, row, col0, full, inv_scale, stage, lane, i); break;
+            case ZEN_DT_F16: epilogue_chunk_act<KIND, ZEN_DT_F16>(r, sc, bi, p, row, col0, full, inv_scale, stage, lane, i); break;
+            default: epilogue_chunk_act<KIND, ZEN_DT_S8>(r, sc, bi, p, row, col0, full, inv_scale, stage, lane, i); break;
+          }
+        } else {
+          if (p.out_dtype == ZEN_DT_F32)
+            epilogue_chunk_act<KIND, ZEN_DT_F32>(r, sc, bi, p, row, col0, full, inv_scale, stage, lane, i);
+          else
+            epilogue_chunk_act<KIND, ZEN_DT_F16>(r, sc, bi, p, row, col0, full, inv_scale, stage, lane, i);
+        }
+      }
+      __syncwarp();
+      tc_fence_before_sync();
+      release_accumulator<PAIR>(tempty, acc, lane);  // the accumulator is free as soon as it has been read
+      if (staged) {
+        fence_proxy_async_smem();  // this lane's writes to the block -> visible to the TMA engine
+        __syncwarp();
+        if (lane == 0 && n0 < p.N && m0 + quad * 32 < p.M) {
+          tma_store_2d(&tmap_c, stage, n0, m0 + quad * 32);
+          tma_store_commit();
+        }
+      }
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+    if (staged && lane == 0) tma_store_wait_all();
+  } else {
+    // no slab for this warp at this tile width: it still owes its arrivals on the accumulator barriers
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int tile = first_tile; tile < num_tiles; tile += tile_step) {
+      if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag)) break;
+      tc_fence_before_sync();
+      release_accumulator<PAIR>(tempty, acc, lane);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+}
+
 template <int KIND, int BN, int STAGES, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -575,127 +729,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
   } else {
     // ------------------------------------------------------------------ epilogue
-    const int quad = warp & 3;        // TMEM lane quadrant this warp may read: rows quad*32 .. +31 of the tile
-    const int sub = (warp - 2) >> 2;  // 64-column slab of the tile owned by this warp
-    constexpr int STEPS = 64 / GEMM_CW;
-    if (sub * 64 < BN) {
-      float* s_scale = epi_rows + (warp - 2) * 2 * 64;
-      float* s_bias = s_scale + 64;
-      const int slab_cols = (BN - sub * 64) < 64 ? (BN - sub * 64) : 64;
-      const int elem = p.out_dtype == ZEN_DT_S8 ? 1 : p.out_dtype == ZEN_DT_F16 ? 2 : 4;
-      const bool vec_ok = (reinterpret_cast<uintptr_t>(p.out) % 16 == 0) && ((p.ldo * elem) % 16 == 0);
-      const bool staged = p.staged_store != 0;
-      uint8_t* stage = staged ? out_stage + size_t(sub * 4 + quad) * 4096 : nullptr;
-      const float inv_scale = ZEN_DIV(1.0f, p.out_scale);
-      int acc = 0;
-      uint32_t acc_phase = 0;
-      // Per-column scale and bias of the slab: lane l holds columns l and l + 32.  The values of the
-      // next tile are fetched while the current tile's steps run, so that no tile starts on a global load.
-      auto fetch_cols = [&](int tile, float (&sv)[2], float (&bv)[2]) {
-        const int nn = (tile / p.tiles_m) * BN + sub * 64;
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          const int col = nn + lane + 32 * u;
-          // predicated loads with no dependent instruction behind them: the warp issues in order and
-          // would otherwise sit on the load until it returns
-          sv[u] = 1.0f;
-          bv[u] = 0.0f;
-          if (p.w_scale != nullptr && col < p.N) sv[u] = __ldg(p.w_scale + col);
-          if (p.bias != nullptr && col < p.N) bv[u] = __ldg(p.bias + col);
-        }
-      };
-      float sv[2] = {1.0f, 1.0f}, bv[2] = {0.0f, 0.0f};
-      if (int(blockIdx.x) < num_tiles) fetch_cols(blockIdx.x, sv, bv);
-      for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-        const int m0 = (tile % p.tiles_m) * GEMM_BM;
-        const int n0 = (tile / p.tiles_m) * BN + sub * 64;
-        __syncwarp();
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          s_scale[lane + 32 * u] = sv[u];
-          s_bias[lane + 32 * u] = bv[u];
-        }
-        if (tile + int(gridDim.x) < num_tiles) fetch_cols(tile + gridDim.x, sv, bv);
-        if (staged) {
-          if (lane == 0) tma_store_wait_read();  // the previous tile's store has finished reading the block
-        }
-        __syncwarp();
-        if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag)) break;
-        tc_fence_after_sync();
-        const int row = m0 + quad * 32 + lane;
-        const bool row_ok = row < p.M;
-        const uint32_t tacc = tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(acc * BN + sub * 64);
-        // The loop is kept rolled: the step body (above all the GELU + requant one) is large, and
-        // unrolling it made instruction fetch the bottleneck.  (Requesting the columns of step i + 1
-        // before working on step i was tried twice and lost both times: 16 more live registers.)
-#pragma unroll 1
-        for (int i = 0; i < STEPS; ++i) {
-          if (i * GEMM_CW >= slab_cols) break;
-          uint32_t r[GEMM_CW];
-          __syncwarp();
-          tmem_ld_32x16(tacc + uint32_t(i * GEMM_CW), r);
-          tmem_wait_ld();
-          const int col0 = n0 + i * GEMM_CW;
-          if constexpr (KIND == KIND_I8) {
-            if (p.out_dtype == ZEN_DT_S8 && p.round_mode == 0) {
-              const float* sc = s_scale + i * GEMM_CW;
-              const float* bi = s_bias + i * GEMM_CW;
-              const uint32_t ta = tacc + uint32_t(i * GEMM_CW);
-              if (p.act == ZEN_ACT_GELU)
-                epilogue_step_s8<ZEN_ACT_GELU>(r, ta, sc, bi, p, row, col0, row_ok, vec_ok, inv_scale, stage, lane, i);
-              else if (p.act == ZEN_ACT_RELU)
-                epilogue_step_s8<ZEN_ACT_RELU>(r, ta, sc, bi, p, row, col0, row_ok, vec_ok, inv_scale, stage, lane, i);
-              else
-                epilogue_step_s8<ZEN_ACT_NONE>(r, ta, sc, bi, p, row, col0, row_ok, vec_ok, inv_scale, stage, lane, i);
-              continue;
-            }
-          }
-          if (!staged && (!row_ok || col0 >= p.N)) continue;
-          const bool full = vec_ok && (col0 + GEMM_CW <= p.N);
-          const float* sc = s_scale + i * GEMM_CW;
-          const float* bi = s_bias + i * GEMM_CW;
-          if constexpr (KIND == KIND_I8) {
-            switch (p.out_dtype) {
-              case ZEN_DT_S32:
-                epilogue_chunk<KIND, ZEN_DT_S32, ZEN_ACT_NONE>(r, sc, bi, p, row, col0, full, inv_scale, stage, lane, i);
-                break;
-              case ZEN_DT_F32: epilogue_chunk_act<KIND, ZEN_DT_F32>(r, sc, bi, p, row, col0, full, inv_scale, stage, lane, i); break;
-              case ZEN_DT_F16: epilogue_chunk_act<KIND, ZEN_DT_F16>(r, sc, bi, p, row, col0, full, inv_scale, stage, lane, i); break;
-              default: epilogue_chunk_act<KIND, ZEN_DT_S8>(r, sc, bi, p, row, col0, full, inv_scale, stage, lane, i); break;
-            }
-          } else {
-            if (p.out_dtype == ZEN_DT_F32)
-              epilogue_chunk_act<KIND, ZEN_DT_F32>(r, sc, bi, p, row, col0, full, inv_scale, stage, lane, i);
-            else
-              epilogue_chunk_act<KIND, ZEN_DT_F16>(r, sc, bi, p, row, col0, full, inv_scale, stage, lane, i);
-          }
-        }
-        __syncwarp();
-        tc_fence_before_sync();
-        mbar_arrive(&tempty_bar[acc]);  // the accumulator is free as soon as it has been read
-        if (staged) {
-          fence_proxy_async_smem();  // this lane's writes to the block -> visible to the TMA engine
-          __syncwarp();
-          if (lane == 0 && n0 < p.N && m0 + quad * 32 < p.M) {
-            tma_store_2d(&tmap_c, stage, n0, m0 + quad * 32);
-            tma_store_commit();
-          }
-        }
-        acc ^= 1;
-        if (acc == 0) acc_phase ^= 1u;
-      }
-      if (staged && lane == 0) tma_store_wait_all();
-    } else {
-      // no slab for this warp at this tile width: it still owes its arrivals on the accumulator barriers
-      int acc = 0;
-      uint32_t acc_phase = 0;
-      for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-        if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag)) break;
-        mbar_arrive(&tempty_bar[acc]);
-        acc ^= 1;
-        if (acc == 0) acc_phase ^= 1u;
-      }
-    }
+    const TmemEmptySignal tempty{tempty_bar, 0u};
+    gemm_epilogue_role<KIND, BN, false>(p, tmap_c, tmem_base, out_stage, epi_rows, tfull_bar, tempty, abort_flag, warp, lane,
+                                        int(blockIdx.x), int(gridDim.x), num_tiles, 0);
   }
 
   tc_fence_before_sync();

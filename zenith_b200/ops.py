@@ -57,9 +57,13 @@ def _call(fn: str, *args) -> None:
 # --------------------------------------------------------------------------------------------
 # GEMMs
 # --------------------------------------------------------------------------------------------
+def _pair_flag(pair) -> int:
+    return 0 if pair is None else (_capi.GEMM_PAIR if pair else _capi.GEMM_NO_PAIR)
+
+
 def linear_int8(xq, wq, x_scale: float, w_scale=None, bias=None, *, act="none", out_dtype=torch.float32,
                 out_scale: float | None = None, round="nearest_even", out=None, prefetch=(), constant_weights=False,
-                tile_n: int = 0):
+                tile_n: int = 0, pair: bool | None = None):
     """W8A8 Linear: ``acc = xq @ wq.T`` in int32, then the fused epilogue.
 
     ``out_dtype=torch.int32`` returns the raw accumulators.  Otherwise
@@ -71,7 +75,8 @@ def linear_int8(xq, wq, x_scale: float, w_scale=None, bias=None, *, act="none", 
     ``prefetch``: up to two CUDA tensors (e.g. the weights of the GEMMs that follow) that the kernel
     hints into L2 while it runs; they are not read and the result does not depend on them.
     ``constant_weights``: promise that ``wq`` is not being written by work still queued on the device
-    (``ZEN_GEMM_CONST_WEIGHTS``, for this call only); ``tile_n`` forces the tile width (benchmark hook).
+    (``ZEN_GEMM_CONST_WEIGHTS``, for this call only); ``tile_n`` forces the tile width and ``pair`` the choice
+    between the CTA-pair kernel (True) and the one-CTA kernel (False); both are benchmark / test hooks.
     """
     _require(xq, "xq", torch.int8, 2)
     _require(wq, "wq", torch.int8, 2)
@@ -100,7 +105,7 @@ def linear_int8(xq, wq, x_scale: float, w_scale=None, bias=None, *, act="none", 
     if M == 0 or N == 0:
         return out
     hint = [v for t in prefetch for v in (t.data_ptr(), t.numel() * t.element_size())] + [None, 0] * (2 - len(prefetch))
-    flags = (_capi.GEMM_CONST_WEIGHTS if constant_weights else 0) | _capi.gemm_tile_n(tile_n)
+    flags = (_capi.GEMM_CONST_WEIGHTS if constant_weights else 0) | _capi.gemm_tile_n(tile_n) | _pair_flag(pair)
     _call("zen_linear_i8_ex", xq.data_ptr(), K, wq.data_ptr(), K, M, N, K, float(x_scale), _ptr(w_scale),
           _ptr(bias), _ACT[act], _OUT[out_dtype], float(out_scale if out_scale is not None else 1.0), _ROUND[round],
           out.data_ptr(), out.stride(0), *hint, flags, _stream())
@@ -159,7 +164,8 @@ def linear_fp16_add_layernorm(x, w, bias, residual, gamma, beta, eps: float, *, 
     return y if yq is None else (y, yq)
 
 
-def linear_fp16(x, w, bias=None, *, act="none", out_dtype=torch.float16, out=None, tile_n: int = 0):
+def linear_fp16(x, w, bias=None, *, act="none", out_dtype=torch.float16, out=None, tile_n: int = 0,
+                pair: bool | None = None):
     """``act(x @ w.T + bias)`` with fp16 operands, fp32 accumulation (core/src/fp16_kernels.cu:92-122)."""
     _require(x, "x", torch.float16, 2)
     _require(w, "w", torch.float16, 2)
@@ -176,7 +182,7 @@ def linear_fp16(x, w, bias=None, *, act="none", out_dtype=torch.float16, out=Non
     if M == 0 or N == 0:
         return out
     _call("zen_linear_f16_ex", x.data_ptr(), K, w.data_ptr(), K, M, N, K, _ptr(bias), _ACT[act], _OUT[out_dtype],
-          out.data_ptr(), out.stride(0), _capi.gemm_tile_n(tile_n), _stream())
+          out.data_ptr(), out.stride(0), _capi.gemm_tile_n(tile_n) | _pair_flag(pair), _stream())
     return out
 
 
