@@ -240,6 +240,22 @@ int zen_flash_attention_f16(const void* q, const void* k, const void* v, void* o
                             int64_t k_ss, int64_t v_sb, int64_t v_sh, int64_t v_ss, int64_t o_sb, int64_t o_sh,
                             int64_t o_ss, const int32_t* kv_lens, int causal, float scale, void* stream);
 
+/* W8A8 QKV projection and attention of an encoder layer in ONE kernel, for sequences of at most 128 tokens and head
+ * size 64:  [Q | K | V] = half((float(xq . wqkv^T) * x_scale) * w_scale[n] + bias[n]) per token, then per (sequence,
+ * head)  ctx = softmax(scale * Q K^T [keys >= kv_lens[b] masked]) V.
+ * xq int8 [B * S, K] (row stride ldx); wqkv int8 [3 * heads * 64, K] (ldw), rows ordered Q | K | V, each head's 64 rows
+ * together; w_scale / bias fp32 [3 * heads * 64] (may be NULL); ctx fp16 [B * S, heads * 64], ctxq (may be NULL) its
+ * int8 copy clamp(round(ctx / ctx_scale)); qkv_out (may be NULL) receives the fp16 projection [B * S, 3 * heads * 64].
+ * The results equal, bit for bit, zen_linear_i8 (fp16 output) followed by zen_flash_attention_f16 on column slices
+ * of that output; the projection never leaves the chip.  next0 / next1: L2 prefetch hints as in
+ * zen_linear_i8_prefetch; flags: ZEN_GEMM_CONST_WEIGHTS.  S > 128 returns ZEN_ERR_UNSUPPORTED (use the two calls).
+ * Replaces linear_gpu x3 + transposes + attention of the reference's encoder drivers
+ * (benchmarks/bert_hybrid.py:96-120) and core/src/flash_attention.cu:194-340. */
+int zen_qkv_attention_i8(const int8_t* xq, int64_t ldx, const int8_t* wqkv, int64_t ldw, int B, int S, int heads, int K,
+                         float x_scale, const float* w_scale, const float* bias, const int32_t* kv_lens, float scale,
+                         void* ctx, int8_t* ctxq, float ctx_scale, void* qkv_out, const void* next0, size_t next0_bytes,
+                         const void* next1, size_t next1_bytes, unsigned flags, void* stream);
+
 /* f32 <-> f16 converts (core/src/fp16_kernels.cu:53-77). */
 int zen_convert_f32_to_f16(const float* x, void* y, int64_t n, void* stream);
 int zen_convert_f16_to_f32(const void* x, float* y, int64_t n, void* stream);

@@ -70,7 +70,7 @@ def test_device_calibration_matches_oracle_calibration(cuda, params):
 def test_int8_encoder_gemms_bit_exact_and_output_tracks_oracle(cuda, params):
     batches = [batch(100 + i) for i in range(4)]
     scales = ER.calibrate_on_oracle(CFG, params, batches, quantize_weights, activation_scales_from_ranges, Int8Scales)
-    enc = Int8Encoder(CFG, params, scales, cuda, fuse_layernorm=False)
+    enc = Int8Encoder(CFG, params, scales, cuda, fuse_layernorm=False, keep_qkv=True)
     ids, lens = batch(2)
     np_ = lambda t: t.cpu().numpy()
     for li, buf in enc.forward_layerwise(*tdev(ids, lens, cuda)):
@@ -102,6 +102,10 @@ def test_int8_encoder_gemms_bit_exact_and_output_tracks_oracle(cuda, params):
     enc.capture(*ids.shape)
     enc.set_inputs(*tdev(ids, lens, cuda))
     assert torch.equal(enc.replay(), eager)
+    # QKV projection and attention as two kernels instead of one: bit-identical
+    two = Int8Encoder(CFG, params, scales, cuda, fuse_layernorm=False, fuse_attention=False)
+    assert torch.equal(two.forward(*tdev(ids, lens, cuda)), eager)
+    assert two.launches_per_layer == 7 and enc.launches_per_layer == 6
     # concurrent micro-batches (sequences are independent): bit-identical, eager and replayed
     for n in (2, 3):
         enc_m = Int8Encoder(CFG, params, scales, cuda, micro_batches=n, fuse_layernorm=False)
@@ -120,7 +124,7 @@ def test_int8_encoder_with_fused_layernorm_kernels(cuda):
                                     activation_scales_from_ranges, Int8Scales)
     ids, lens = mk(50)
     enc = Int8Encoder(cfg, params, scales, cuda)
-    assert enc.fuse_layernorm and enc.launches_per_layer == 5
+    assert enc.fuse_layernorm
     np_ = lambda t: t.cpu().numpy()
     for li, buf in enc.forward_layerwise(*tdev(ids, lens, cuda)):
         a, wq, lp = scales.act[li], scales.weights[li], params["layers"][li]
@@ -138,8 +142,11 @@ def test_int8_encoder_with_fused_layernorm_kernels(cuda):
     got = np_(enc.out.float())
     want8 = ER.encoder_int8(cfg, params, scales, ids, lens, fused_layernorm=True).astype(np.float32)
     assert np.mean(np.abs(got - want8)) < 5e-3 and np.max(np.abs(got - want8)) < 0.1
+    assert enc.launches_per_layer == 4  # QKV + attention, attention-out + LN, FFN1, FFN2 + LN
     unfused = Int8Encoder(cfg, params, scales, cuda, fuse_layernorm=False).forward(*tdev(ids, lens, cuda)).float()
     assert (unfused - enc.out.float()).abs().mean().item() < 5e-3
+    two = Int8Encoder(cfg, params, scales, cuda, fuse_attention=False)
+    assert torch.equal(two.forward(*tdev(ids, lens, cuda)), enc.out) and two.launches_per_layer == 5
     eager = enc.out.clone()
     enc.capture(*ids.shape)
     enc.set_inputs(*tdev(ids, lens, cuda))

@@ -59,6 +59,8 @@ SIGNATURES = {
     "zen_quantize_f16": [_p, _p, _i64, _f, _i, _i, _p],
     "zen_dequantize_f32": [_p, _p, _i64, _f, _i, _p],
     "zen_flash_attention_f16": [_p, _p, _p, _p, _p, _f, _i, _i, _i, _i] + [_i64] * 12 + [_p, _i, _f, _p],
+    "zen_qkv_attention_i8": [_p, _i64, _p, _i64, _i, _i, _i, _i, _f, _p, _p, _p, _f, _p, _p, _f, _p, _p, C.c_size_t, _p,
+                             C.c_size_t, _u, _p],
     "zen_convert_f32_to_f16": [_p, _p, _i64, _p],
     "zen_convert_f16_to_f32": [_p, _p, _i64, _p],
     "zen_minmax_workspace_bytes": [],

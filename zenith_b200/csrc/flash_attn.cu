@@ -63,6 +63,7 @@ __device__ __forceinline__ void fa_tma_tile(uint8_t* dst, const CUtensorMap* map
 
 }  // namespace zen
 #include "flash_attn_pipe.cuh"
+#include "qkv_attn.cuh"
 namespace zen {
 
 // Sequences of at most one key block (S <= 128, the encoder's case).  P reuses the Q / K tiles and
@@ -449,4 +450,65 @@ extern "C" int zen_flash_attention_f16(const void* q, const void* k, const void*
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (S <= FA_BKV) return D == 64 ? launch_fa<64>(tq, tk, tv, p, s) : launch_fa<128>(tq, tk, tv, p, s);
   return D == 64 ? launch_fa_pipe<64, 2>(tq, tk, tv, p, s) : launch_fa_pipe<128, 1>(tq, tk, tv, p, s);
+}
+
+extern "C" int zen_qkv_attention_i8(const int8_t* xq, int64_t ldx, const int8_t* wqkv, int64_t ldw, int B, int S, int heads,
+                                    int K, float x_scale, const float* w_scale, const float* bias,
+                                    const int32_t* kv_lens, float scale, void* ctx, int8_t* ctxq, float ctx_scale,
+                                    void* qkv_out, const void* next0, size_t next0_bytes, const void* next1,
+                                    size_t next1_bytes, unsigned flags, void* stream) {
+  if (!xq || !wqkv || !ctx || B <= 0 || S <= 0 || heads <= 0 || K <= 0) return ZEN_ERR_INVALID_ARG;
+  if ((next0_bytes != 0 && !next0) || (next1_bytes != 0 && !next1)) return ZEN_ERR_INVALID_ARG;
+  if (flags & ~unsigned(ZEN_GEMM_CONST_WEIGHTS)) return ZEN_ERR_INVALID_ARG;
+  if (ctxq && !(ctx_scale > 0.f)) return ZEN_ERR_INVALID_ARG;
+  if (S > 128 || B > 65535 || heads > 65535) return ZEN_ERR_UNSUPPORTED;  // longer sequences: zen_linear_i8 + zen_flash_attention_f16
+  if (K % 16 || ldx % 16 || ldw % 16 || ldx < K || ldw < K) return ZEN_ERR_UNSUPPORTED;
+  const int hidden = heads * 64;
+  if (reinterpret_cast<uintptr_t>(ctx) % 16 || reinterpret_cast<uintptr_t>(ctxq) % 16 ||
+      reinterpret_cast<uintptr_t>(qkv_out) % 16)
+    return ZEN_ERR_UNSUPPORTED;
+  QkvAttnParams p{};
+  p.B = B; p.S = S; p.heads = heads; p.K = K;
+  p.num_k_blocks = (K + 127) / 128;
+  p.x_scale = x_scale; p.w_scale = w_scale; p.bias = bias; p.kv_lens = kv_lens;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.ctxq = ctxq; p.ctx_scale = ctxq ? ctx_scale : 1.0f;
+  p.qkv_out = static_cast<__half*>(qkv_out);
+  p.early_b = (flags & ZEN_GEMM_CONST_WEIGHTS) ? 1 : 0;
+  const void* next[2] = {next0, next1};
+  const size_t next_bytes[2] = {next0_bytes, next1_bytes};
+  for (int i = 0; i < 2; ++i) {
+    const uintptr_t lo = (reinterpret_cast<uintptr_t>(next[i]) + 15u) & ~uintptr_t(15);
+    const uintptr_t hi = (reinterpret_cast<uintptr_t>(next[i]) + next_bytes[i]) & ~uintptr_t(15);
+    if (next_bytes[i] != 0 && hi > lo) {
+      p.pf_ptr[i] = reinterpret_cast<const uint8_t*>(lo);
+      p.pf_bytes[i] = uint64_t(hi - lo);
+    }
+  }
+  // activations as (k, token of the sequence, sequence): rows beyond S read as zero, so a tile never holds a
+  // neighbouring sequence's tokens
+  CUtensorMap ta, tb, to, toq;
+  {
+    const uint64_t dims[3] = {uint64_t(K), uint64_t(S), uint64_t(B)};
+    const uint64_t str[2] = {uint64_t(ldx), uint64_t(ldx) * uint64_t(S)};
+    const uint32_t box[3] = {128u, 128u, 1u};
+    if (int st = encode_tmap(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, xq, dims, str, box); st != ZEN_OK) return st;
+  }
+  if (int st = encode_tmap_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, wqkv, uint64_t(K), uint64_t(3) * hidden, uint64_t(ldw), 128, 64);
+      st != ZEN_OK)
+    return st;
+  // outputs: ctx[b * S + s, h * 64 + d] seen as (d, seq, head, batch), 32-row boxes (one per softmax warp)
+  int perm_q[3];
+  if (int st = encode_qkv_map(&to, ctx, B, heads, S, 64, int64_t(S) * hidden, 64, hidden, p.o_perm, 32u, 2); st != ZEN_OK)
+    return st;
+  toq = to;
+  if (ctxq)
+    if (int st = encode_qkv_map(&toq, ctxq, B, heads, S, 64, int64_t(S) * hidden, 64, hidden, perm_q, 32u, 1); st != ZEN_OK)
+      return st;
+  constexpr size_t smem = qkv_attn_smem_bytes();
+  if (int st = ensure_dynamic_smem(reinterpret_cast<const void*>(qkv_attn_kernel), smem); st != ZEN_OK) return st;
+  const int items = B * heads;
+  const int grid = items < num_sms() ? items : num_sms();
+  return launch_pdl(PDL_GEMM, qkv_attn_kernel, dim3(grid), dim3(QA_THREADS), smem, static_cast<cudaStream_t>(stream), ta, tb,
+                    to, toq, p);
 }

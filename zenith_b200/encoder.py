@@ -27,7 +27,7 @@ import numpy as np
 import torch
 
 from . import _capi, ops
-from ._capi import ACT_GELU, ACT_NONE, DT_F16, DT_S8, GEMM_CONST_WEIGHTS, ROUND_NEAREST_EVEN
+from ._capi import ACT_GELU, ACT_NONE, DT_F16, DT_S8, GEMM_CONST_WEIGHTS, GEMM_NO_PAIR, GEMM_PAIR, ROUND_NEAREST_EVEN
 
 
 @dataclass
@@ -93,7 +93,10 @@ def _dev(a, dtype, device):
 class _EncoderBase:
     """Shared plumbing: embedding tables, per-shape buffers, the launch list, CUDA-graph capture."""
 
-    def __init__(self, cfg: EncoderConfig, params: dict, device, micro_batches: int = 1):
+    def __init__(self, cfg: EncoderConfig, params: dict, device, micro_batches: int = 1, gemm_pair: bool | None = None):
+        """``gemm_pair``: force the plain GEMMs onto the CTA-pair kernel (True) or the one-CTA kernel (False);
+        None lets the library choose by shape."""
+        self.gemm_flags = GEMM_CONST_WEIGHTS | (0 if gemm_pair is None else (GEMM_PAIR if gemm_pair else GEMM_NO_PAIR))
         if cfg.head_dim not in (64, 128):
             raise RuntimeError("head_dim must be 64 or 128")
         self.cfg = cfg
@@ -215,10 +218,10 @@ class Fp16Encoder(_EncoderBase):
     """fp16 weights and activations, fp32 accumulation and statistics."""
 
     def __init__(self, cfg: EncoderConfig, params: dict, device="cuda:0", micro_batches: int = 1,
-                 fuse_layernorm: bool | None = None):
+                 fuse_layernorm: bool | None = None, gemm_pair: bool | None = None):
         """``fuse_layernorm``: attention-output and FFN2 as one GEMM + residual + LayerNorm kernel each (5 launches
         per layer instead of 7); possible for hidden 768 and 1024, on by default for 768."""
-        super().__init__(cfg, params, device, micro_batches)
+        super().__init__(cfg, params, device, micro_batches, gemm_pair)
         self.fuse_layernorm = (cfg.hidden == 768) if fuse_layernorm is None else bool(fuse_layernorm)
         if self.fuse_layernorm and cfg.hidden not in (768, 1024):
             raise RuntimeError("the fused GEMM + LayerNorm kernel needs hidden == 768 or 1024")
@@ -254,6 +257,7 @@ class Fp16Encoder(_EncoderBase):
         # the weights of this object are written once, in __init__: every GEMM of the launch list carries the
         # constant-weights promise for its own call (nothing process-wide is switched)
         CW = GEMM_CONST_WEIGHTS
+        GF = self.gemm_flags  # the plain GEMMs also carry the kernel choice
         self._add("zen_embed_layernorm_f16", P(self.ids), None, self.word.data_ptr(), self.pos.data_ptr(),
                   self.type.data_ptr(), self.emb_g.data_ptr(), self.emb_b.data_ptr(), P(self.x[0]), None, 1.0,
                   ROUND_NEAREST_EVEN, T, S, H, cfg.vocab, cfg.eps)
@@ -264,7 +268,7 @@ class Fp16Encoder(_EncoderBase):
         for L in self.layers:
             x, xn = self.x[cur], self.x[cur ^ 1]
             self._add("zen_linear_f16_ex", P(x), H, L["wqkv"].data_ptr(), H, T, 3 * H, H, L["bqkv"].data_ptr(),
-                      ACT_NONE, DT_F16, P(self.qkv), 3 * H, CW)
+                      ACT_NONE, DT_F16, P(self.qkv), 3 * H, GF)
             self._add("zen_flash_attention_f16", P(self.qkv), P(self.qkv) + 2 * H, P(self.qkv) + 4 * H, P(self.ctx), None,
                       1.0, B, nh, S, hd, *qs, *qs, *qs, *os_, kv, 0, 1.0 / math.sqrt(hd))
             if self.fuse_layernorm:
@@ -273,18 +277,18 @@ class Fp16Encoder(_EncoderBase):
                           None, 1.0, ROUND_NEAREST_EVEN, CW)
             else:
                 self._add("zen_linear_f16_ex", P(self.ctx), H, L["wo"].data_ptr(), H, T, H, H, L["bo"].data_ptr(),
-                          ACT_NONE, DT_F16, P(self.ao), H, CW)
+                          ACT_NONE, DT_F16, P(self.ao), H, GF)
                 self._add("zen_add_layernorm_f16", P(self.ao), P(x), L["ln1_g"].data_ptr(), L["ln1_b"].data_ptr(),
                           P(self.h1), None, 1.0, ROUND_NEAREST_EVEN, T, H, cfg.eps)
             self._add("zen_linear_f16_ex", P(self.h1), H, L["w1"].data_ptr(), H, T, F, H, L["b1"].data_ptr(),
-                      ACT_GELU, DT_F16, P(self.g), F, CW)
+                      ACT_GELU, DT_F16, P(self.g), F, GF)
             if self.fuse_layernorm:
                 self._add("zen_linear_f16_add_layernorm_ex", P(self.g), F, L["w2"].data_ptr(), F, T, H, F,
                           L["b2"].data_ptr(), P(self.h1), H, L["ln2_g"].data_ptr(), L["ln2_b"].data_ptr(), cfg.eps, P(xn),
                           None, 1.0, ROUND_NEAREST_EVEN, CW)
             else:
                 self._add("zen_linear_f16_ex", P(self.g), F, L["w2"].data_ptr(), F, T, H, F, L["b2"].data_ptr(),
-                          ACT_NONE, DT_F16, P(self.o), H, CW)
+                          ACT_NONE, DT_F16, P(self.o), H, GF)
                 self._add("zen_add_layernorm_f16", P(self.o), P(self.h1), L["ln2_g"].data_ptr(), L["ln2_b"].data_ptr(),
                           P(xn), None, 1.0, ROUND_NEAREST_EVEN, T, H, cfg.eps)
             cur ^= 1
@@ -358,12 +362,18 @@ class Int8Encoder(_EncoderBase):
     """W8A8 encoder: int8 GEMM operands, int32 accumulation, fp16 residual stream / LayerNorm / softmax."""
 
     def __init__(self, cfg: EncoderConfig, params: dict, scales: Int8Scales, device="cuda:0", micro_batches: int = 1,
-                 fuse_layernorm: bool | None = None, prefetch_weights: bool = True):
+                 fuse_layernorm: bool | None = None, prefetch_weights: bool = True, gemm_pair: bool | None = None,
+                 fuse_attention: bool | None = None, keep_qkv: bool = False):
         """``fuse_layernorm``: run attention-output and FFN2 as one GEMM + residual + LayerNorm kernel each
         (5 launches per layer instead of 7).  Possible for hidden 768 and 1024; on by default for 768 only (at
         BERT-large's 12k-token shards the separate kernels measured faster: 8.98 vs 10.26 ms per pass).  In the
-        fused form the projection output is not rounded to fp16 before the residual add."""
-        super().__init__(cfg, params, device, micro_batches)
+        fused form the projection output is not rounded to fp16 before the residual add.
+        ``fuse_attention``: QKV projection and attention as ONE kernel (``zen_qkv_attention_i8``), possible for
+        sequences of at most 128 tokens with head size 64 and on by default there; same results bit for bit.
+        ``keep_qkv``: the fused kernel also writes the fp16 projection to ``self.qkv`` (tests, inspection)."""
+        super().__init__(cfg, params, device, micro_batches, gemm_pair)
+        self.fuse_attention = fuse_attention
+        self.keep_qkv = bool(keep_qkv)
         self.fuse_layernorm = (cfg.hidden == 768) if fuse_layernorm is None else bool(fuse_layernorm)
         if self.fuse_layernorm and cfg.hidden not in (768, 1024):
             raise RuntimeError("the fused GEMM + LayerNorm kernel needs hidden == 768 or 1024")
@@ -410,7 +420,13 @@ class Int8Encoder(_EncoderBase):
         # the weights of this object are written once, in __init__: every GEMM of the launch list carries the
         # constant-weights promise for its own call (nothing process-wide is switched)
         CW = GEMM_CONST_WEIGHTS
+        GF = self.gemm_flags  # the plain GEMMs also carry the kernel choice
         sc = self.act_scales
+        can_fuse = S <= 128 and hd == 64
+        if self.fuse_attention and not can_fuse:
+            raise RuntimeError("the fused QKV + attention kernel needs seq <= 128 and head_dim == 64")
+        fused_attn = can_fuse if self.fuse_attention is None else bool(self.fuse_attention)
+        self.launches_per_layer = (5 if self.fuse_layernorm else 7) - (1 if fused_attn else 0)
         self._add("zen_embed_layernorm_f16", P(self.ids), None, self.word.data_ptr(), self.pos.data_ptr(),
                   self.type.data_ptr(), self.emb_g.data_ptr(), self.emb_b.data_ptr(), P(self.x[0]), P(self.xq[0]),
                   sc[0]["x"], ROUND_NEAREST_EVEN, T, S, H, cfg.vocab, cfg.eps)
@@ -426,11 +442,16 @@ class Int8Encoder(_EncoderBase):
             nbytes = lambda t: t.numel() * t.element_size()
             pf = lambda *ts: [v for t in ts for v in ((t.data_ptr(), nbytes(t)) if self.prefetch_weights and t is not None
                                                        else (None, 0))]
-            self._add("zen_linear_i8_ex", P(xq), H, L["wqkv"].data_ptr(), H, T, 3 * H, H, a["x"],
-                      L["wqkv_s"].data_ptr(), L["bqkv"].data_ptr(), ACT_NONE, DT_F16, 1.0, ROUND_NEAREST_EVEN,
-                      P(self.qkv), 3 * H, *pf(L["wo"], L["w1"]), CW)
-            self._add("zen_flash_attention_f16", P(self.qkv), P(self.qkv) + 2 * H, P(self.qkv) + 4 * H, P(self.ctx),
-                      P(self.ctxq), a["ctx"], B, nh, S, hd, *qs, *qs, *qs, *os_, kv, 0, 1.0 / math.sqrt(hd))
+            if fused_attn:
+                self._add("zen_qkv_attention_i8", P(xq), H, L["wqkv"].data_ptr(), H, B, S, nh, H, a["x"],
+                          L["wqkv_s"].data_ptr(), L["bqkv"].data_ptr(), kv, 1.0 / math.sqrt(hd), P(self.ctx), P(self.ctxq),
+                          a["ctx"], P(self.qkv) if self.keep_qkv else None, *pf(L["wo"], L["w1"]), CW)
+            else:
+                self._add("zen_linear_i8_ex", P(xq), H, L["wqkv"].data_ptr(), H, T, 3 * H, H, a["x"],
+                          L["wqkv_s"].data_ptr(), L["bqkv"].data_ptr(), ACT_NONE, DT_F16, 1.0, ROUND_NEAREST_EVEN,
+                          P(self.qkv), 3 * H, *pf(L["wo"], L["w1"]), GF)
+                self._add("zen_flash_attention_f16", P(self.qkv), P(self.qkv) + 2 * H, P(self.qkv) + 4 * H, P(self.ctx),
+                          P(self.ctxq), a["ctx"], B, nh, S, hd, *qs, *qs, *qs, *os_, kv, 0, 1.0 / math.sqrt(hd))
             if self.fuse_layernorm:
                 self._add("zen_linear_i8_add_layernorm_ex", P(self.ctxq), H, L["wo"].data_ptr(), H, T, H, H, a["ctx"],
                           L["wo_s"].data_ptr(), L["bo"].data_ptr(), P(x), H, L["ln1_g"].data_ptr(), L["ln1_b"].data_ptr(),
@@ -438,12 +459,12 @@ class Int8Encoder(_EncoderBase):
             else:
                 self._add("zen_linear_i8_ex", P(self.ctxq), H, L["wo"].data_ptr(), H, T, H, H, a["ctx"],
                           L["wo_s"].data_ptr(), L["bo"].data_ptr(), ACT_NONE, DT_F16, 1.0, ROUND_NEAREST_EVEN,
-                          P(self.ao), H, None, 0, None, 0, CW)
+                          P(self.ao), H, None, 0, None, 0, GF)
                 self._add("zen_add_layernorm_f16", P(self.ao), P(x), L["ln1_g"].data_ptr(), L["ln1_b"].data_ptr(),
                           P(self.h1), P(self.h1q), a["h1"], ROUND_NEAREST_EVEN, T, H, cfg.eps)
             self._add("zen_linear_i8_ex", P(self.h1q), H, L["w1"].data_ptr(), H, T, F, H, a["h1"],
                       L["w1_s"].data_ptr(), L["b1"].data_ptr(), ACT_GELU, DT_S8, a["gelu"], ROUND_NEAREST_EVEN,
-                      P(self.gq), F, *pf(L["w2"], None if last else self.layers[li + 1]["wqkv"]), CW)
+                      P(self.gq), F, *pf(L["w2"], None if last else self.layers[li + 1]["wqkv"]), GF)
             if self.fuse_layernorm:
                 self._add("zen_linear_i8_add_layernorm_ex", P(self.gq), F, L["w2"].data_ptr(), F, T, H, F, a["gelu"],
                           L["w2_s"].data_ptr(), L["b2"].data_ptr(), P(self.h1), H, L["ln2_g"].data_ptr(),
@@ -452,7 +473,7 @@ class Int8Encoder(_EncoderBase):
             else:
                 self._add("zen_linear_i8_ex", P(self.gq), F, L["w2"].data_ptr(), F, T, H, F, a["gelu"],
                           L["w2_s"].data_ptr(), L["b2"].data_ptr(), ACT_NONE, DT_F16, 1.0, ROUND_NEAREST_EVEN,
-                          P(self.o), H, None, 0, None, 0, CW)
+                          P(self.o), H, None, 0, None, 0, GF)
                 self._add("zen_add_layernorm_f16", P(self.o), P(self.h1), L["ln2_g"].data_ptr(), L["ln2_b"].data_ptr(),
                           P(xn), None if last else P(xqn), 1.0 if last else sc[li + 1]["x"], ROUND_NEAREST_EVEN, T, H,
                           cfg.eps)

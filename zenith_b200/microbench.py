@@ -47,6 +47,7 @@ def main() -> None:
     ap.add_argument("--k", type=int, default=768)
     ap.add_argument("--epilogue", choices=["s32", "f32", "f16", "gelu_s8", "gelu_f16"], default="f16")
     ap.add_argument("--tile-n", type=int, default=0)
+    ap.add_argument("--pair", choices=["auto", "on", "off"], default="auto", help="CTA-pair kernel: forced on / off")
     ap.add_argument("--rows", type=int, default=4096)
     ap.add_argument("--hidden", type=int, default=768)
     ap.add_argument("--b", type=int, default=32)
@@ -60,6 +61,7 @@ def main() -> None:
     dev = torch.device("cuda:0")
     flush = None if a.no_flush else torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     out = {"case": a.case}
+    pair = {"auto": None, "on": True, "off": False}[a.pair]
     if a.case == "gemm_i8":
         x = torch.randint(-128, 128, (a.m, a.k), dtype=torch.int8, device=dev)
         w = torch.randint(-128, 128, (a.n, a.k), dtype=torch.int8, device=dev)
@@ -69,8 +71,8 @@ def main() -> None:
               "gelu_s8": dict(act="gelu", out_dtype=torch.int8, out_scale=0.05),
               "gelu_f16": dict(act="gelu", out_dtype=torch.float16)}[a.epilogue]
         y = torch.empty((a.m, a.n), dtype=kw["out_dtype"], device=dev)
-        med, best = _time(lambda: ops.linear_int8(x, w, 0.02, ws, b, out=y, tile_n=a.tile_n, **kw), a.iters, flush)
-        out.update(m=a.m, n=a.n, k=a.k, epilogue=a.epilogue, tile_n=a.tile_n, us=med, us_min=best,
+        med, best = _time(lambda: ops.linear_int8(x, w, 0.02, ws, b, out=y, tile_n=a.tile_n, pair=pair, **kw), a.iters, flush)
+        out.update(m=a.m, n=a.n, k=a.k, epilogue=a.epilogue, tile_n=a.tile_n, pair=a.pair, us=med, us_min=best,
                    tops=2.0 * a.m * a.n * a.k / med / 1e6)
     elif a.case == "gemm_i8_ln":
         n = a.n if a.n in (768, 1024) else 768
@@ -89,7 +91,7 @@ def main() -> None:
         w = torch.randn(a.n, a.k, device=dev, dtype=torch.float16)
         b = torch.randn(a.n, device=dev)
         y = torch.empty((a.m, a.n), dtype=torch.float16, device=dev)
-        med, best = _time(lambda: ops.linear_fp16(x, w, b, out=y, tile_n=a.tile_n), a.iters, flush)
+        med, best = _time(lambda: ops.linear_fp16(x, w, b, out=y, tile_n=a.tile_n, pair=pair), a.iters, flush)
         out.update(m=a.m, n=a.n, k=a.k, tile_n=a.tile_n, us=med, us_min=best, tflops=2.0 * a.m * a.n * a.k / med / 1e6)
     elif a.case == "add_ln":
         x = torch.randn(a.rows, a.hidden, device=dev, dtype=torch.float16)
@@ -115,16 +117,16 @@ def main() -> None:
             return ids, lens
 
         if a.dtype == "int8":
-            enc = Int8Encoder(cfg, params, calibrate(cfg, params, [batch() for _ in range(4)], dev), dev)
+            enc = Int8Encoder(cfg, params, calibrate(cfg, params, [batch() for _ in range(4)], dev), dev, gemm_pair=pair)
         else:
-            enc = Fp16Encoder(cfg, params, dev)
+            enc = Fp16Encoder(cfg, params, dev, gemm_pair=pair)
         enc.capture(a.batch, a.seq)
         enc.set_inputs(*batch())
         med, best = _time(enc.replay, a.iters, flush)
         T = a.batch * a.seq
         gemm_ops = 2.0 * T * (4 * cfg.hidden**2 + 2 * cfg.hidden * cfg.ffn) * cfg.layers
         attn_flops = 4.0 * a.batch * cfg.heads * a.seq * a.seq * cfg.head_dim * cfg.layers
-        out.update(config=a.config, dtype=a.dtype, batch=a.batch, seq=a.seq, us=med, us_min=best,
+        out.update(config=a.config, dtype=a.dtype, batch=a.batch, seq=a.seq, pair=a.pair, us=med, us_min=best,
                    seq_per_s=a.batch / med * 1e6, gemm_tops=gemm_ops / med / 1e6, attn_tflops=attn_flops / med / 1e6,
                    launches=enc.launches_per_forward)
     else:

@@ -453,6 +453,42 @@ def flash_attention(q, k, v, *, causal: bool = False, kv_lens=None, scale: float
     return out
 
 
+def qkv_attention_int8(xq, wqkv, x_scale: float, w_scale, bias, B: int, S: int, heads: int, *, kv_lens=None,
+                       scale: float | None = None, out_scale: float | None = None, emit_qkv: bool = False,
+                       constant_weights=False, prefetch=()):
+    """W8A8 QKV projection + attention in one kernel (``zen_qkv_attention_i8``): sequences of at most 128 tokens,
+    head size 64.  ``xq`` int8 ``[B*S, K]``, ``wqkv`` int8 ``[3*heads*64, K]``.  Returns fp16 ``ctx [B*S, heads*64]``,
+    then (with ``out_scale``) its int8 copy, then (with ``emit_qkv``) the fp16 projection ``[B*S, 3*heads*64]``.
+    Bit-identical to ``linear_int8(..., out_dtype=float16)`` followed by ``flash_attention_strided``."""
+    _require(xq, "xq", torch.int8, 2)
+    _require(wqkv, "wqkv", torch.int8, 2)
+    hidden = heads * 64
+    T, K = xq.shape
+    if T != B * S or tuple(wqkv.shape) != (3 * hidden, K):
+        raise RuntimeError("shape mismatch")
+    if w_scale is not None:
+        _require(w_scale, "w_scale", torch.float32, 1)
+    if bias is not None:
+        _require(bias, "bias", torch.float32, 1)
+    if kv_lens is not None:
+        _require(kv_lens, "kv_lens", torch.int32, 1)
+    if len(prefetch) > 2:
+        raise RuntimeError("prefetch takes at most two CUDA tensors")
+    ctx = torch.empty((T, hidden), dtype=torch.float16, device=xq.device)
+    ctxq = torch.empty((T, hidden), dtype=torch.int8, device=xq.device) if out_scale is not None else None
+    qkv = torch.empty((T, 3 * hidden), dtype=torch.float16, device=xq.device) if emit_qkv else None
+    hint = [v for t in prefetch for v in (t.data_ptr(), t.numel() * t.element_size())] + [None, 0] * (2 - len(prefetch))
+    _call("zen_qkv_attention_i8", xq.data_ptr(), K, wqkv.data_ptr(), K, B, S, heads, K, float(x_scale), _ptr(w_scale),
+          _ptr(bias), _ptr(kv_lens), float(1.0 / math.sqrt(64) if scale is None else scale), ctx.data_ptr(), _ptr(ctxq),
+          float(out_scale or 1.0), _ptr(qkv), *hint, _capi.GEMM_CONST_WEIGHTS if constant_weights else 0, _stream())
+    out = [ctx]
+    if ctxq is not None:
+        out.append(ctxq)
+    if qkv is not None:
+        out.append(qkv)
+    return out[0] if len(out) == 1 else tuple(out)
+
+
 # --------------------------------------------------------------------------------------------
 # embedding
 # --------------------------------------------------------------------------------------------
