@@ -35,7 +35,7 @@ def test_patterns_are_found_and_replaced_by_kernel_leaves():
     assert counts["gelu_tanh_to_native"] == 1 and counts["manual_layernorm_to_native"] == 1
     assert counts["linear_gelu_to_fused"] == 1
     after = targets(gm)
-    for leaf in ("zenith_flash_attention", "zenith_causal_flash_attention", "zenith_gelu", "zenith_layernorm",
+    for leaf in ("zenith_flash_attention", "zenith_masked_flash_attention", "zenith_gelu", "zenith_layernorm",
                  "zenith_linear_gelu"):
         assert leaf in after
     assert "softmax" not in after and "tanh" not in after and "sqrt" not in after
@@ -70,3 +70,57 @@ def test_replacements_refuse_cpu_tensors():
         P.zenith_flash_attention(x, x, x)
     with pytest.raises(RuntimeError):
         P.zenith_gelu(x)
+
+
+def test_the_masked_pattern_keeps_the_mask_and_the_leaf_reads_it():
+    """A key-padding mask must not be turned into causal attention: the rewritten node still receives the mask,
+    and the classifier tells the three kinds of mask apart."""
+    class Att(torch.nn.Module):
+        def forward(self, q, k, v, mask):
+            return P.causal_sdpa_pattern(q, k, v, mask)
+
+    gm = torch.fx.symbolic_trace(Att())
+    assert P.apply_patterns(gm)["causal_sdpa_to_flash"] == 1
+    node = next(n for n in gm.graph.nodes if n.op == "call_function" and n.target is P.zenith_masked_flash_attention)
+    assert len(node.args) == 4 and node.args[3].name == "mask"
+    B, S = 3, 16
+    neg = torch.finfo(torch.float32).min
+    causal = torch.zeros(S, S).masked_fill(torch.ones(S, S, dtype=torch.bool).triu(1), neg)
+    assert P.classify_mask(causal, B, S, S)[0] == "causal"
+    assert P.classify_mask(causal[None, None], B, S, S)[0] == "causal"
+    lens = torch.tensor([16, 9, 1])
+    pad = torch.zeros(B, 1, 1, S).masked_fill(torch.arange(S)[None, None, None, :] >= lens[:, None, None, None], neg)
+    kind, got = P.classify_mask(pad, B, S, S)
+    assert kind == "kv_lens" and got.tolist() == [16, 9, 1] and got.dtype == torch.int32
+    kind, got = P.classify_mask(pad.expand(B, 1, S, S), B, S, S)  # the same mask, materialised per query
+    assert kind == "kv_lens" and got.tolist() == [16, 9, 1]
+    assert P.classify_mask(torch.zeros(B, 1, 1, S), B, S, S)[0] == "none"
+    holes = pad.clone()
+    holes[1, 0, 0, 2] = neg  # a masked key in the middle: not a suffix
+    assert P.classify_mask(holes, B, S, S)[0] == "other"
+    assert P.classify_mask(torch.randn(B, 1, S, S), B, S, S)[0] == "other"  # a relative-position bias
+    assert P.classify_mask(torch.ones(B, 1, 1, S, dtype=torch.bool), B, S, S)[0] == "other"
+
+
+def test_shapes_the_kernels_do_not_cover_are_computed_by_pytorch():
+    """head size 32 (no kernel) and a bias-like mask: the leaves return what the original expression returns, on
+    any device, instead of raising."""
+    g = torch.Generator().manual_seed(0)
+    q, k, v = (torch.randn(2, 3, 10, 32, generator=g) for _ in range(3))
+    mask = torch.randn(2, 1, 10, 10, generator=g)
+    assert torch.allclose(P.zenith_flash_attention(q, k, v), P.sdpa_pattern(q, k, v), atol=1e-6)
+    assert torch.allclose(P.zenith_masked_flash_attention(q, k, v, mask), P.causal_sdpa_pattern(q, k, v, mask), atol=1e-6)
+    x, w, b = torch.randn(5, 12, generator=g), torch.randn(7, 12, generator=g), torch.randn(7, generator=g)
+    assert torch.allclose(P.zenith_linear_gelu(x, w, b), P.linear_gelu_pattern(x, w, b), atol=1e-6)
+
+
+def test_functional_sdpa_calls_are_rewritten():
+    class Att(torch.nn.Module):
+        def forward(self, q, k, v, mask):
+            a = F.scaled_dot_product_attention(q, k, v, attn_mask=mask, dropout_p=0.0, is_causal=False)
+            return a + F.scaled_dot_product_attention(q, k, v)
+
+    gm = torch.fx.symbolic_trace(Att())
+    counts = P.apply_patterns(gm)
+    assert counts["functional_sdpa_masked_to_flash"] == 1 and counts["functional_sdpa_to_flash"] == 1
+    assert "scaled_dot_product_attention" not in targets(gm)

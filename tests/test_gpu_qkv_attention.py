@@ -32,13 +32,13 @@ def two_kernels(xq, wq, ws, b, B, S, heads, lens, out_scale, x_scale=0.02):
 
 @pytest.mark.parametrize("B,S,heads,K,lens", [
     (1, 128, 1, 128, None), (2, 128, 2, 256, [128, 77]), (3, 96, 4, 256, [96, 64, 1]), (2, 17, 2, 64, [17, 5]),
-    (1, 1, 1, 64, None), (4, 128, 12, 768, [128, 100, 33, 0]), (5, 40, 3, 192, [40, 39, 16, 15, 0]),
+    (2, 8, 1, 64, [8, 3]), (4, 128, 12, 768, [128, 100, 33, 0]), (5, 40, 3, 192, [40, 39, 16, 15, 0]),
     (32, 128, 12, 768, "ragged")])
 def test_fused_equals_projection_then_attention(cuda, B, S, heads, K, lens):
     H = heads * 64
     x = rng(B * S + K).integers(-128, 128, (B * S, K), dtype=np.int8)
     w = rng(K).integers(-128, 128, (3 * H, K), dtype=np.int8)
-    ws = ((rng(3).random(3 * H) + 0.5) * (0.4 / np.sqrt(K))).astype(np.float32)
+    ws = ((rng(3).random(3 * H) + 0.5) * (0.009 / np.sqrt(K))).astype(np.float32)  # Q, K, V of unit scale
     b = (rng(4).standard_normal(3 * H) * 0.1).astype(np.float32)
     if isinstance(lens, str):
         lens = (S - rng(5).integers(0, 33, B)).tolist()
@@ -63,7 +63,7 @@ def test_fused_equals_projection_then_attention(cuda, B, S, heads, K, lens):
         o = O.attention(split(f[:, :H]), split(f[:, H:2 * H]), split(f[:, 2 * H:]), None if lens is None else np.array(lens, np.int32))
         o = o.transpose(0, 2, 1, 3).reshape(B * S, H)
         got = ctx.float().cpu().numpy()
-        assert np.max(np.abs(got - o)) < 1e-2
+        assert np.max(np.abs(got - o)) < 1e-2 * max(1.0, np.abs(o).max())
         assert np.array_equal(ctxq.cpu().numpy(), O.quantize(got, 0.02))
 
 

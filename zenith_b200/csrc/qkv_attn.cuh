@@ -296,37 +296,37 @@ qkv_attn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       // ---- projection epilogue: 192 accumulators of this row -> fp16 Q, K, V rows in shared memory
       if (!mbar_wait(&acc_full[set], it & 1u, abort_flag)) break;
       tc_fence_after_sync();
+      // one step per tile (Q, K, V): 64 accumulator columns in one tensor-memory load, so that the load latency is
+      // paid three times per row instead of twelve and the 32 column pairs of a step overlap one another
 #pragma unroll 1
-      for (int i = 0; i < QA_BN / 16; ++i) {
-        uint32_t a[16];
+      for (int t = 0; t < 3; ++t) {
+        uint32_t a[64];
         __syncwarp();
-        tmem_ld_32x16(region + uint32_t(i * 16), a);
+        tmem_ld_32x64(region + uint32_t(t * 64), a);
         tmem_wait_ld();
-        uint32_t w[8];
+        uint8_t* trow = sQ + t * QA_TILE_BYTES + r * 128;
+        __half* grow = (p.qkv_out != nullptr && r < p.S)
+                           ? p.qkv_out + (size_t(b) * p.S + r) * (3 * hidden) + t * hidden + h * 64
+                           : nullptr;
 #pragma unroll
-        for (int j4 = 0; j4 < 4; ++j4) {
-          const float4 s4 = reinterpret_cast<const float4*>(s_scale + i * 16)[j4];
-          const float4 b4 = reinterpret_cast<const float4*>(s_bias + i * 16)[j4];
+        for (int u = 0; u < 8; ++u) {  // 16-byte unit u of the row: columns 8 u .. 8 u + 7
+          uint32_t w[4];
 #pragma unroll
-          for (int hh = 0; hh < 2; ++hh) {
-            const int e = 4 * j4 + 2 * hh;
-            const float2 av = make_float2(float(int32_t(a[e])), float(int32_t(a[e + 1])));
-            // zen_det_dequant on a column pair: each product rounded before the bias is added
-            const float2 v = f2mul_then_add(f2mul(av, xs2), hh ? make_float2(s4.z, s4.w) : make_float2(s4.x, s4.y),
-                                            hh ? make_float2(b4.z, b4.w) : make_float2(b4.x, b4.y));
-            const __half2 hv = __floats2half2_rn(v.x, v.y);
-            w[e >> 1] = *reinterpret_cast<const uint32_t*>(&hv);
+          for (int j2 = 0; j2 < 2; ++j2) {
+            const float4 s4 = reinterpret_cast<const float4*>(s_scale + t * 64 + u * 8)[j2];
+            const float4 b4 = reinterpret_cast<const float4*>(s_bias + t * 64 + u * 8)[j2];
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+              // zen_det_dequant on a column pair: each product rounded before the bias is added
+              const int e = u * 8 + 4 * j2 + 2 * hh;
+              const float2 v = f2mul_then_add(f2mul(make_float2(float(int32_t(a[e])), float(int32_t(a[e + 1]))), xs2), hh ? make_float2(s4.z, s4.w) : make_float2(s4.x, s4.y),
+                                              hh ? make_float2(b4.z, b4.w) : make_float2(b4.x, b4.y));
+              const __half2 hv = __floats2half2_rn(v.x, v.y);
+              w[2 * j2 + hh] = *reinterpret_cast<const uint32_t*>(&hv);
+            }
           }
-        }
-        // step i: tile i / 4 (Q, K, V), 16-byte units 2 (i % 4) and 2 (i % 4) + 1 of the row, 128-byte swizzle
-        uint8_t* trow = sQ + (i >> 2) * QA_TILE_BYTES + r * 128;
-        *reinterpret_cast<uint4*>(trow + (((2 * (i & 3)) ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-        *reinterpret_cast<uint4*>(trow + (((2 * (i & 3) + 1) ^ (r & 7)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
-        if (p.qkv_out != nullptr && r < p.S) {
-          uint4* dst = reinterpret_cast<uint4*>(p.qkv_out + (size_t(b) * p.S + r) * (3 * hidden) + (i >> 2) * hidden + h * 64 +
-                                                (i & 3) * 16);
-          dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
-          dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+          *reinterpret_cast<uint4*>(trow + ((u ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);  // 128-byte swizzle
+          if (grow != nullptr) reinterpret_cast<uint4*>(grow)[u] = make_uint4(w[0], w[1], w[2], w[3]);
         }
       }
       tc_fence_before_sync();
@@ -340,19 +340,19 @@ qkv_attn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       float l_sum = 0.f;
       float mx = -INFINITY;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        const int rem = lim - c * 32;
+      for (int c = 0; c < 2; ++c) {
+        const int rem = lim - c * 64;
         if (rem <= 0) break;  // uniform: the key length is the same for every row of the sequence
-        uint32_t sv[32];
+        uint32_t sv[64];
         __syncwarp();
-        tmem_ld_32x32(region + uint32_t(c * 32), sv);
+        tmem_ld_32x64(region + uint32_t(c * 64), sv);
         tmem_wait_ld();
-        if (rem >= 32) {
+        if (rem >= 64) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sv[i]));
+          for (int i = 0; i < 64; ++i) mx = fmaxf(mx, __uint_as_float(sv[i]));
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
+          for (int i = 0; i < 64; ++i)
             if (i < rem) mx = fmaxf(mx, __uint_as_float(sv[i]));
         }
       }
@@ -412,38 +412,40 @@ qkv_attn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
       uint8_t* sty = sQ + quad * 4096;  // 32 rows x 128 B, 128-byte swizzle
       uint8_t* stq = sK + quad * 4096;  // 32 rows x 64 B, 64-byte swizzle
-#pragma unroll 1
-      for (int g = 0; g < 4; ++g) {
-        uint32_t ov[16];
+      {
+        uint32_t ov[64];
         if (kv_len > 0) {
           __syncwarp();
-          tmem_ld_32x16(region + 128u + uint32_t(g * 16), ov);
+          tmem_ld_32x64(region + 128u, ov);
           tmem_wait_ld();
         } else {
 #pragma unroll
-          for (int i = 0; i < 16; ++i) ov[i] = 0u;  // a sequence without keys yields zeros
-        }
-        uint32_t w[8];
-        float2 val[8];  // the fp16 values that are stored: the int8 copy quantizes these
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const __half2 hv = __floats2half2_rn(__uint_as_float(ov[2 * i]) * inv, __uint_as_float(ov[2 * i + 1]) * inv);
-          w[i] = *reinterpret_cast<const uint32_t*>(&hv);
-          val[i] = __half22float2(hv);
+          for (int i = 0; i < 64; ++i) ov[i] = 0u;  // a sequence without keys yields zeros
         }
         uint8_t* srow = sty + lane * 128;
-        *reinterpret_cast<uint4*>(srow + (((2 * g) ^ (lane & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-        *reinterpret_cast<uint4*>(srow + (((2 * g + 1) ^ (lane & 7)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
-        if (p.ctxq) {
-          uint32_t qw[4];
-          const uint32_t risky = quantize_pairs_rn<16>(val, inv_o_scale, qw);
-          if (risky) {
 #pragma unroll
-            for (int e = 0; e < 16; ++e)
-              if (risky & (1u << e))
-                patch_q_byte(qw, e, zen_det_round_clamp_i8(ZEN_DIV((e & 1) ? val[e >> 1].y : val[e >> 1].x, p.ctx_scale), 0));
+        for (int g = 0; g < 4; ++g) {
+          uint32_t w[8];
+          float2 val[8];  // the fp16 values that are stored: the int8 copy quantizes these
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const __half2 hv = __floats2half2_rn(__uint_as_float(ov[16 * g + 2 * i]) * inv, __uint_as_float(ov[16 * g + 2 * i + 1]) * inv);
+            w[i] = *reinterpret_cast<const uint32_t*>(&hv);
+            val[i] = __half22float2(hv);
           }
-          *reinterpret_cast<uint4*>(stq + lane * 64 + ((g ^ ((lane >> 1) & 3)) << 4)) = make_uint4(qw[0], qw[1], qw[2], qw[3]);
+          *reinterpret_cast<uint4*>(srow + (((2 * g) ^ (lane & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+          *reinterpret_cast<uint4*>(srow + (((2 * g + 1) ^ (lane & 7)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
+          if (p.ctxq) {
+            uint32_t qw[4];
+            const uint32_t risky = quantize_pairs_rn<16>(val, inv_o_scale, qw);
+            if (risky) {
+#pragma unroll
+              for (int e = 0; e < 16; ++e)
+                if (risky & (1u << e))
+                  patch_q_byte(qw, e, zen_det_round_clamp_i8(ZEN_DIV((e & 1) ? val[e >> 1].y : val[e >> 1].x, p.ctx_scale), 0));
+            }
+            *reinterpret_cast<uint4*>(stq + lane * 64 + ((g ^ ((lane >> 1) & 3)) << 4)) = make_uint4(qw[0], qw[1], qw[2], qw[3]);
+          }
         }
       }
       tc_fence_before_sync();

@@ -2,10 +2,15 @@
 
 Same surface as the reference's pattern module (zenith/optimization/fx_patterns.py:60-230: ``FXPattern``,
 ``sdpa_pattern`` / ``zenith_sdpa_replacement``, ``causal_sdpa_pattern``, ``gelu_tanh_pattern``,
-``layernorm_pattern``, ``get_*_patterns``), with three differences: the replacements call the B200 kernels
-and nothing else (no PyTorch fallback: they raise on CPU tensors); the causal pattern, which the reference
-defines but never returns from ``get_attention_patterns`` (fx_patterns.py:117-135, 187-196), is registered;
-and two fused patterns the kernels support are added (Linear -> tanh-GELU, residual add -> LayerNorm).
+``layernorm_pattern``, ``get_*_patterns``), with these differences: the replacements call the B200 kernels
+(a CPU tensor of a supported shape raises; there is no CPU path); the masked pattern, which the reference
+defines but never returns from ``get_attention_patterns`` (fx_patterns.py:117-135, 187-196), is registered,
+and its replacement READS the mask: a lower-triangular additive mask runs the causal kernel, a key-padding
+mask (the same suffix of keys masked for every query of a sequence) becomes per-sequence key lengths, and
+any other mask - like any head size or width the kernels do not cover - is computed with the original
+PyTorch expression, so a rewrite never changes what a model computes and never makes a working model fail;
+patterns for ``F.scaled_dot_product_attention`` (the form a HuggingFace encoder traces to) are added, and so
+are two fused patterns the kernels support (Linear -> tanh-GELU, residual add -> LayerNorm).
 
 ``apply_patterns(gm)`` rewrites a ``torch.fx.GraphModule`` in place; ``zenith_backend`` is a
 ``torch.compile(model, backend=zenith_backend)`` entry that applies them to the captured graph.
@@ -36,22 +41,86 @@ class FXPattern:
 # ---------------------------------------------------------------------------------------------
 # leaves: calls into the kernels (opaque to the tracer, so they survive as single graph nodes)
 # ---------------------------------------------------------------------------------------------
-def _attention(q, k, v, causal):
+_SUPPORTED_HEAD_DIMS = (64, 128)
+_MASKED = -1.0e4  # additive-mask entries at or below this count as "masked" (HuggingFace uses the dtype's minimum)
+
+
+def _reference_attention(q, k, v, mask=None, causal=False, scale=None):
+    """The expression the patterns match, evaluated by PyTorch: what runs when the kernels do not cover a case."""
+    scale = q.shape[-1] ** -0.5 if scale is None else scale
+    w = torch.matmul(q, k.transpose(-2, -1)) * scale
+    if causal:
+        S = q.shape[-2]
+        w = w.masked_fill(torch.ones(S, k.shape[-2], dtype=torch.bool, device=q.device).triu(1), float("-inf"))
+    if mask is not None:
+        w = w + mask
+    return torch.matmul(F.softmax(w, dim=-1), v)
+
+
+def classify_mask(mask, batch: int, q_len: int, k_len: int):
+    """What an additive attention mask means for the kernels: ``("none", None)`` (all zeros), ``("causal", None)``
+    (0 on and below the diagonal, masked above, the same for every batch / head), ``("kv_lens", lengths)`` (for
+    every query of sequence b the keys from ``lengths[b]`` on are masked and the others are 0), or
+    ``("other", None)``.  ``mask`` broadcasts against ``[batch, heads, q_len, k_len]``."""
+    if mask is None:
+        return "none", None
+    if mask.dtype == torch.bool:
+        return "other", None
+    m = mask
+    while m.dim() < 4:
+        m = m.unsqueeze(0)
+    if m.shape[-1] != k_len or m.shape[1] != 1 or m.shape[0] not in (1, batch) or m.shape[2] not in (1, q_len):
+        return "other", None
+    masked = m <= _MASKED
+    if not bool(((m == 0) | masked).all()):
+        return "other", None
+    if not bool(masked.any()):
+        return "none", None
+    if m.shape[2] == q_len and q_len == k_len and m.shape[0] == 1:
+        tri = torch.ones(q_len, k_len, dtype=torch.bool, device=m.device).triu(1)
+        if bool((masked[0, 0] == tri).all()):
+            return "causal", None
+    rows = masked if m.shape[2] == 1 else masked[:, :, :1]
+    if m.shape[2] != 1 and not bool((masked == rows).all()):
+        return "other", None  # the mask differs between queries and is not the causal one
+    key = rows[:, 0, 0]  # [1 or batch, k_len]
+    lengths = (~key).sum(dim=-1)
+    prefix = torch.arange(k_len, device=m.device)[None, :] < lengths[:, None]
+    if not bool((prefix == ~key).all()):
+        return "other", None  # masked keys are not a suffix
+    return "kv_lens", lengths.expand(batch).to(torch.int32).contiguous()
+
+
+def _kernel_covers(q, k, v) -> bool:
+    return (q.dim() == 4 and q.shape == k.shape == v.shape and q.shape[-1] in _SUPPORTED_HEAD_DIMS and q.is_floating_point())
+
+
+def _attention(q, k, v, causal=False, kv_lens=None, scale=None):
     dt = q.dtype
     out = ops.flash_attention(q.to(torch.float16).contiguous(), k.to(torch.float16).contiguous(),
-                              v.to(torch.float16).contiguous(), causal=causal)
+                              v.to(torch.float16).contiguous(), causal=causal, kv_lens=kv_lens, scale=scale)
     return out.to(dt)
 
 
 @torch.fx.wrap
 def zenith_flash_attention(q, k, v):
-    """softmax(q k^T / sqrt(d)) v on ``[batch, heads, seq, d]`` tensors (d = 64 or 128)."""
-    return _attention(q, k, v, False)
+    """softmax(q k^T / sqrt(d)) v on ``[batch, heads, seq, d]`` tensors; d = 64 or 128 run on the kernels, any
+    other shape is computed by PyTorch."""
+    if not _kernel_covers(q, k, v):
+        return _reference_attention(q, k, v)
+    return _attention(q, k, v)
 
 
 @torch.fx.wrap
-def zenith_causal_flash_attention(q, k, v):
-    return _attention(q, k, v, True)
+def zenith_masked_flash_attention(q, k, v, mask, scale=None, is_causal=False):
+    """softmax(scale q k^T + mask) v.  The mask is read (``classify_mask``): causal and key-padding masks run on
+    the kernels, anything else is computed by PyTorch with the mask as given."""
+    if not _kernel_covers(q, k, v):
+        return _reference_attention(q, k, v, mask, is_causal, scale)
+    kind, lens = classify_mask(mask, q.shape[0], q.shape[-2], k.shape[-2])
+    if kind == "other":
+        return _reference_attention(q, k, v, mask, is_causal, scale)
+    return _attention(q, k, v, bool(is_causal) or kind == "causal", lens, scale)
 
 
 @torch.fx.wrap
@@ -76,6 +145,8 @@ def zenith_add_layernorm(x, residual, weight, bias, eps):
 
 @torch.fx.wrap
 def zenith_linear_gelu(x, weight, bias):
+    if x.shape[-1] % 8 or x.dtype not in (torch.float16, torch.float32):  # widths the GEMM kernels do not take
+        return F.gelu(F.linear(x, weight, bias), approximate="tanh")
     x2 = x.reshape(-1, x.shape[-1]).contiguous()
     if x.dtype == torch.float16:
         y = ops.linear_fp16(x2, weight.contiguous(), None if bias is None else bias.float(), act="gelu")
@@ -105,9 +176,21 @@ def causal_sdpa_pattern(q, k, v, mask):
 
 
 def zenith_causal_sdpa_replacement(q, k, v, mask):
-    """``mask`` is taken to be the additive lower-triangular mask the pattern's name promises (the reference
-    makes the same assumption: it passes ``is_causal=True``, fx_patterns.py:127-130); it is not read."""
-    return zenith_causal_flash_attention(q, k, v)
+    """The pattern matches ANY additive mask (a key-padding mask as well as the causal one the reference's name
+    promises, fx_patterns.py:117-135), so the replacement hands the mask on and the leaf decides what it is."""
+    return zenith_masked_flash_attention(q, k, v, mask)
+
+
+def functional_sdpa_pattern(q, k, v):
+    return F.scaled_dot_product_attention(q, k, v)
+
+
+def functional_sdpa_masked_pattern(q, k, v, mask):
+    return F.scaled_dot_product_attention(q, k, v, attn_mask=mask, dropout_p=0.0, is_causal=False)
+
+
+def functional_sdpa_masked_replacement(q, k, v, mask):
+    return zenith_masked_flash_attention(q, k, v, mask)
 
 
 def gelu_tanh_pattern(x):
@@ -150,7 +233,10 @@ def make_add_layernorm_pattern(hidden: int, eps: float) -> FXPattern:
 
 def get_attention_patterns() -> list:
     return [FXPattern("causal_sdpa_to_flash", causal_sdpa_pattern, zenith_causal_sdpa_replacement, priority=21),
-            FXPattern("sdpa_to_flash", sdpa_pattern, zenith_sdpa_replacement, priority=20)]
+            FXPattern("sdpa_to_flash", sdpa_pattern, zenith_sdpa_replacement, priority=20),
+            FXPattern("functional_sdpa_masked_to_flash", functional_sdpa_masked_pattern, functional_sdpa_masked_replacement,
+                      priority=19),
+            FXPattern("functional_sdpa_to_flash", functional_sdpa_pattern, zenith_sdpa_replacement, priority=18)]
 
 
 def get_activation_patterns() -> list:
