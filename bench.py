@@ -1,25 +1,32 @@
 #!/usr/bin/env python
-"""Benchmark of the W8A8 BERT-base encoder (batch 32 per GPU, seq 128) on N B200s of one node.
+"""Benchmark of the W8A8 BERT encoder on N B200s of one node.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config bert_base|bert_large]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
-A step is one forward pass of the encoder over one batch of 32 synthetic sequences per GPU
-(BASELINE.json configs[2]: 12 layers, hidden 768, 12 heads, FFN 3072, post-LN, tanh-GELU, W8A8 with
-per-channel weight scales and min-max activation scales from 16 seeded batches; token ids uniform
-over 30522 words, the last 0..32 positions of each row masked).  Ranks are independent replicas
-(weak scaling, global batch 32 * N); for N > 1 each step ends with the NCCL gather of the hidden
-states onto rank 0.  Rank 0 prints ONE JSON line.
+``--config bert_base`` (default, the headline): a step is one forward pass over one batch of 32 synthetic
+sequences of 128 tokens per GPU (BASELINE.json configs[2]: 12 layers, hidden 768, 12 heads, FFN 3072, post-LN,
+tanh-GELU, W8A8 with per-channel weight scales and min-max activation scales from 16 seeded batches; token ids
+uniform over 30522 words, the last 0..32 positions of each row masked).  Ranks are independent replicas (weak
+scaling, global batch 32 * N).  ``--config bert_large``: BASELINE.json configs[4], global batch 256 x 384 tokens
+split over the ranks (strong scaling).  For N > 1 every step ends with the gather of the hidden states onto rank
+0.  Rank 0 prints ONE JSON line.
 
-`value`      sequences/s with token ids already in HBM (CUDA-graph replay of the 61 launches).
+`value`      sequences/s with token ids already in HBM (CUDA-graph replay of the launch list).
 `e2e`        the same through the public host API (zenith_b200.serve.HostPipeline) with HOST buffers: every
              step copies pinned ids / lengths to the device and the fp16 hidden states back to pinned host
              memory inside the timed region; the copy back of step i overlaps the compute of step i + 1.
-`roofline`   the int8 tcgen05 GEMM family (4 shapes x 12 layers per step): average launch durations measured with
+`sustained`  seconds of back-to-back replays under the clock sampler: the power-capped rate, beside the burst
+             rate of the short timed region.
+`roofline`   the launches of a layer that carry its int8 GEMM work: average launch durations measured with
              CUDA events inside a graph of 12 launches per shape, as the step runs them.
-`cpu_baseline` the CPU restatement of the reference's quantized executor (fake-quant + fp32 BLAS
-             matmul), timed on this host's cores on a bounded sample.
-`--impl reference` times that CPU executor alone, on the same workload definition.
+`secondary`  the other configurations of BASELINE.json measured in the same run (fp16 encoder, attention
+             sweep, a BERT-large shard), kernel yardsticks (int8 8192^3 against the library GEMM, add+LayerNorm
+             against the copy bandwidth).
+`parity_check` one layer's FFN1 int8 output of the timed encoder against the CPU oracle, and replay == eager.
+`cpu_baseline` the CPU restatement of the reference's quantized executor (fake-quant + fp32 BLAS matmul) on a
+             bounded sample, plus the reference's two single-Linear CPU forms on BASELINE.json configs[0].
+`--impl reference` times that CPU executor alone, on the same workload definition (32 sequences per step).
 """
 from __future__ import annotations
 
@@ -43,6 +50,9 @@ MASTER_SEED = 1234
 CALIB_BATCHES = 16
 METRIC = "bert_base_int8_seq128_sequences_per_sec"
 WORKLOAD = "bert-base W8A8 encoder, batch 32 per GPU, seq 128 (BASELINE.json configs[2])"
+LARGE_GLOBAL_BATCH, LARGE_SEQ = 256, 384
+LARGE_METRIC = "bert_large_int8_seq384_sequences_per_sec"
+LARGE_WORKLOAD = "bert-large W8A8 encoder, global batch 256 split over the GPUs, seq 384 (BASELINE.json configs[4])"
 
 
 def make_batch(seed: int, vocab: int, batch: int = BATCH, seq: int = SEQ):
@@ -134,17 +144,18 @@ def blas_threads_all() -> int:
         return int(os.environ.get("OMP_NUM_THREADS", n))
 
 
-def cpu_executor(sample_seqs: int, steps: int, warmup: int) -> dict:
+def cpu_executor(sample_seqs: int, steps: int, warmup: int, large: bool = False) -> dict:
     threads = blas_threads_all()
     from oracle import encoder_ref as ER
     from zenith_b200.calibrate import activation_scales_from_ranges, quantize_weights
-    from zenith_b200.encoder import BERT_BASE, Int8Scales, init_params
+    from zenith_b200.encoder import BERT_BASE, BERT_LARGE, Int8Scales, init_params
 
-    cfg = BERT_BASE
+    cfg = BERT_LARGE if large else BERT_BASE
+    seq = LARGE_SEQ if large else SEQ
     params = init_params(cfg, MASTER_SEED)
-    cal = [make_batch(MASTER_SEED + 1 + i, cfg.vocab, batch=2) for i in range(2)]  # scales do not affect timing
+    cal = [make_batch(MASTER_SEED + 1 + i, cfg.vocab, batch=2, seq=seq) for i in range(2)]  # scales do not affect timing
     scales = ER.calibrate_on_oracle(cfg, params, cal, quantize_weights, activation_scales_from_ranges, Int8Scales)
-    ids, lens = make_batch(MASTER_SEED, cfg.vocab, batch=sample_seqs)
+    ids, lens = make_batch(MASTER_SEED, cfg.vocab, batch=sample_seqs, seq=seq)
     for _ in range(warmup):
         ER.encoder_fake_quant(cfg, params, scales, ids, lens)
     times = []
@@ -154,8 +165,50 @@ def cpu_executor(sample_seqs: int, steps: int, warmup: int) -> dict:
         times.append(time.perf_counter() - t0)
     total = sum(times)
     return {"seq_per_s": sample_seqs * steps / total, "ms_per_step": 1e3 * total / steps,
-            "cores": threads, "sample": f"{steps} passes of {sample_seqs} sequences x {SEQ} tokens "
+            "cores": threads, "sample": f"{steps} passes of {sample_seqs} sequences x {seq} tokens "
             f"(numpy fake-quant + fp32 BLAS matmul on {threads} BLAS threads of {os.cpu_count()} host cores)"}
+
+
+def cpu_single_linear_baselines() -> list:
+    """The reference's two other CPU forms of a quantized Linear, on BASELINE.json configs[0] (X [128, 768],
+    W [3072, 768]): the true-integer numpy product (benchmarks/int8_bench.py:42-45: int32 matmul, then dequant) and
+    the reference's own AVX2 fp32 GEMM (core/src/cpu_kernels.cpp:129-165, compiled as it stands into oracle/_ref) on
+    the dequantised operands.  Both are single-threaded by construction."""
+    from oracle import oracle as O
+
+    M, K, N = 128, 768, 3072
+    rng = np.random.default_rng(MASTER_SEED)
+    xq = rng.integers(-128, 128, (M, K), dtype=np.int8)
+    wq = rng.integers(-128, 128, (N, K), dtype=np.int8)
+    s_x, s_w = np.float32(0.03), np.float32(1e-3)
+
+    def median_ms(fn, reps=10, warm=3):
+        for _ in range(warm):
+            fn()
+        t = []
+        for _ in range(reps):
+            t0 = time.perf_counter()
+            fn()
+            t.append(time.perf_counter() - t0)
+        return 1e3 * statistics.median(t), 1e3 * min(t)
+
+    out = []
+    b32 = np.ascontiguousarray(wq.astype(np.int32).T)
+    med, best = median_ms(lambda: (xq.astype(np.int32) @ b32).astype(np.float32) * s_x * s_w, reps=3, warm=1)
+    out.append({"name": "true-integer numpy GEMM + dequant (int8_bench.py:42-45)", "workload": "configs[0]: 128 x 3072 x 768",
+                "ms": round(med, 3), "ms_min": round(best, 3), "gops": round(2.0 * M * N * K / med / 1e6, 2), "cores": 1,
+                "kind": "reference formula in numpy"})
+    if O.ref_lib() is not None:
+        xf = xq.astype(np.float32) * s_x
+        wt = np.ascontiguousarray((wq.astype(np.float32) * s_w).T)  # [K, N]
+        med, best = median_ms(lambda: O.ref_matmul_avx2(xf, wt))
+        out.append({"name": "reference AVX2 fp32 GEMM on dequantised operands (cpu_kernels.cpp:129-165)",
+                    "workload": "configs[0]: 128 x 3072 x 768", "ms": round(med, 3), "ms_min": round(best, 3),
+                    "gflops": round(2.0 * M * N * K / med / 1e6, 2), "cores": 1, "kind": "reference"})
+    else:
+        out.append({"name": "reference AVX2 fp32 GEMM", "ms": None, "kind": "reference",
+                    "why": "oracle/_ref was not built (the reference tree was not mounted when build() ran)"})
+    return out
 
 
 _RESULT_FD = None
@@ -180,17 +233,34 @@ def emit(line: dict) -> None:
         os.write(_RESULT_FD, data)
 
 
+def workload_of(args, world: int) -> dict:
+    """Metric, per-rank batch and names for the selected configuration."""
+    if args.config == "bert_large":
+        from zenith_b200.dist import shard_bounds
+
+        rank = int(os.environ.get("RANK", "0"))
+        _, local = shard_bounds(LARGE_GLOBAL_BATCH, world, rank)
+        return {"metric": LARGE_METRIC, "workload": LARGE_WORKLOAD, "seq": LARGE_SEQ, "local_batch": local,
+                "global_batch": LARGE_GLOBAL_BATCH, "scaling": "strong", "large": True}
+    return {"metric": METRIC, "workload": WORKLOAD, "seq": SEQ, "local_batch": BATCH, "global_batch": BATCH * world,
+            "scaling": "weak", "large": False}
+
+
 def run_reference_arm(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    sample = 4
-    r = cpu_executor(sample, max(1, args.steps), max(1, min(args.warmup, 2)))
+    wl = workload_of(args, 1)
+    # one step = the same batch a GPU gets in a step of the other arm (32 sequences; BERT-large: a 4-sequence sample
+    # of its 256, a pass over all of them takes minutes on host cores)
+    sample = BATCH if not wl["large"] else 4
+    r = cpu_executor(sample, max(1, args.steps), 1 if args.warmup > 0 else 0, large=wl["large"])
     line = {
-        "impl": "reference", "metric": METRIC, "value": r["seq_per_s"], "unit": "sequences/s", "n_gpus": args.gpus,
+        "impl": "reference", "metric": wl["metric"], "value": r["seq_per_s"], "unit": "sequences/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32 (fake-quantized int8 values)", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "step_sample": f"{sample} sequences per step"},
+        "scaling": wl["scaling"], "vs_baseline": None, "dtype": "f32 (fake-quantized int8 values)", "data": "synthetic",
+        "config": {"workload": wl["workload"], "global_batch": sample, "seq_len": wl["seq"],
+                   "step_sample": f"{sample} sequences per step", "warmup_run": 1 if args.warmup > 0 else 0},
         "cpu_baseline": {"value": r["seq_per_s"], "unit": "sequences/s", "cores": r["cores"], "kind": "port",
                          "sample": r["sample"]},
         "e2e": {"value": r["seq_per_s"], "unit": "sequences/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -202,24 +272,52 @@ def run_reference_arm(args) -> None:
 # ------------------------------------------------------------------------------------------------
 # GPU arm
 # ------------------------------------------------------------------------------------------------
+def _graph_of(torch, fn):
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        fn()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        fn()
+    return graph
+
+
+def _event_us(torch, fn, reps, flush=None):
+    us = []
+    for _ in range(reps):
+        if flush is not None:
+            flush()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        e.synchronize()
+        us.append(s.elapsed_time(e) * 1e3)
+    return statistics.median(us)
+
+
 def time_gemm_shapes(torch, ops, dev, flush) -> dict:
-    """The four int8 GEMM launches of one encoder layer with the epilogue each has in the encoder: QKV (-> fp16),
-    attention-out (+ residual + LayerNorm, cluster kernel), FFN1 (+ GELU + requant), FFN2 (+ residual +
-    LayerNorm), timed with CUDA events in two ways:
+    """The four launches of one encoder layer that carry its int8 GEMM work, with the epilogue each has in the
+    encoder: QKV projection fused with attention, attention-out (+ residual + LayerNorm, cluster kernel), FFN1
+    (+ GELU + requant), FFN2 (+ residual + LayerNorm), timed with CUDA events in two ways:
 
     * ``in_step``: as the step runs them - a CUDA graph of 12 back-to-back launches of the shape, one per layer,
       each with its own weight matrix, L2 flushed before every replay (so the weights come from HBM, as in the
       step); average launch duration = replay time / 12.  `roofline.achieved` uses these.
     * ``cold``: one launch alone, L2 flushed, launch latency included (the upper bound a profiler also sees).
+    The plain QKV GEMM (the projection alone, as a two-kernel encoder runs it) is timed as well, for reference.
     """
-    T, H, F, LAYERS = BATCH * SEQ, 768, 3072, 12
+    T, H, F, LAYERS, HEADS = BATCH * SEQ, 768, 3072, 12, 12
 
     def plain(N, K, **kw):
         x = torch.randint(-128, 128, (T, K), dtype=torch.int8, device=dev)
         ws_ = [torch.randint(-128, 128, (N, K), dtype=torch.int8, device=dev) for _ in range(LAYERS)]
         ws, b = torch.rand(N, device=dev) * 1e-3, torch.randn(N, device=dev)
         out = torch.empty((T, N), dtype=kw["out_dtype"], device=dev)
-        return lambda i: ops.linear_int8(x, ws_[i], 0.02, ws, b, out=out, **kw)
+        return lambda i: ops.linear_int8(x, ws_[i], 0.02, ws, b, out=out, constant_weights=True, **kw)
 
     def with_ln(K):
         x = torch.randint(-128, 128, (T, K), dtype=torch.int8, device=dev)
@@ -227,48 +325,148 @@ def time_gemm_shapes(torch, ops, dev, flush) -> dict:
         ws, b = torch.rand(H, device=dev) * 1e-3, torch.randn(H, device=dev)
         res = torch.randn(T, H, device=dev, dtype=torch.float16)
         g, be = torch.ones(H, device=dev, dtype=torch.float16), torch.zeros(H, device=dev, dtype=torch.float16)
-        return lambda i: ops.linear_int8_add_layernorm(x, ws_[i], 0.02, ws, b, res, g, be, 1e-12, out_scale=0.03)
+        return lambda i: ops.linear_int8_add_layernorm(x, ws_[i], 0.02, ws, b, res, g, be, 1e-12, out_scale=0.03,
+                                                       constant_weights=True)
 
-    shapes = [("qkv", 3 * H, H, plain(3 * H, H, out_dtype=torch.float16)),
-              ("attn_out_add_layernorm", H, H, with_ln(H)),
-              ("ffn1_gelu_requant", F, H, plain(F, H, act="gelu", out_dtype=torch.int8, out_scale=0.05)),
-              ("ffn2_add_layernorm", H, F, with_ln(F))]
+    def qkv_attention():
+        x = torch.randint(-128, 128, (T, H), dtype=torch.int8, device=dev)
+        ws_ = [torch.randint(-128, 128, (3 * H, H), dtype=torch.int8, device=dev) for _ in range(LAYERS)]
+        ws, b = torch.rand(3 * H, device=dev) * 1e-4, torch.randn(3 * H, device=dev) * 0.1
+        lens = torch.full((BATCH,), SEQ - 16, dtype=torch.int32, device=dev)  # the mean key length of the workload
+        return lambda i: ops.qkv_attention_int8(x, ws_[i], 0.02, ws, b, BATCH, SEQ, HEADS, kv_lens=lens, out_scale=0.02,
+                                                constant_weights=True)
 
-    def event_us(fn, reps):
-        us = []
-        for _ in range(reps):
-            flush()
-            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            s.record()
-            fn()
-            e.record()
-            e.synchronize()
-            us.append(s.elapsed_time(e) * 1e3)
-        return statistics.median(us)
-
-    per_shape, tot_ops, tot_us = {}, 0.0, 0.0
-    for name, N, K, fn in shapes:
+    # (name, GEMM N, GEMM K, launcher, counted in the family)
+    shapes = [("qkv_projection_attention", 3 * H, H, qkv_attention(), True),
+              ("attn_out_add_layernorm", H, H, with_ln(H), True),
+              ("ffn1_gelu_requant", F, H, plain(F, H, act="gelu", out_dtype=torch.int8, out_scale=0.05), True),
+              ("ffn2_add_layernorm", H, F, with_ln(F), True),
+              ("qkv_projection_alone", 3 * H, H, plain(3 * H, H, out_dtype=torch.float16), False)]
+    per_shape, tot_ops, tot_us, alg_bytes = {}, 0.0, 0.0, 0.0
+    for name, N, K, fn, counted in shapes:
         def all_layers():
             for i in range(LAYERS):
                 fn(i)
-        side = torch.cuda.Stream(device=dev)
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            all_layers()
-        torch.cuda.current_stream().wait_stream(side)
-        torch.cuda.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            all_layers()
+        graph = _graph_of(torch, all_layers)
         for _ in range(3):
             graph.replay()
-        in_step = event_us(graph.replay, 9) / LAYERS
-        cold = event_us(lambda: fn(0), 9)
+        in_step = _event_us(torch, graph.replay, 9, flush) / LAYERS
+        cold = _event_us(torch, lambda: fn(0), 9, flush)
         ops_ = 2.0 * T * N * K
         per_shape[name] = {"us": round(in_step, 2), "tops": round(ops_ / in_step / 1e6, 1), "cold_us": round(cold, 2)}
-        tot_ops += ops_
-        tot_us += in_step
-    return {"per_shape": per_shape, "ops_per_layer": tot_ops, "us_per_layer": tot_us}
+        if counted:
+            tot_ops += ops_
+            tot_us += in_step
+    # operand, residual and output bytes of the four launches, from the shapes: int8 operands M K + N K, per-column
+    # scale and bias 8 N, then what each launch writes (and, for the LayerNorm launches, the fp16 residual it reads)
+    alg_bytes += T * H + 3 * H * H + 8 * 3 * H + T * H * (2 + 1)                # projection + attention: ctx fp16 + int8
+    alg_bytes += T * H + H * H + 8 * H + T * H * (2 + 2 + 1)                    # attention-out: residual, y fp16, y int8
+    alg_bytes += T * H + F * H + 8 * F + T * F                                  # FFN1: int8 out
+    alg_bytes += T * F + H * F + 8 * H + T * H * (2 + 2 + 1)                    # FFN2
+    return {"per_shape": per_shape, "ops_per_layer": tot_ops, "us_per_layer": tot_us, "algorithmic_bytes": alg_bytes}
+
+
+def secondary_metrics(torch, ops, dev, flush, peaks, cfg_base, params_base) -> dict:
+    """The other BASELINE.json configurations and two kernel yardsticks, measured in this run (CUDA events, L2
+    flushed between launches, medians)."""
+    from zenith_b200.encoder import BERT_LARGE, Fp16Encoder, Int8Encoder, Int8Scales, init_params
+
+    out = {}
+    # configs[1]: the fp16 encoder, batch 32 x 128
+    enc = Fp16Encoder(cfg_base, params_base, dev)
+    ids, lens = make_batch(MASTER_SEED + 1000, cfg_base.vocab)
+    enc.capture(BATCH, SEQ)
+    enc.set_inputs(torch.from_numpy(ids).to(dev), torch.from_numpy(lens).to(dev))
+    for _ in range(3):
+        enc.replay()
+    us = _event_us(torch, enc.replay, 15, flush)
+    out["bert_base_fp16_seq128"] = {"sequences_per_s": round(BATCH / us * 1e6, 1), "ms_per_step": round(us / 1e3, 4),
+                                    "launches": enc.launches_per_forward, "workload": "BASELINE.json configs[1]"}
+    del enc
+    # configs[3]: attention forward sweep, B = 8, H = 16
+    fp16_peak = peaks["bf16_tflops"]
+    sweep = {}
+    for D in (64, 128):
+        for S in (512, 2048, 8192):
+            q, k, v = (torch.randn(8, 16, S, D, device=dev, dtype=torch.float16) for _ in range(3))
+            for causal in (False, True):
+                fn = lambda: ops.flash_attention(q, k, v, causal=causal)
+                for _ in range(2):
+                    fn()
+                us = _event_us(torch, fn, 5, flush)
+                tf = 4.0 * 8 * 16 * S * S * D * (0.5 if causal else 1.0) / us / 1e6
+                sweep[f"d{D}_s{S}_{'causal' if causal else 'full'}"] = {"tflops": round(tf, 1), "frac_of_fp16_peak": round(tf / fp16_peak, 3)}
+            del q, k, v
+    out["attention_fwd_b8_h16"] = {"cases": sweep, "peak_tflops": fp16_peak,
+                                   "peak_source": f"{peaks['source']} bf16 GEMM burst", "workload": "BASELINE.json configs[3]"}
+    # int8 GEMM yardstick: own kernel against the library GEMM on the same device in the same run
+    n = 8192
+    a = torch.randint(-128, 128, (n, n), dtype=torch.int8, device=dev)
+    b = torch.randint(-128, 128, (n, n), dtype=torch.int8, device=dev)
+    o16 = torch.empty((n, n), dtype=torch.float16, device=dev)
+    ws = torch.rand(n, device=dev) * 1e-4
+    own = lambda: ops.linear_int8(a, b, 0.02, ws, None, out=o16, out_dtype=torch.float16)
+    lib = lambda: torch._int_mm(a, b.t())
+    for f in (own, lib):
+        for _ in range(2):
+            f()
+    us_own, us_lib = _event_us(torch, own, 7, flush), _event_us(torch, lib, 7, flush)
+    out["int8_gemm_8192"] = {"own_tops": round(2.0 * n**3 / us_own / 1e6, 1), "library_int_mm_tops": round(2.0 * n**3 / us_lib / 1e6, 1),
+                             "note": "own: fp16 output with per-column scales (CTA-pair kernel); library: torch._int_mm, int32 output"}
+    del a, b, o16
+    # add + LayerNorm (fp16 in / out + int8 copy) against the measured copy bandwidth
+    rows, hidden = 98304, 1024
+    x = torch.randn(rows, hidden, device=dev, dtype=torch.float16)
+    r = torch.randn_like(x)
+    g, be = torch.ones(hidden, device=dev, dtype=torch.float16), torch.zeros(hidden, device=dev, dtype=torch.float16)
+    fn = lambda: ops.add_layernorm(x, r, g, be, 1e-12, out_scale=0.03)
+    for _ in range(2):
+        fn()
+    us = _event_us(torch, fn, 7, flush)
+    gbs = rows * hidden * 7 / us / 1e3
+    out["add_layernorm_98304x1024"] = {"gb_per_s": round(gbs, 1), "frac_of_hbm": round(gbs / peaks["hbm_gbs"], 3),
+                                       "hbm_gbs": peaks["hbm_gbs"], "bytes_per_row": hidden * 7}
+    del x, r
+    # configs[4]: one GPU's shard of the BERT-large run at 8 GPUs (32 sequences x 384 tokens)
+    cfg = BERT_LARGE
+    params = init_params(cfg, MASTER_SEED)
+    from zenith_b200.calibrate import calibrate
+    cal = [make_batch(MASTER_SEED + 1 + i, cfg.vocab, batch=8, seq=LARGE_SEQ) for i in range(2)]
+    scales = calibrate(cfg, params, [(torch.from_numpy(i).to(dev), torch.from_numpy(l).to(dev)) for i, l in cal], dev)
+    enc = Int8Encoder(cfg, params, scales, dev)
+    ids, lens = make_batch(MASTER_SEED + 2000, cfg.vocab, batch=32, seq=LARGE_SEQ)
+    enc.capture(32, LARGE_SEQ)
+    enc.set_inputs(torch.from_numpy(ids).to(dev), torch.from_numpy(lens).to(dev))
+    for _ in range(3):
+        enc.replay()
+    us = _event_us(torch, enc.replay, 9, flush)
+    out["bert_large_int8_seq384_shard32"] = {"ms_per_step": round(us / 1e3, 3), "sequences_per_s": round(32 / us * 1e6, 1),
+                                             "launches": enc.launches_per_forward,
+                                             "workload": "BASELINE.json configs[4], the 32-sequence shard one of 8 GPUs holds"}
+    return out
+
+
+def parity_check(torch, enc, scales, params, ids_np, lens_np, dev) -> dict:
+    """The encoder that was timed, checked: the CUDA-graph replay equals the eager launch list bit for bit, and the
+    FFN1 int8 output of one layer (GELU + requantisation epilogue) equals the CPU oracle on sampled rows, computed
+    from the int8 input the device itself gave that GEMM."""
+    from oracle import oracle as O
+
+    enc.set_inputs(torch.from_numpy(ids_np).to(dev), torch.from_numpy(lens_np).to(dev))
+    replayed = enc.replay().clone()
+    layer = len(params["layers"]) // 2
+    rows = np.arange(5, ids_np.size, max(1, ids_np.size // 96))
+    ok, checked = True, 0
+    for li, buf in enc.forward_layerwise(torch.from_numpy(ids_np).to(dev), torch.from_numpy(lens_np).to(dev)):
+        if li == layer:
+            a, wq, lp = scales.act[li], scales.weights[li], params["layers"][li]
+            want = O.linear_int8(buf["h1q"].cpu().numpy()[rows], wq["w1"][0], a["h1"], wq["w1"][1], lp["b1"], "gelu", "s8", a["gelu"])
+            got = buf["gq"].cpu().numpy()[rows]
+            ok = bool(np.array_equal(got, want))
+            checked = int(got.size)
+    same = bool(torch.equal(enc.out, replayed))
+    return {"status": "ok" if (ok and same) else "MISMATCH", "ffn1_int8_elements_checked": checked, "layer": layer,
+            "replay_equals_eager": same}
 
 
 def run_ours(args) -> None:
@@ -278,7 +476,7 @@ def run_ours(args) -> None:
     from zenith_b200 import _capi, ops
     from zenith_b200.calibrate import calibrate
     from zenith_b200.dist import OutputGatherer, init_from_env
-    from zenith_b200.encoder import BERT_BASE, Int8Encoder, init_params
+    from zenith_b200.encoder import BERT_BASE, BERT_LARGE, Int8Encoder, init_params
     from zenith_b200.serve import HostPipeline
 
     if not torch.cuda.is_available():
@@ -287,19 +485,22 @@ def run_ours(args) -> None:
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     _capi.lib()
-    cfg = BERT_BASE
+    wl = workload_of(args, world)
+    cfg = BERT_LARGE if wl["large"] else BERT_BASE
+    B, S = wl["local_batch"], wl["seq"]
     K, W = args.steps, max(3, args.warmup)
 
     params = init_params(cfg, MASTER_SEED)
-    calib = [make_batch(MASTER_SEED + 1 + i, cfg.vocab) for i in range(CALIB_BATCHES)]
+    n_cal, cal_batch = (CALIB_BATCHES, BATCH) if not wl["large"] else (CALIB_BATCHES, 8)
+    calib = [make_batch(MASTER_SEED + 1 + i, cfg.vocab, batch=cal_batch, seq=S) for i in range(n_cal)]
     scales = calibrate(cfg, params, [(torch.from_numpy(i).to(dev), torch.from_numpy(l).to(dev)) for i, l in calib], dev)
     enc = Int8Encoder(cfg, params, scales, dev, micro_batches=args.micro_batches)
-    ids_np, lens_np = make_batch(MASTER_SEED + 1000 + rank, cfg.vocab)
+    ids_np, lens_np = make_batch(MASTER_SEED + 1000 + rank, cfg.vocab, batch=B, seq=S)
     ids_h = torch.from_numpy(ids_np).pin_memory()
     lens_h = torch.from_numpy(lens_np).pin_memory()
-    enc.capture(BATCH, SEQ)
+    enc.capture(B, S)
     enc.set_inputs(ids_h.to(dev), lens_h.to(dev))
-    gatherer = OutputGatherer(BATCH * world, SEQ, cfg.hidden, torch.float16, dev, root=0) if world > 1 else None
+    gatherer = OutputGatherer(wl["global_batch"], S, cfg.hidden, torch.float16, dev, root=0) if world > 1 else None
 
     l2_flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # 2 x the 126 MB L2
 
@@ -320,8 +521,9 @@ def run_ours(args) -> None:
     # End to end through the public host API (zenith_b200.serve.HostPipeline): every step copies its ids /
     # lengths from pinned host memory and its hidden states back to pinned host memory; the device->host
     # copy of step i runs on a copy stream while step i + 1 computes, and the host waits for step i - 1's
-    # result before it queues step i + 1 (the loop a server would run).
-    pipe = HostPipeline(enc, BATCH, SEQ, gatherer=gatherer)
+    # result before it queues step i + 1 (the loop a server would run).  With several GPUs every rank delivers
+    # its own shard to host memory over its own PCIe link (host memory is where the shards meet).
+    pipe = HostPipeline(enc, B, S)
 
     def timed_e2e(steps):
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -334,7 +536,7 @@ def run_ours(args) -> None:
                 pipe.result(prev)
             prev = t
         pipe.result(prev)
-        pipe.drain()  # the last gathers are ordered before the end event
+        pipe.drain()
         e.record()
         barrier()
         t = torch.tensor([s.elapsed_time(e)], dtype=torch.float64, device=dev)
@@ -358,6 +560,28 @@ def run_ours(args) -> None:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    def sustained(seconds):
+        """Back-to-back steps for `seconds`: no L2 flush (a step's working set exceeds the L2), one event pair."""
+        sampler_ = ClockSampler(local_rank) if rank == 0 else None
+        n_guess = max(10, int(seconds / max(1e-4, total_ms / K / 1e3)))
+        barrier()
+        if sampler_:
+            sampler_.start()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(n_guess):
+            step_device()
+        e.record()
+        barrier()
+        clk = sampler_.stop() if sampler_ else None
+        t = torch.tensor([s.elapsed_time(e)], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        return {"value": wl["global_batch"] * n_guess / (ms / 1e3) if wl["large"] else world * B * n_guess / (ms / 1e3),
+                "unit": "sequences/s", "seconds": round(ms / 1e3, 2), "steps": n_guess, "ms_per_step": ms / n_guess,
+                "clocks": clk, "how": "back-to-back steps, one event pair, no L2 flush between steps"}
+
     for _ in range(W):
         step_device()
     sampler = ClockSampler(local_rank) if rank == 0 else None
@@ -371,6 +595,7 @@ def run_ours(args) -> None:
     e2e_ms = timed_e2e(K)
     e2e_launches = enc.launches_per_forward + 1  # + the device copy that parks the result for the copy stream
     clocks = sampler.stop() if sampler else None
+    sus = sustained(args.sustain_seconds) if args.sustain_seconds > 0 else None
     status = _capi.device_status()
 
     if rank != 0:
@@ -378,50 +603,67 @@ def run_ours(args) -> None:
             dist.destroy_process_group()
         return
 
-    value = world * BATCH * K / (total_ms / 1e3)
-    e2e_value = world * BATCH * K / (e2e_ms / 1e3)
+    seqs_per_step = wl["global_batch"] if wl["large"] else world * B
+    value = seqs_per_step * K / (total_ms / 1e3)
+    e2e_value = seqs_per_step * K / (e2e_ms / 1e3)
     peaks = measured_peaks()
     line = {
-        "metric": METRIC, "value": value, "unit": "sequences/s", "n_gpus": world, "steps": K, "warmup": W,
-        "ms_per_step": total_ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "metric": wl["metric"], "value": value, "unit": "sequences/s", "n_gpus": world, "steps": K, "warmup": W,
+        "ms_per_step": total_ms / K, "higher_is_better": True, "scaling": wl["scaling"], "vs_baseline": None,
         "dtype": "s8 operands, s32 accumulators (fp16 LayerNorm / softmax / residual)", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "global_batch": BATCH * world, "seq_len": SEQ, "parallelism": f"replicas x{world}" + (", NCCL gather of the hidden states onto rank 0 inside every step" if world > 1 else ""),
-                   "l2": "256 MB buffer written between timed steps", "launch": f"CUDA-graph replay of {enc.launches_per_forward} kernels in {args.micro_batches} concurrent micro-batch(es)"},
+        "config": {"workload": wl["workload"], "global_batch": seqs_per_step, "seq_len": S,
+                   "parallelism": f"replicas x{world}" + (", gather of the hidden states onto rank 0 (NCCL) inside every step" if world > 1 else ""),
+                   "l2": "256 MB buffer written between timed steps",
+                   "launch": f"CUDA-graph replay of {enc.launches_per_forward} kernels in {args.micro_batches} concurrent micro-batch(es)"},
         "e2e": {"value": e2e_value, "unit": "sequences/s", "ms_per_step": e2e_ms / K,
                 "h2d_bytes_per_step": int(ids_h.numel() * ids_h.element_size() + lens_h.numel() * lens_h.element_size()),
                 "d2h_bytes_per_step": int(pipe.host_out[0].numel() * 2),
                 "how": "zenith_b200.serve.HostPipeline: one event pair around all steps; per step pinned-host ids -> device, "
                        "graph replay, hidden states -> pinned host on a copy stream that overlaps the next step's compute; "
-                       "no L2 flush in this loop (a step's working set, 85 MB of weights + 60 MB of activations, exceeds "
-                       "the 126 MB L2; flushing changed the device-resident step time by 0.3 %)",
+                       "no L2 flush in this loop (a step's working set of weights + activations exceeds the 126 MB L2); "
+                       "with several GPUs every rank delivers its own shard to host memory (bytes are per rank)",
                 "launches_per_step": e2e_launches},
         "gpu_launches": int(launches),
         "clocks": clocks,
         "device_status": status,
     }
-    if world == 1:
+    if sus is not None:
+        line["sustained"] = sus
+    if world == 1 and not wl["large"]:
         g = time_gemm_shapes(torch, ops, dev, flush)
         int8_peak = 2.0 * peaks["bf16_tflops"]
         achieved = g["ops_per_layer"] / g["us_per_layer"] / 1e6
         line["roofline"] = {
-            "kernel": "int8 tcgen05 GEMM family of one layer: gemm_tc_kernel (QKV, FFN1+GELU+requant) and "
-                      "gemm_i8_ln_kernel (attention-out / FFN2 + residual + LayerNorm)",
+            "kernel": "the launches of one layer that carry its int8 GEMM work: qkv_attn_kernel (QKV projection fused with "
+                      "attention; only the projection's operations are counted), gemm_i8_ln_kernel (attention-out / FFN2 + "
+                      "residual + LayerNorm) and gemm_tc_kernel (FFN1 + GELU + requant)",
             "bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TOP/s", "frac": achieved / int8_peak,
             "peak_source": f"2 x {peaks['source']} bf16 GEMM burst ({peaks['bf16_tflops']} TFLOP/s): int8 issues at "
                            "twice the bf16 rate; nominal dense int8 is 4500 TOP/s",
             "frac_of_nominal": achieved / 4500.0,
-            # DRAM bytes of the same four launches from profiles/gemm_i8_bert_base_layer_shapes.md (ncu): reads
-            # only and equal to the operand (+ residual) bytes; the outputs are still in L2 when each kernel ends
-            "traffic": 42.0e6, "traffic_unit": "bytes per layer (4 launches)",
-            "algorithmic_bytes": 92.1e6, "per_shape": g["per_shape"],
-            "gemm_share_of_step": 12.0 * g["us_per_layer"] / (total_ms / K * 1e3),
+            "traffic": None,
+            "traffic_note": "DRAM bytes per launch come from profiler captures, which cannot run inside this program: see the "
+                            "committed summaries of the GEMM launches (reads only, equal to the operand + residual bytes; "
+                            "outputs are still in L2 when a kernel ends)",
+            "algorithmic_bytes": g["algorithmic_bytes"], "algorithmic_bytes_unit": "bytes per layer (4 launches), from the shapes",
+            "per_shape": g["per_shape"],
+            "gemm_share_of_step": len(params["layers"]) * g["us_per_layer"] / (total_ms / K * 1e3),
             "duration": "average launch duration inside a CUDA graph of 12 back-to-back launches of the shape (one per "
                         "layer, 12 different weight matrices, L2 flushed before every replay), CUDA events; cold_us: one "
                         "launch alone after an L2 flush, launch latency included"}
         try:
+            line["parity_check"] = parity_check(torch, enc, scales, params, ids_np, lens_np, dev)
+        except Exception as exc:
+            line["parity_check"] = {"status": f"failed to run: {exc}"}
+        if not args.no_secondary:
+            try:
+                line["secondary"] = secondary_metrics(torch, ops, dev, flush, peaks, cfg, params)
+            except Exception as exc:  # a secondary measurement must never take the headline down with it
+                line["secondary"] = {"error": str(exc)}
+        try:
             r = cpu_executor(8, 3, 1)
             line["cpu_baseline"] = {"value": r["seq_per_s"], "unit": "sequences/s", "cores": r["cores"], "kind": "port",
-                                    "sample": r["sample"]}
+                                    "sample": r["sample"], "others": cpu_single_linear_baselines()}
         except Exception as exc:  # the CPU leg must never take the GPU numbers down with it
             line["cpu_baseline"] = {"value": None, "unit": "sequences/s", "cores": os.cpu_count(), "kind": "port",
                                     "sample": f"failed: {exc}"}
@@ -437,8 +679,12 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--config", choices=["bert_base", "bert_large"], default="bert_base",
+                    help="bert_base: BASELINE.json configs[2] (the headline); bert_large: configs[4], global batch 256 x 384")
     ap.add_argument("--micro-batches", type=int, default=1,
                     help="cut each GPU's batch into this many concurrently running micro-batches")
+    ap.add_argument("--sustain-seconds", type=float, default=3.0, help="length of the sustained leg (0 = skip it)")
+    ap.add_argument("--no-secondary", action="store_true", help="skip the secondary measurements (other configurations)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)

@@ -148,11 +148,16 @@ static int run_gemm(const void* A, int64_t lda, const void* B, int64_t ldb, Gemm
   else return launch_gemm<KIND, BN, STAGES, B_MN>(ta, tb, tc, p, stream);
 }
 
-// Whether a GEMM of this shape runs on CTA pairs.  ZEN_GEMM_PAIR / ZEN_GEMM_NO_PAIR force the choice.
-static bool use_pair(int M, unsigned flags) {
+// Whether a GEMM of this shape runs on CTA pairs.  ZEN_GEMM_PAIR / ZEN_GEMM_NO_PAIR force the choice.  A pair
+// moves a third fewer operand bytes per operation but starts and ends more slowly (cluster scheduling, two
+// cluster-wide rendezvous), and it does nothing for the epilogue: it pays when the main loop dominates, i.e. for
+// large products, and for the GELU + requantisation epilogue only with a deep K (measured on 11 shapes: wins of
+// 8 - 17 % above the thresholds, losses of 3 - 9 % below them).
+static bool use_pair(int M, int N, int K, bool heavy_epilogue, unsigned flags) {
   if (flags & ZEN_GEMM_NO_PAIR) return false;
   if (flags & ZEN_GEMM_PAIR) return true;
-  return false;
+  const double work = double(M) * double(N) * double(K);
+  return M >= 1024 && work >= 34359738368.0 /* 2^35 */ && (!heavy_epilogue || K >= 4096);
 }
 
 // Pair tile width: fewest rounds of the resident pairs, wider tiles preferred on a tie (less traffic per operation).
@@ -275,7 +280,7 @@ int zen_linear_i8_ex(const int8_t* xq, int64_t ldx, const int8_t* wq, int64_t ld
   }
   static const int allowed[] = {64, 128, 192, 256};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (use_pair(M, flags)) {
+  if (use_pair(M, N, K, out_dtype == ZEN_DT_S8 && act == ZEN_ACT_GELU, flags)) {
     switch (pick_bn_pair(M, N, flags)) {
       case 128: return run_gemm<KIND_I8, 128, 6, false, true>(xq, ldx, wq, ldw, p, s);
       case 192: return run_gemm<KIND_I8, 192, 5, false, true>(xq, ldx, wq, ldw, p, s);
@@ -308,7 +313,7 @@ int zen_linear_f16_ex(const void* x, int64_t ldx, const void* w, int64_t ldw, in
   p.early_b = (flags & ZEN_GEMM_CONST_WEIGHTS) ? 1 : 0;
   static const int allowed[] = {64, 128, 192, 256};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (use_pair(M, flags)) {
+  if (use_pair(M, N, 2 * K /* fp16 operands: twice the bytes per element */, false, flags)) {
     switch (pick_bn_pair(M, N, flags)) {
       case 128: return run_gemm<KIND_F16, 128, 6, false, true>(x, ldx, w, ldw, p, s);
       case 192: return run_gemm<KIND_F16, 192, 5, false, true>(x, ldx, w, ldw, p, s);
