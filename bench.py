@@ -475,7 +475,7 @@ def run_ours(args) -> None:
 
     from zenith_b200 import _capi, ops
     from zenith_b200.calibrate import calibrate
-    from zenith_b200.dist import OutputGatherer, init_from_env
+    from zenith_b200.dist import OutputGatherer, PeerGatherer, init_from_env
     from zenith_b200.encoder import BERT_BASE, BERT_LARGE, Int8Encoder, init_params
     from zenith_b200.serve import HostPipeline
 
@@ -500,7 +500,16 @@ def run_ours(args) -> None:
     lens_h = torch.from_numpy(lens_np).pin_memory()
     enc.capture(B, S)
     enc.set_inputs(ids_h.to(dev), lens_h.to(dev))
-    gatherer = OutputGatherer(wl["global_batch"], S, cfg.hidden, torch.float16, dev, root=0) if world > 1 else None
+    # The gather of the hidden states onto rank 0, one per step.  "peer" (default): every rank pushes its shard into
+    # rank 0's buffer with its copy engine over NVLink (zenith_b200.dist.PeerGatherer), the push of step i running
+    # under the kernels of step i + 1; "nccl": an NCCL gather in the compute stream after every pass.
+    gatherer = peer = None
+    if world > 1 and args.gather == "nccl":
+        gatherer = OutputGatherer(wl["global_batch"], S, cfg.hidden, torch.float16, dev, root=0)
+    elif world > 1:
+        peer = PeerGatherer(wl["global_batch"], S, cfg.hidden, torch.float16, dev, root=0, depth=3)
+        parked = [torch.empty_like(enc.out) for _ in range(peer.depth)]
+    ticket = [0]
 
     l2_flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # 2 x the 126 MB L2
 
@@ -517,6 +526,29 @@ def run_ours(args) -> None:
         enc.replay()
         if gatherer is not None:
             gatherer.gather(enc.out)
+        elif peer is not None:
+            t = ticket[0]
+            ticket[0] += 1
+            buf = parked[t % peer.depth]
+            buf.copy_(enc.out, non_blocking=True)  # the next pass overwrites the encoder's output buffer at once
+            peer.push(buf, t)
+            if t >= 1 and peer.pushed(t - 1) is not None:
+                # the previous step's push is part of this step's timed region: it must have finished by now
+                torch.cuda.current_stream().wait_event(peer.pushed(t - 1))
+            lag = peer.depth - 1
+            if rank == 0 and t >= lag:
+                peer.wait(t - lag)  # host-side: every shard of that ticket has landed in rank 0's buffer
+                peer.release(t - lag)
+
+    def finish_gathers():
+        """Rank 0 collects the tickets still in flight; every rank's queued copies complete."""
+        if peer is None:
+            return
+        if rank == 0:
+            for t in range(max(0, ticket[0] - (peer.depth - 1)), ticket[0]):
+                peer.wait(t)
+                peer.release(t)
+        peer.drain()
 
     # End to end through the public host API (zenith_b200.serve.HostPipeline): every step copies its ids /
     # lengths from pinned host memory and its hidden states back to pinned host memory; the device->host
@@ -552,7 +584,10 @@ def run_ours(args) -> None:
             flush()
             starts[i].record()
             step_fn()
+            if i == steps - 1 and peer is not None and peer.pushed(ticket[0] - 1) is not None:
+                torch.cuda.current_stream().wait_event(peer.pushed(ticket[0] - 1))  # the last push ends inside the region
             ends[i].record()
+        finish_gathers()
         barrier()
         ms = sum(s.elapsed_time(e) for s, e in zip(starts, ends))
         t = torch.tensor([ms], dtype=torch.float64, device=dev)
@@ -571,7 +606,10 @@ def run_ours(args) -> None:
         s.record()
         for _ in range(n_guess):
             step_device()
+        if peer is not None and peer.pushed(ticket[0] - 1) is not None:
+            torch.cuda.current_stream().wait_event(peer.pushed(ticket[0] - 1))
         e.record()
+        finish_gathers()
         barrier()
         clk = sampler_.stop() if sampler_ else None
         t = torch.tensor([s.elapsed_time(e)], dtype=torch.float64, device=dev)
@@ -584,6 +622,7 @@ def run_ours(args) -> None:
 
     for _ in range(W):
         step_device()
+    finish_gathers()
     sampler = ClockSampler(local_rank) if rank == 0 else None
     if sampler:
         sampler.start()
@@ -596,6 +635,21 @@ def run_ours(args) -> None:
     e2e_launches = enc.launches_per_forward + 1  # + the device copy that parks the result for the copy stream
     clocks = sampler.stop() if sampler else None
     sus = sustained(args.sustain_seconds) if args.sustain_seconds > 0 else None
+    gather_check = None
+    if peer is not None:
+        # what the pushes delivered against an NCCL all_gather of the same tensors
+        t = ticket[0]
+        step_device()
+        finish_gathers()
+        barrier()
+        ref = torch.empty((wl["global_batch"] * S, cfg.hidden), dtype=torch.float16, device=dev)
+        if len({c for _, c in peer.bounds}) == 1:
+            dist.all_gather_into_tensor(ref, enc.out.contiguous())
+            if rank == 0:
+                gather_check = "ok" if torch.equal(peer.data[t % peer.depth], ref) else "MISMATCH"
+        else:
+            gather_check = "not run (uneven shards)"
+        barrier()
     status = _capi.device_status()
 
     if rank != 0:
@@ -612,7 +666,10 @@ def run_ours(args) -> None:
         "ms_per_step": total_ms / K, "higher_is_better": True, "scaling": wl["scaling"], "vs_baseline": None,
         "dtype": "s8 operands, s32 accumulators (fp16 LayerNorm / softmax / residual)", "data": "synthetic",
         "config": {"workload": wl["workload"], "global_batch": seqs_per_step, "seq_len": S,
-                   "parallelism": f"replicas x{world}" + (", gather of the hidden states onto rank 0 (NCCL) inside every step" if world > 1 else ""),
+                   "parallelism": f"replicas x{world}" + ("" if world == 1 else
+                                                             ", NCCL gather of the hidden states onto rank 0 inside every step" if peer is None else
+                                                             ", hidden states pushed onto rank 0 by the copy engines over NVLink every step "
+                                                             "(peer-to-peer copies, the push of step i under the kernels of step i + 1)"),
                    "l2": "256 MB buffer written between timed steps",
                    "launch": f"CUDA-graph replay of {enc.launches_per_forward} kernels in {args.micro_batches} concurrent micro-batch(es)"},
         "e2e": {"value": e2e_value, "unit": "sequences/s", "ms_per_step": e2e_ms / K,
@@ -629,6 +686,8 @@ def run_ours(args) -> None:
     }
     if sus is not None:
         line["sustained"] = sus
+    if gather_check is not None:
+        line["gather_check"] = gather_check
     if world == 1 and not wl["large"]:
         g = time_gemm_shapes(torch, ops, dev, flush)
         int8_peak = 2.0 * peaks["bf16_tflops"]
@@ -683,6 +742,8 @@ def main() -> None:
                     help="bert_base: BASELINE.json configs[2] (the headline); bert_large: configs[4], global batch 256 x 384")
     ap.add_argument("--micro-batches", type=int, default=1,
                     help="cut each GPU's batch into this many concurrently running micro-batches")
+    ap.add_argument("--gather", choices=["peer", "nccl"], default="peer",
+                    help="N > 1: how the hidden states reach rank 0 (copy-engine pushes, or an NCCL gather in the compute stream)")
     ap.add_argument("--sustain-seconds", type=float, default=3.0, help="length of the sustained leg (0 = skip it)")
     ap.add_argument("--no-secondary", action="store_true", help="skip the secondary measurements (other configurations)")
     args = ap.parse_args()

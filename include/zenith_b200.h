@@ -57,6 +57,13 @@ const char* zen_status_string(int status);
 int zen_device_status_read(int* status_host);
 int zen_device_status_clear(void);
 
+/* Stream-ordered copy by a copy engine (cudaMemcpyAsync, kind inferred from the pointers): device memory of this or
+ * of a peer GPU, a CUDA IPC mapping of another process's buffer, or pinned host memory, in either direction.  No
+ * kernel runs, so the copy never takes an SM from the persistent GEMM kernels it overlaps; the multi-GPU gather of
+ * the encoder outputs is built on it.  The reference has no multi-GPU data path
+ * (benchmarks/mlperf_suite.py:750-850 runs independent replicas). */
+int zen_memcpy_async(void* dst, const void* src, size_t bytes, void* stream);
+
 /* Self-test of the wait limit: one small CTA waits on a barrier that nothing signals, in a build of the wait
  * loop whose limit is 1 ms.  The wait gives up by itself, the kernel returns normally and leaves
  * ZEN_ERR_TIMEOUT in the device status word (read it with zen_device_status_read, reset it with

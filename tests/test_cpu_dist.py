@@ -78,3 +78,58 @@ def test_bad_shard_is_refused_on_the_host():
         out = m.dict()
         mp.spawn(_worker, args=(2, _free_port(), 8, 1, out), nprocs=2, join=True)
         assert out[1] == "refused"
+
+
+def _peer_worker(rank, world, port, gb, silent_rank, out):
+    """The copy-engine gather's protocol on CPU ranks (shared-memory file instead of a CUDA IPC mapping)."""
+    from zenith_b200.dist import PeerGatherer
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        seq, hidden, depth, steps = 4, 8, 2, 7
+        pg = PeerGatherer(gb, seq, hidden, torch.float32, "cpu", root=0, depth=depth, timeout_s=2.0 if silent_rank is not None else 20.0)
+        start, count = shard_bounds(gb, world, rank)
+        base = torch.arange(start * seq, (start + count) * seq, dtype=torch.float32)[:, None] + torch.zeros(hidden)[None, :]
+        want = torch.arange(gb * seq, dtype=torch.float32)[:, None] + torch.zeros(hidden)[None, :]
+        ok = True
+        if silent_rank is None:
+            # more tickets than slots: the pushers are held back until the root has released the slot they need
+            for t in range(steps):
+                pg.push(base + 100 * t, t)
+                if rank == 0:
+                    full = pg.wait(t)
+                    ok = ok and bool(torch.equal(full, want + 100 * t))
+                    pg.release(t)
+            out[rank] = ok
+        else:
+            # one rank never pushes: the root's wait runs out on the host and raises instead of hanging
+            if rank != silent_rank:
+                pg.push(base, 0)
+            if rank == 0:
+                try:
+                    pg.wait(0)
+                    out[rank] = "returned"
+                except RuntimeError as e:
+                    out[rank] = "timed out" if "timed out" in str(e) else str(e)
+            else:
+                out[rank] = "done"
+        dist.barrier()
+        pg.close()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,gb", [(2, 8), (3, 7)])
+def test_peer_gather_protocol(world, gb):
+    with mp.Manager() as m:
+        out = m.dict()
+        mp.spawn(_peer_worker, args=(world, _free_port(), gb, None, out), nprocs=world, join=True)
+        assert dict(out) == {r: True for r in range(world)}
+
+
+def test_peer_gather_reports_a_rank_that_never_pushes():
+    with mp.Manager() as m:
+        out = m.dict()
+        mp.spawn(_peer_worker, args=(2, _free_port(), 8, 1, out), nprocs=2, join=True)
+        assert out[0] == "timed out" and out[1] == "done"

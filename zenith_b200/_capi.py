@@ -30,6 +30,7 @@ SIGNATURES = {
     "zen_device_status_read": [C.POINTER(C.c_int)],
     "zen_device_status_clear": [],
     "zen_selftest_wait_limit": [_p, _p],
+    "zen_memcpy_async": [_p, _p, C.c_size_t, _p],
     "zen_linear_i8": [_p, _i64, _p, _i64, _i, _i, _i, _f, _p, _p, _i, _i, _f, _i, _p, _i64, _p],
     "zen_linear_i8_prefetch": [_p, _i64, _p, _i64, _i, _i, _i, _f, _p, _p, _i, _i, _f, _i, _p, _i64, _p, C.c_size_t, _p,
                                C.c_size_t, _p],

@@ -35,3 +35,15 @@ extern "C" int zen_device_status_read(int* status_host) {
 }
 
 extern "C" int zen_device_status_clear(void) { return fold_status(nullptr, 1); }
+
+// Copy-engine copy between any two ranges the calling process can address: device memory of the current or of a
+// peer GPU (a CUDA IPC mapping included) and pinned host memory.  Stream-ordered, no kernel is launched.
+extern "C" int zen_memcpy_async(void* dst, const void* src, size_t bytes, void* stream) {
+  if (bytes == 0) return ZEN_OK;
+  if (!dst || !src) return ZEN_ERR_INVALID_ARG;
+  if (cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDefault, static_cast<cudaStream_t>(stream)) != cudaSuccess) {
+    cudaGetLastError();
+    return ZEN_ERR_LAUNCH;
+  }
+  return ZEN_OK;
+}
