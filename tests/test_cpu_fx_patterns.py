@@ -99,7 +99,11 @@ def test_the_masked_pattern_keeps_the_mask_and_the_leaf_reads_it():
     holes[1, 0, 0, 2] = neg  # a masked key in the middle: not a suffix
     assert P.classify_mask(holes, B, S, S)[0] == "other"
     assert P.classify_mask(torch.randn(B, 1, S, S), B, S, S)[0] == "other"  # a relative-position bias
-    assert P.classify_mask(torch.ones(B, 1, 1, S, dtype=torch.bool), B, S, S)[0] == "other"
+    keep = torch.arange(S)[None, None, None, :] < lens[:, None, None, None]  # boolean form: True = attend
+    kind, got = P.classify_mask(keep, B, S, S)
+    assert kind == "kv_lens" and got.tolist() == [16, 9, 1]
+    assert P.classify_mask(torch.ones(B, 1, 1, S, dtype=torch.bool), B, S, S)[0] == "none"
+    assert P.classify_mask(torch.ones(S, S, dtype=torch.bool).tril(), B, S, S)[0] == "causal"
 
 
 def test_shapes_the_kernels_do_not_cover_are_computed_by_pytorch():
@@ -124,3 +128,37 @@ def test_functional_sdpa_calls_are_rewritten():
     counts = P.apply_patterns(gm)
     assert counts["functional_sdpa_masked_to_flash"] == 1 and counts["functional_sdpa_to_flash"] == 1
     assert "scaled_dot_product_attention" not in targets(gm)
+
+
+def test_a_huggingface_bert_traces_onto_the_kernel_leaves():
+    """``torch.compile(BertModel, backend=...)``: in the graph Dynamo hands the backend, every layer's attention, both
+    residual LayerNorms and the Linear + GELU are rewritten (zenith/adapters/pytorch_adapter.py:606-744 is the
+    reference's hook for the same thing; its pattern set only knows the hand-written softmax form).  The rewritten
+    graph is inspected, the original one is run (this host has no GPU)."""
+    import copy
+
+    import pytest
+
+    transformers = pytest.importorskip("transformers")
+    cfg = transformers.BertConfig(hidden_size=128, num_attention_heads=2, num_hidden_layers=2, intermediate_size=256,
+                                  hidden_act="gelu_new", vocab_size=1000, max_position_embeddings=64)
+    model = transformers.BertModel(cfg, add_pooling_layer=False).eval()
+    seen = []
+
+    def backend(gm, example_inputs):
+        g2 = copy.deepcopy(gm)
+        seen.append((P.apply_patterns(g2), targets(g2)))
+        return gm.forward
+
+    ids = torch.randint(0, 1000, (2, 32))
+    mask = torch.ones(2, 32, dtype=torch.long)
+    mask[1, 20:] = 0
+    with torch.no_grad():
+        torch.compile(model, backend=backend)(input_ids=ids, attention_mask=mask)
+    counts, after = seen[0]
+    layers = cfg.num_hidden_layers
+    assert counts["functional_sdpa_call_to_flash"] == layers
+    assert counts["add_layer_norm_call"] >= 2 * layers
+    assert counts["linear_then_gelu"] == layers and counts["gelu_new_to_native"] == layers
+    assert "scaled_dot_product_attention" not in after and "layer_norm" not in after and "tanh" not in after
+    assert after.count("zenith_masked_flash_attention") == layers and after.count("zenith_linear_gelu") == layers

@@ -133,3 +133,35 @@ def test_fx_rewritten_module_matches_the_original(cuda):
     got = gm(q, k, v, mask)
     assert got.shape == want.shape and (got - want).abs().max().item() < 2e-2
     assert _capi.device_status() == 0
+
+
+def test_torch_compile_of_a_huggingface_bert_runs_on_the_kernels(cuda):
+    """A stock HuggingFace ``BertModel`` (BERT-base widths, tanh GELU, random init) through
+    ``torch.compile(model, backend=zenith_backend)``: per layer the attention (with the key-padding mask turned into
+    key lengths), both residual LayerNorms and the Linear + GELU run on this library's kernels, and the hidden
+    states match eager PyTorch within the fp16-attention / TF32-GEMM tolerance.  This is the use the reference's
+    torch.compile backend exists for (zenith/adapters/pytorch_adapter.py:606-744, fx_patterns.py:95-114)."""
+    transformers = pytest.importorskip("transformers")
+    from zenith_b200 import fx_patterns as P
+    from zenith_b200 import ops
+
+    torch.manual_seed(0)
+    layers = 2
+    cfg = transformers.BertConfig(hidden_act="gelu_new", num_hidden_layers=layers, vocab_size=2000, max_position_embeddings=128)
+    model = transformers.BertModel(cfg, add_pooling_layer=False).eval().to(cuda)
+    ids = torch.randint(0, 2000, (3, 96), device=cuda)
+    mask = torch.ones(3, 96, dtype=torch.long, device=cuda)
+    mask[1, 70:] = 0
+    mask[2, 33:] = 0
+    with torch.no_grad():
+        want = model(input_ids=ids, attention_mask=mask).last_hidden_state
+        before = ops.launch_count
+        got = torch.compile(model, backend=P.zenith_backend)(input_ids=ids, attention_mask=mask).last_hidden_state
+    counts = dict(P.last_backend_counts)
+    assert counts["functional_sdpa_call_to_flash"] == layers and counts["linear_then_gelu"] == layers
+    assert counts["add_layer_norm_call"] >= 2 * layers
+    assert ops.launch_count - before >= 4 * layers  # the leaves really launched this library's kernels
+    assert got.shape == want.shape and not torch.isnan(got).any()
+    err = (got - want).abs()
+    assert err.max().item() < 3e-2 and err.mean().item() < 2e-3
+    assert _capi.device_status() == 0

@@ -17,6 +17,7 @@ are two fused patterns the kernels support (Linear -> tanh-GELU, residual add ->
 """
 from __future__ import annotations
 
+import math
 from dataclasses import dataclass
 from typing import Callable
 
@@ -53,7 +54,7 @@ def _reference_attention(q, k, v, mask=None, causal=False, scale=None):
         S = q.shape[-2]
         w = w.masked_fill(torch.ones(S, k.shape[-2], dtype=torch.bool, device=q.device).triu(1), float("-inf"))
     if mask is not None:
-        w = w + mask
+        w = w.masked_fill(~mask, float("-inf")) if mask.dtype == torch.bool else w + mask
     return torch.matmul(F.softmax(w, dim=-1), v)
 
 
@@ -61,19 +62,21 @@ def classify_mask(mask, batch: int, q_len: int, k_len: int):
     """What an additive attention mask means for the kernels: ``("none", None)`` (all zeros), ``("causal", None)``
     (0 on and below the diagonal, masked above, the same for every batch / head), ``("kv_lens", lengths)`` (for
     every query of sequence b the keys from ``lengths[b]`` on are masked and the others are 0), or
-    ``("other", None)``.  ``mask`` broadcasts against ``[batch, heads, q_len, k_len]``."""
+    ``("other", None)``.  ``mask`` broadcasts against ``[batch, heads, q_len, k_len]`` and is additive (0 / very
+    negative) or boolean (True = attend), the two forms ``F.scaled_dot_product_attention`` takes."""
     if mask is None:
         return "none", None
-    if mask.dtype == torch.bool:
-        return "other", None
     m = mask
     while m.dim() < 4:
         m = m.unsqueeze(0)
     if m.shape[-1] != k_len or m.shape[1] != 1 or m.shape[0] not in (1, batch) or m.shape[2] not in (1, q_len):
         return "other", None
-    masked = m <= _MASKED
-    if not bool(((m == 0) | masked).all()):
-        return "other", None
+    if m.dtype == torch.bool:  # the boolean form: True = attend
+        masked = ~m
+    else:
+        masked = m <= _MASKED
+        if not bool(((m == 0) | masked).all()):
+            return "other", None
     if not bool(masked.any()):
         return "none", None
     if m.shape[2] == q_len and q_len == k_len and m.shape[0] == 1:
@@ -201,6 +204,11 @@ def zenith_gelu_replacement(x):
     return zenith_gelu(x)
 
 
+def gelu_new_pattern(x):
+    """The tanh GELU as HuggingFace writes it (``NewGELUActivation``: the cube through ``torch.pow``)."""
+    return 0.5 * x * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (x + 0.044715 * torch.pow(x, 3.0))))
+
+
 def layernorm_pattern(x, weight, bias, eps=1e-5):
     mean = x.mean(-1, keepdim=True)
     var = ((x - mean) ** 2).mean(-1, keepdim=True)
@@ -241,7 +249,8 @@ def get_attention_patterns() -> list:
 
 def get_activation_patterns() -> list:
     return [FXPattern("linear_gelu_to_fused", linear_gelu_pattern, zenith_linear_gelu_replacement, priority=12),
-            FXPattern("gelu_tanh_to_native", gelu_tanh_pattern, zenith_gelu_replacement, priority=10)]
+            FXPattern("gelu_tanh_to_native", gelu_tanh_pattern, zenith_gelu_replacement, priority=10),
+            FXPattern("gelu_new_to_native", gelu_new_pattern, zenith_gelu_replacement, priority=10)]
 
 
 def get_normalization_patterns() -> list:
@@ -253,8 +262,94 @@ def get_all_patterns() -> list:
     return get_attention_patterns() + get_activation_patterns() + get_normalization_patterns()
 
 
-def apply_patterns(gm: torch.fx.GraphModule, patterns: list | None = None) -> dict:
-    """Rewrite ``gm`` in place, highest priority first; returns ``{pattern name: matches replaced}``."""
+def rewrite_calls(gm: torch.fx.GraphModule) -> dict:
+    """Node-by-node rewrites of calls whose arguments vary too much for a fixed pattern - the forms a HuggingFace
+    encoder traces to under ``torch.compile``:
+
+    * ``dropout(x, p, training=False)`` and ``dropout(x, 0.0, ...)`` are removed (identity at inference);
+    * ``F.scaled_dot_product_attention(q, k, v, attn_mask=, dropout_p=0.0, scale=, is_causal=)`` with any mask /
+      scale / causal arguments becomes ``zenith_masked_flash_attention`` (which reads the mask at run time);
+    * ``F.layer_norm(x + r, (H,), w, b, eps)`` becomes ``zenith_add_layernorm``, a plain ``F.layer_norm`` over the
+      last dimension ``zenith_layernorm``;
+    * ``zenith_gelu(F.linear(x, w, b))`` becomes ``zenith_linear_gelu``.
+    Returns ``{rewrite name: count}``."""
+    import operator
+
+    counts = {"dropout_removed": 0, "functional_sdpa_call_to_flash": 0, "add_layer_norm_call": 0, "layer_norm_call": 0,
+              "linear_then_gelu": 0}
+    g = gm.graph
+
+    def is_fn(n, *fns):
+        return n.op == "call_function" and any(n.target is f for f in fns)
+
+    for n in list(g.nodes):
+        if is_fn(n, F.dropout, torch.dropout):
+            a = list(n.args) + [None] * 4
+            p_ = n.kwargs.get("p", a[1] if a[1] is not None else 0.5)
+            training = n.kwargs.get("training", n.kwargs.get("train", a[2] if a[2] is not None else True))
+            if training is False or p_ == 0.0:
+                n.replace_all_uses_with(n.args[0])
+                g.erase_node(n)
+                counts["dropout_removed"] += 1
+    for n in list(g.nodes):
+        if is_fn(n, F.scaled_dot_product_attention):
+            kw = dict(n.kwargs)
+            a = list(n.args)
+            mask = kw.get("attn_mask", a[3] if len(a) > 3 else None)
+            drop = kw.get("dropout_p", a[4] if len(a) > 4 else 0.0)
+            causal = kw.get("is_causal", a[5] if len(a) > 5 else False)
+            scale = kw.get("scale", None)
+            if drop != 0.0 or kw.get("enable_gqa", False) or isinstance(causal, torch.fx.Node):
+                continue
+            with g.inserting_before(n):
+                new = g.call_function(zenith_masked_flash_attention, (a[0], a[1], a[2], mask, scale, causal))
+            n.replace_all_uses_with(new)
+            g.erase_node(n)
+            counts["functional_sdpa_call_to_flash"] += 1
+    for n in list(g.nodes):
+        if is_fn(n, F.layer_norm):
+            a = list(n.args)
+            shape = n.kwargs.get("normalized_shape", a[1] if len(a) > 1 else None)
+            w = n.kwargs.get("weight", a[2] if len(a) > 2 else None)
+            b = n.kwargs.get("bias", a[3] if len(a) > 3 else None)
+            eps = n.kwargs.get("eps", a[4] if len(a) > 4 else 1e-5)
+            if not isinstance(shape, (tuple, list)) or len(shape) != 1 or w is None or b is None:
+                continue
+            src = a[0]
+            with g.inserting_before(n):
+                if isinstance(src, torch.fx.Node) and is_fn(src, operator.add, torch.add) and len(src.users) == 1 and \
+                        len(src.args) == 2 and all(isinstance(t, torch.fx.Node) for t in src.args) and not src.kwargs:
+                    new = g.call_function(zenith_add_layernorm, (src.args[0], src.args[1], w, b, eps))
+                    counts["add_layer_norm_call"] += 1
+                else:
+                    src = None
+                    new = g.call_function(zenith_layernorm, (a[0], w, b, eps))
+                    counts["layer_norm_call"] += 1
+            n.replace_all_uses_with(new)
+            g.erase_node(n)
+            if src is not None:
+                g.erase_node(src)
+    for n in list(g.nodes):
+        if is_fn(n, zenith_gelu):
+            src = n.args[0]
+            if isinstance(src, torch.fx.Node) and is_fn(src, F.linear) and len(src.users) == 1:
+                a = list(src.args)
+                w = src.kwargs.get("weight", a[1] if len(a) > 1 else None)
+                b = src.kwargs.get("bias", a[2] if len(a) > 2 else None)
+                with g.inserting_before(n):
+                    new = g.call_function(zenith_linear_gelu, (a[0], w, b))
+                n.replace_all_uses_with(new)
+                g.erase_node(n)
+                g.erase_node(src)
+                counts["linear_then_gelu"] += 1
+    g.lint()
+    gm.recompile()
+    return counts
+
+
+def apply_patterns(gm: torch.fx.GraphModule, patterns: list | None = None, calls: bool = True) -> dict:
+    """Rewrite ``gm`` in place, highest priority first, then (``calls``) the node-by-node rewrites of
+    ``rewrite_calls``; returns ``{name: matches replaced}``."""
     from torch.fx import subgraph_rewriter
 
     counts = {}
@@ -263,10 +358,18 @@ def apply_patterns(gm: torch.fx.GraphModule, patterns: list | None = None) -> di
             continue
         counts[pat.name] = len(subgraph_rewriter.replace_pattern(gm, pat.pattern_fn, pat.replacement_fn))
     gm.recompile()
+    if calls and patterns is None:
+        counts.update(rewrite_calls(gm))
     return counts
 
 
+last_backend_counts: dict = {}
+
+
 def zenith_backend(gm: torch.fx.GraphModule, example_inputs):
-    """``torch.compile(model, backend=zenith_backend)``: apply the patterns to the captured graph, run it eagerly."""
-    apply_patterns(gm)
+    """``torch.compile(model, backend=zenith_backend)``: apply the patterns to the captured graph, run it eagerly.
+    The rewrite counts of the most recent graph are left in ``last_backend_counts``."""
+    counts = apply_patterns(gm)
+    last_backend_counts.clear()
+    last_backend_counts.update(counts)
     return gm.forward
