@@ -141,6 +141,8 @@ def zenith_layernorm(x, weight, bias, eps):
 
 @torch.fx.wrap
 def zenith_add_layernorm(x, residual, weight, bias, eps):
+    if residual.shape != x.shape or residual.dtype != x.dtype:  # a broadcast add (embedding sums): add first
+        return zenith_layernorm(x + residual, weight, bias, eps)
     x2 = x.reshape(-1, x.shape[-1]).contiguous()
     r2 = residual.reshape(-1, x.shape[-1]).contiguous()
     return ops.add_layernorm(x2, r2, weight.to(x.dtype), bias.to(x.dtype), float(eps)).reshape(x.shape)
