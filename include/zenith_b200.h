@@ -277,10 +277,17 @@ int zen_convert_f16_to_f32(const void* x, float* y, int64_t n, void* stream);
  * zen_absmax_rows_f32: out[r] = max_c |w[r, c]|, the per-output-channel observer
  *   (zenith/optimization/qat.py:195-199).
  * zen_quantize_rows_f32: q[r, c] = clamp(round(w[r, c] / scale[r]), -128, 127), per-channel int8 weights
- *   (the int8 form of core/src/qat_cuda.cu:90-114). */
+ *   (the int8 form of core/src/qat_cuda.cu:90-114).
+ * zen_histogram_*: hist[i] += number of x in bin i of `bins` equal bins over [minmax[0], minmax[1]] (device fp32[2],
+ *   read by the kernel: run zen_minmax_* first and the range is the running one, with no host read-back), binned
+ *   exactly as numpy.histogram bins a float32 array; hist is int64[bins] in device memory, bins <= 4096.  The running
+ *   histogram of TensorStats.update (zenith/optimization/quantization.py:69-83), which the percentile and entropy
+ *   calibrators read (:119-214); replaces nothing on the device: the reference's observers are host numpy. */
 size_t zen_minmax_workspace_bytes(void);
 int zen_minmax_f32(const float* x, int64_t n, float* minmax, void* workspace, size_t workspace_bytes, void* stream);
 int zen_minmax_f16(const void* x, int64_t n, float* minmax, void* workspace, size_t workspace_bytes, void* stream);
+int zen_histogram_f32(const float* x, int64_t n, const float* minmax, int bins, long long* hist, void* stream);
+int zen_histogram_f16(const void* x, int64_t n, const float* minmax, int bins, long long* hist, void* stream);
 int zen_absmax_rows_f32(const float* w, int rows, int cols, int64_t ld, float* out, void* stream);
 int zen_quantize_rows_f32(const float* w, const float* scale, int rows, int cols, int64_t ldw, int8_t* q, int64_t ldq,
                           int round_mode, void* stream);

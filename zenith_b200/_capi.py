@@ -67,6 +67,8 @@ SIGNATURES = {
     "zen_minmax_workspace_bytes": [],
     "zen_minmax_f32": [_p, _i64, _p, _p, C.c_size_t, _p],
     "zen_minmax_f16": [_p, _i64, _p, _p, C.c_size_t, _p],
+    "zen_histogram_f32": [_p, _i64, _p, _i, _p, _p],
+    "zen_histogram_f16": [_p, _i64, _p, _i, _p, _p],
     "zen_absmax_rows_f32": [_p, _i, _i, _i64, _p, _p],
     "zen_quantize_rows_f32": [_p, _p, _i, _i, _i64, _p, _i64, _i, _p],
     "zen_embed_layernorm_f16": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _f, _i, _i, _i, _i, _i, _f, _p],

@@ -40,18 +40,37 @@ def activation_scales_from_ranges(ranges: dict, n_layers: int) -> list:
             for li in range(n_layers)]
 
 
-def calibrate(cfg: EncoderConfig, params: dict, batches, device="cuda:0") -> Int8Scales:
+def activation_scales_from_stats(stats: dict, n_layers: int, method: CalibrationMethod, percentile: float = 99.99) -> list:
+    """``stats[point][layer]`` = ``TensorStats`` (range + histogram) -> per-layer scale dicts through the
+    reference's calibrators (zenith/optimization/quantization.py:95-214), symmetric."""
+    from .quantization import EntropyCalibrator, MinMaxCalibrator, PercentileCalibrator
+
+    cal = {CalibrationMethod.MINMAX: MinMaxCalibrator(True), CalibrationMethod.PERCENTILE: PercentileCalibrator(percentile, True),
+           CalibrationMethod.ENTROPY: EntropyCalibrator(True)}[method]
+    return [{point: float(cal.compute_params(stats[point][li]).scale) for point in ACT_POINTS} for li in range(n_layers)]
+
+
+def calibrate(cfg: EncoderConfig, params: dict, batches, device="cuda:0", method: CalibrationMethod | str = CalibrationMethod.MINMAX,
+              percentile: float = 99.99) -> Int8Scales:
     """``batches``: iterable of ``(ids [B,S] integer tensor, kv_lens [B] int32 tensor or None)``.
 
-    The activation ranges accumulate on the device (``ops.RangeObserver``: running min / max, the statistic of
-    ``TensorStats.update``) over all batches and are read back once; min / max select among the inputs, so
-    the scales are those the per-batch host observers would give."""
+    The activation statistics accumulate on the device over all batches and are read back once: the running min /
+    max (``ops.RangeObserver``, the statistic of ``TensorStats.update``) for min-max calibration - min / max select
+    among the inputs, so the scales are those the per-batch host observers would give - and, for ``method``
+    "percentile" / "entropy", also the running 2048-bin histogram (``ops.HistogramObserver``), which the reference's
+    calibrators then turn into a clipping range."""
+    method = CalibrationMethod(method) if not isinstance(method, CalibrationMethod) else method
     enc = Fp16Encoder(cfg, params, device)
-    observers = enc.make_observers()
+    observers = enc.make_observers(histogram=method != CalibrationMethod.MINMAX)
     for ids, kv_lens in batches:
         enc.forward_with_taps(ids, kv_lens, observers)
-    ranges = {p: [[observers[p][li].range()] for li in range(cfg.layers)] for p in ACT_POINTS}
-    return Int8Scales(act=activation_scales_from_ranges(ranges, cfg.layers), weights=quantize_weights(params))
+    if method == CalibrationMethod.MINMAX:
+        ranges = {p: [[observers[p][li].range()] for li in range(cfg.layers)] for p in ACT_POINTS}
+        act = activation_scales_from_ranges(ranges, cfg.layers)
+    else:
+        stats = {p: [observers[p][li].stats() for li in range(cfg.layers)] for p in ACT_POINTS}
+        act = activation_scales_from_stats(stats, cfg.layers, method, percentile)
+    return Int8Scales(act=act, weights=quantize_weights(params))
 
 
 def quantize_weights_on_device(params: dict, device="cuda:0") -> list:

@@ -156,9 +156,83 @@ __global__ void __launch_bounds__(256) quantize_rows_kernel(const float* __restr
     qr[c] = int8_t(zen_det_round_clamp_i8(ZEN_DIV(wr[c], s), round_mode));
 }
 
+// ------------------------------------------------------------------------------------------------
+// histogram of an activation tensor over the running range, as TensorStats.update keeps it
+// (zenith/optimization/quantization.py:69-83: np.histogram(tensor, bins, range=(min, max)) added to the running
+// histogram, the range being the running one AFTER this tensor's min / max went into it).
+// Bin of a value, as numpy's uniform-bin path computes it for a float32 array:
+//   edges[i] = float32(i * step + lo)  with step = (hi - lo) / bins in float64 (np.linspace), edges[bins] = hi
+//   i = trunc(((x - lo) / float32(hi - lo)) * bins)   in float32;  i == bins -> bins - 1
+//   x <  edges[i]                        -> i - 1
+//   x >= edges[i + 1] and i != bins - 1  -> i + 1
+// Values outside [lo, hi] (and NaNs) are not counted.  lo >= hi: the range (0, 1), as the reference does.
+// Counts are integers: the result does not depend on the order of the atomic additions.
+// ------------------------------------------------------------------------------------------------
+constexpr int HIST_THREADS = 256;
+constexpr int HIST_MAX_BINS = 4096;
+
+template <typename T>
+__global__ void __launch_bounds__(HIST_THREADS) histogram_kernel(const T* __restrict__ x, int64_t n, const float* __restrict__ minmax,
+                                                                  int bins, unsigned long long* __restrict__ hist) {
+  extern __shared__ unsigned char hist_smem[];
+  float* edges = reinterpret_cast<float*>(hist_smem);                    // [bins + 1]
+  unsigned int* local = reinterpret_cast<unsigned int*>(edges + bins + 1);  // [bins]
+  float lo = minmax[0], hi = minmax[1];
+  if (!(lo < hi)) {
+    lo = 0.0f;
+    hi = 1.0f;
+  }
+  const double step = __ddiv_rn(__dsub_rn(double(hi), double(lo)), double(bins));
+  for (int i = threadIdx.x; i <= bins; i += HIST_THREADS) {
+    edges[i] = i == bins ? hi : float(__dadd_rn(__dmul_rn(double(i), step), double(lo)));
+    if (i < bins) local[i] = 0u;
+  }
+  __syncthreads();
+  const float denom = float(__dsub_rn(double(hi), double(lo)));
+  const float fbins = float(bins);
+  const int64_t nthreads = int64_t(gridDim.x) * HIST_THREADS;
+  for (int64_t k = int64_t(blockIdx.x) * HIST_THREADS + threadIdx.x; k < n; k += nthreads) {
+    const float v = to_f32<T>(x[k]);
+    if (!(v >= lo && v <= hi)) continue;
+    int i = int(ZEN_MUL(ZEN_DIV(ZEN_SUB(v, lo), denom), fbins));
+    if (i == bins) i = bins - 1;
+    if (i < 0 || i >= bins) continue;  // cannot happen for v in [lo, hi]; guards the table accesses below
+    if (v < edges[i]) {
+      if (i == 0) continue;
+      i -= 1;
+    }
+    if (i != bins - 1 && v >= edges[i + 1]) i += 1;
+    atomicAdd(&local[i], 1u);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < bins; i += HIST_THREADS)
+    if (local[i] != 0u) atomicAdd(&hist[i], static_cast<unsigned long long>(local[i]));
+}
+
+template <typename T>
+static int run_histogram(const T* x, int64_t n, const float* minmax, int bins, long long* hist, cudaStream_t s) {
+  if (n < 0 || bins <= 0 || bins > HIST_MAX_BINS || !minmax || !hist) return ZEN_ERR_INVALID_ARG;
+  if (n == 0) return ZEN_OK;
+  if (!x) return ZEN_ERR_INVALID_ARG;
+  int64_t want = (n + HIST_THREADS * 16 - 1) / (HIST_THREADS * 16);
+  const int cap = num_sms() * 4;
+  const int ctas = int(want < 1 ? 1 : (want > cap ? cap : want));
+  const size_t smem = size_t(2 * bins + 1) * 4;
+  histogram_kernel<T><<<ctas, HIST_THREADS, smem, s>>>(x, n, minmax, bins, reinterpret_cast<unsigned long long*>(hist));
+  return cudaGetLastError() == cudaSuccess ? ZEN_OK : ZEN_ERR_LAUNCH;
+}
+
 }  // namespace zen
 
 using namespace zen;
+
+extern "C" int zen_histogram_f32(const float* x, int64_t n, const float* minmax, int bins, long long* hist, void* stream) {
+  return run_histogram<float>(x, n, minmax, bins, hist, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int zen_histogram_f16(const void* x, int64_t n, const float* minmax, int bins, long long* hist, void* stream) {
+  return run_histogram<__half>(static_cast<const __half*>(x), n, minmax, bins, hist, static_cast<cudaStream_t>(stream));
+}
 
 extern "C" size_t zen_minmax_workspace_bytes(void) { return size_t(MM_MAX_CTAS) * sizeof(float2); }
 

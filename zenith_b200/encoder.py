@@ -325,9 +325,11 @@ class Fp16Encoder(_EncoderBase):
             return None
         return {p: [o.range() for o in v] for p, v in observers.items()}
 
-    def make_observers(self) -> dict:
-        """``{point: [RangeObserver per layer]}`` for ``forward_with_taps``."""
-        return {p: [ops.RangeObserver(self.device) for _ in self.layers] for p in ACT_POINTS}
+    def make_observers(self, histogram: bool = False) -> dict:
+        """``{point: [observer per layer]}`` for ``forward_with_taps``: running range only (``ops.RangeObserver``),
+        or range + running histogram (``ops.HistogramObserver``) for the percentile / entropy calibrators."""
+        make = ops.HistogramObserver if histogram else ops.RangeObserver
+        return {p: [make(self.device) for _ in self.layers] for p in ACT_POINTS}
 
 
 @dataclass

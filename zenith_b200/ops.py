@@ -372,6 +372,30 @@ class RangeObserver:
         return lo, hi
 
 
+class HistogramObserver(RangeObserver):
+    """``RangeObserver`` that also keeps the running histogram of ``TensorStats.update``
+    (zenith/optimization/quantization.py:69-83) on the device: after each tensor's min / max have gone into the
+    running range, the tensor is binned over that range (``num_bins`` equal bins, numpy's binning) and added to the
+    histogram - the statistics the percentile and entropy calibrators need.  Nothing is read back until ``stats()``."""
+
+    def __init__(self, device, num_bins: int = 2048):
+        super().__init__(device)
+        self.num_bins = int(num_bins)
+        self.hist = torch.zeros(self.num_bins, dtype=torch.int64, device=device)
+
+    def observe(self, x: torch.Tensor) -> None:
+        super().observe(x)
+        fn = "zen_histogram_f16" if x.dtype == torch.float16 else "zen_histogram_f32"
+        _call(fn, x.data_ptr(), x.numel(), self.minmax.data_ptr(), self.num_bins, self.hist.data_ptr(), _stream())
+
+    def stats(self):
+        """The observations as a ``quantization.TensorStats`` (host): min, max and the int64 histogram."""
+        from .quantization import TensorStats
+
+        lo, hi = self.range()
+        return TensorStats(min_val=lo, max_val=hi, histogram=self.hist.cpu().numpy().copy(), num_bins=self.num_bins)
+
+
 def absmax_rows(w):
     """``max_c |w[r, c]|`` per row of a CUDA fp32 matrix: the per-output-channel weight observer
     (zenith/optimization/qat.py:195-199)."""
