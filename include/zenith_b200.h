@@ -209,6 +209,10 @@ int zen_matmul_f32_static(const float* A, const float* B, float* C, int M, int N
 int zen_gelu_f32(const float* x, float* y, int64_t n, void* stream);
 int zen_gelu_f16(const void* x, void* y, int64_t n, void* stream);
 int zen_relu_f32(const float* x, float* y, int64_t n, void* stream);
+/* tanh, the activation of the BERT pooler (the HuggingFace BertModel the reference measures itself against keeps
+ * one: benchmarks/bert_hybrid.py:188-196); the reference's own kernel set has none. */
+int zen_tanh_f32(const float* x, float* y, int64_t n, void* stream);
+int zen_tanh_f16(const void* x, void* y, int64_t n, void* stream);
 
 /* bias + GELU over [rows, features]: core/src/fused_kernels.cu:47-62,347-353 (fused_bias_gelu). */
 int zen_bias_gelu_f32(const float* x, const float* bias, float* y, int rows, int features, void* stream);

@@ -122,6 +122,13 @@ def gelu_libm(x):
     return y
 
 
+def tanh(x, libm=False):
+    x = _c(x, np.float32)
+    y = np.empty_like(x)
+    (_load().orc_tanh_libm_f32 if libm else _load().orc_tanh_f32)(_p(x), _p(y), C.c_size_t(x.size))
+    return y
+
+
 def add_layernorm(x, residual, gamma, beta, eps=1e-5):
     """Two-pass fp32 ``LayerNorm(x + residual)`` (python/src/features_bindings.hpp:116-171)."""
     x = _c(x, np.float32)

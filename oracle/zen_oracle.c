@@ -74,6 +74,15 @@ void orc_gelu_libm_f32(const float* x, float* y, size_t n) {
   }
 }
 
+/* tanh as the device evaluates it (det_math.h) and with libm, for the pooler head
+ * (HuggingFace BertPooler, the FP reference of benchmarks/bert_hybrid.py:188-196). */
+void orc_tanh_f32(const float* x, float* y, size_t n) {
+  for (size_t i = 0; i < n; ++i) y[i] = zen_det_tanh(x[i]);
+}
+void orc_tanh_libm_f32(const float* x, float* y, size_t n) {
+  for (size_t i = 0; i < n; ++i) y[i] = tanhf(x[i]);
+}
+
 /* y = LayerNorm(x [+ residual]) * gamma + beta, two-pass, biased variance, fp32.
  * core/src/cuda_kernels.cu:132-184 (layernorm_parallel_kernel) and
  * python/src/features_bindings.hpp:116-171 (fused_add_layernorm_cpu). */

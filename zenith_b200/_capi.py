@@ -51,6 +51,8 @@ SIGNATURES = {
     "zen_gelu_f32": [_p, _p, _i64, _p],
     "zen_gelu_f16": [_p, _p, _i64, _p],
     "zen_relu_f32": [_p, _p, _i64, _p],
+    "zen_tanh_f32": [_p, _p, _i64, _p],
+    "zen_tanh_f16": [_p, _p, _i64, _p],
     "zen_bias_gelu_f32": [_p, _p, _p, _i, _i, _p],
     "zen_layernorm_f32": [_p, _p, _p, _p, _i, _i, _f, _p],
     "zen_layernorm_f16": [_p, _p, _p, _p, _i, _i, _f, _p],

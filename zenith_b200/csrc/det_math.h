@@ -89,6 +89,12 @@ ZEN_DM_FN float zen_det_gelu(float x) {
   return ZEN_DIV(x, ZEN_ADD(1.0f, e));
 }
 
+/* tanh(x) = 2 / (1 + exp(-2x)) - 1 with the exponential above (absolute error below 2e-7; the pooler's activation). */
+ZEN_DM_FN float zen_det_tanh(float x) {
+  const float e = zen_det_exp2(ZEN_MUL(x, -2.885390081777927f)); /* exp(-2x): -2 log2(e) folded */
+  return ZEN_SUB(ZEN_DIV(2.0f, ZEN_ADD(1.0f, e)), 1.0f);
+}
+
 /* clamp(round(v), -128, 127); mode 0 = nearest-even, 1 = toward zero.  NaN maps to -128. */
 ZEN_DM_FN int zen_det_round_clamp_i8(float v, int round_mode) {
   v = v > -128.0f ? v : -128.0f;

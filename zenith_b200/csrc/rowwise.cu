@@ -357,7 +357,7 @@ static int launch_ln(const RowParams& p, cudaStream_t s) {
 // ------------------------------------------------------------------------------------------
 // elementwise
 // ------------------------------------------------------------------------------------------
-enum { EW_GELU = 0, EW_RELU = 1, EW_BIAS_GELU = 2, EW_QUANT = 3, EW_DEQUANT = 4, EW_CONVERT = 5 };
+enum { EW_GELU = 0, EW_RELU = 1, EW_BIAS_GELU = 2, EW_QUANT = 3, EW_DEQUANT = 4, EW_CONVERT = 5, EW_TANH = 6 };
 
 struct EwParams {
   const void* x;
@@ -378,6 +378,7 @@ __device__ __forceinline__ TO ew_apply(TI xin, const EwParams& p, int64_t idx) {
     const float x = float(xin);
     if constexpr (OP == EW_GELU) return TO(zen_det_gelu(x));
     else if constexpr (OP == EW_RELU) return TO(x > 0.f ? x : 0.f);
+    else if constexpr (OP == EW_TANH) return TO(zen_det_tanh(x));
     else if constexpr (OP == EW_BIAS_GELU) return TO(zen_det_gelu(ZEN_ADD(x, __ldg(p.bias + (idx % p.features)))));
     else if constexpr (OP == EW_QUANT) return TO(quantize_value(x, p.scale, p.zero_point, p.round_mode));
     else return TO(x);
@@ -455,6 +456,16 @@ int zen_gelu_f16(const void* x, void* y, int64_t n, void* stream) {
   if (n < 0 || (n > 0 && (!x || !y))) return ZEN_ERR_INVALID_ARG;
   EwParams p{x, y, nullptr, n, 1, 1.f, 0, 0};
   return launch_ew<EW_GELU, __half, __half>(p, static_cast<cudaStream_t>(stream));
+}
+int zen_tanh_f32(const float* x, float* y, int64_t n, void* stream) {
+  if (n < 0 || (n > 0 && (!x || !y))) return ZEN_ERR_INVALID_ARG;
+  EwParams p{x, y, nullptr, n, 1, 1.f, 0, 0};
+  return launch_ew<EW_TANH, float, float>(p, static_cast<cudaStream_t>(stream));
+}
+int zen_tanh_f16(const void* x, void* y, int64_t n, void* stream) {
+  if (n < 0 || (n > 0 && (!x || !y))) return ZEN_ERR_INVALID_ARG;
+  EwParams p{x, y, nullptr, n, 1, 1.f, 0, 0};
+  return launch_ew<EW_TANH, __half, __half>(p, static_cast<cudaStream_t>(stream));
 }
 int zen_relu_f32(const float* x, float* y, int64_t n, void* stream) {
   if (n < 0 || (n > 0 && (!x || !y))) return ZEN_ERR_INVALID_ARG;

@@ -167,7 +167,7 @@ def linear_fp16_add_layernorm(x, w, bias, residual, gamma, beta, eps: float, *, 
 def linear_fp16(x, w, bias=None, *, act="none", out_dtype=torch.float16, out=None, tile_n: int = 0,
                 pair: bool | None = None):
     """``act(x @ w.T + bias)`` with fp16 operands, fp32 accumulation (core/src/fp16_kernels.cu:92-122)."""
-    _require(x, "x", torch.float16, 2)
+    _require(x, "x", torch.float16, 2, rows_may_be_strided=True)
     _require(w, "w", torch.float16, 2)
     M, K = x.shape
     N, K2 = w.shape
@@ -181,7 +181,7 @@ def linear_fp16(x, w, bias=None, *, act="none", out_dtype=torch.float16, out=Non
         out = torch.empty((M, N), dtype=out_dtype, device=x.device)
     if M == 0 or N == 0:
         return out
-    _call("zen_linear_f16_ex", x.data_ptr(), K, w.data_ptr(), K, M, N, K, _ptr(bias), _ACT[act], _OUT[out_dtype],
+    _call("zen_linear_f16_ex", x.data_ptr(), x.stride(0) if M > 1 else K, w.data_ptr(), K, M, N, K, _ptr(bias), _ACT[act], _OUT[out_dtype],
           out.data_ptr(), out.stride(0), _capi.gemm_tile_n(tile_n) | _pair_flag(pair), _stream())
     return out
 
@@ -262,6 +262,17 @@ def gelu(x):
     y = torch.empty_like(x)
     if x.numel():
         _call("zen_gelu_f16", x.data_ptr(), y.data_ptr(), x.numel(), _stream())
+    return y
+
+
+def tanh(x):
+    """Elementwise tanh, fp32 or fp16 (the pooler's activation)."""
+    if x.dtype not in (torch.float32, torch.float16):
+        raise RuntimeError("input must be fp32 or fp16")
+    _require(x, "input", x.dtype)
+    y = torch.empty_like(x)
+    if x.numel():
+        _call("zen_tanh_f32" if x.dtype == torch.float32 else "zen_tanh_f16", x.data_ptr(), y.data_ptr(), x.numel(), _stream())
     return y
 
 
