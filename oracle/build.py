@@ -2,7 +2,8 @@
 
 * ``oracle/_build/libzen_oracle.so``  from ``oracle/zen_oracle.c`` (gcc, -ffp-contract=off).
 * ``oracle/_ref/libzenith_ref_cpu.so`` from the REFERENCE's own ``core/src/cpu_kernels.cpp``, compiled
-  where it lies under the mounted reference tree (environment variable ``ZENITH_REFERENCE``) with
+  where it lies under the mounted reference tree (environment variable ``ZENITH_REFERENCE``, else a directory
+  named ``reference`` beside this repository) with
   ``g++ -O3 -mavx2 -mfma -std=c++20`` plus a C-linkage shim.  Skipped when the tree is absent: a
   prebuilt ``_ref`` library is then used as it is.
 
@@ -20,7 +21,7 @@ BUILD = HERE / "_build"
 REF_OUT = HERE / "_ref"
 ORACLE_SO = BUILD / "libzen_oracle.so"
 REF_SO = REF_OUT / "libzenith_ref_cpu.so"
-REFERENCE = Path(os.environ.get("ZENITH_REFERENCE", "/root/reference"))
+REFERENCE = Path(os.environ.get("ZENITH_REFERENCE") or HERE.parent.parent / "reference")
 
 
 def _run(cmd):

@@ -1,19 +1,24 @@
 """Generates tests/golden/quant_golden.npz and config1_golden.json by IMPORTING THE REFERENCE
 (vibeswithkk/ZENITH, read-only tree) and running its own quantization / QAT code on seeded inputs.
 
-    PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py [/path/to/reference]
+    PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py /path/to/reference
+    (or with the environment variable ZENITH_REFERENCE set to that path)
 
 The outputs are committed; the tests never need the reference tree.  Inputs are regenerated in the
 tests from the seeds below, only the reference's OUTPUTS are stored.
 """
 import hashlib
+import importlib.util
 import json
+import os
 import sys
 from pathlib import Path
 
 import numpy as np
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("ZENITH_REFERENCE")
+if not REF or not (Path(REF) / "zenith").is_dir():
+    raise SystemExit("usage: make_golden.py /path/to/reference   (the directory that holds the `zenith` package)")
 sys.dont_write_bytecode = True
 sys.path.insert(0, REF)
 
@@ -107,11 +112,23 @@ fqw.disable_observer()
 s_w = np.asarray(fqw.scale, dtype=np.float32)
 Wq = np.clip(np.round(Wc / s_w[:, None]), -128, 127).astype(np.int8)
 Xq = np.clip(np.round(X / np.float32(s_x)), -128, 127).astype(np.int8)
-acc = Xq.astype(np.int32) @ Wq.astype(np.int32).T
+# the integer product by the reference's own function (benchmarks/int8_bench.py:42-45; unit scales: the float32
+# result is exact, |acc| < 2^24)
+_spec = importlib.util.spec_from_file_location("ref_int8_bench", Path(REF) / "benchmarks" / "int8_bench.py")
+ib = importlib.util.module_from_spec(_spec)
+_spec.loader.exec_module(ib)
+acc = ib.int8_matmul_reference(Xq, np.ascontiguousarray(Wq.T), np.float32(1.0), np.float32(1.0)).astype(np.int32)
+assert np.array_equal(acc, Xq.astype(np.int32) @ Wq.astype(np.int32).T)
 sha = lambda a: hashlib.sha256(np.ascontiguousarray(a).tobytes()).hexdigest()
+# ... and that benchmark's own per-tensor pipeline on the same tensors (int8_bench.py:19-25, 42-45)
+bqx, bsx, _ = ib.quantize_to_int8(X)
+bqw, bsw, _ = ib.quantize_to_int8(Wc)
+by = ib.int8_matmul_reference(bqx, np.ascontiguousarray(bqw.T), bsx, bsw)
 cfg1 = {"s_x": float(s_x), "s_w_sha256": sha(s_w), "s_w_first": [float(v) for v in s_w[:4]],
         "Wq_sha256": sha(Wq), "Wq_minus128": int((Wq == -128).sum()), "Xq_sha256": sha(Xq),
         "acc_sha256": sha(acc), "acc_sum": int(acc.astype(np.int64).sum()),
-        "fake_quant_W_sha256": sha(np.asarray(fqw.forward(Wc), dtype=np.float32))}
+        "fake_quant_W_sha256": sha(np.asarray(fqw.forward(Wc), dtype=np.float32)),
+        "bench_sx": float(bsx), "bench_sw": float(bsw), "bench_qx_sha256": sha(bqx), "bench_qw_sha256": sha(bqw),
+        "bench_y_sha256": sha(np.asarray(by, dtype=np.float32)), "bench_y_dtype": str(np.asarray(by).dtype)}
 (HERE / "config1_golden.json").write_text(json.dumps(cfg1, indent=1))
 print("wrote", HERE / "quant_golden.npz", (HERE / "quant_golden.npz").stat().st_size, "bytes;", cfg1)

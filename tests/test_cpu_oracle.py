@@ -140,3 +140,19 @@ def test_attention_rows_is_a_row_subset_of_attention():
     for causal in (False, True):
         full = O.attention(q, k, v, [70, 33], causal)
         assert np.array_equal(full[:, :, rows], O.attention_rows(q, k, v, rows, [70, 33], causal))
+
+
+def test_oracle_reproduces_the_reference_benchmark_pipeline_on_config1():
+    """benchmarks/int8_bench.py:19-25, 42-45 run on the config-1 tensors (digests stored by make_golden.py): per-tensor
+    symmetric quantization of X and W, int32 product, dequantised with the two scales."""
+    cfg1 = json.loads((Path(__file__).parent / "golden" / "config1_golden.json").read_text())
+    sha = lambda a: hashlib.sha256(np.ascontiguousarray(a).tobytes()).hexdigest()
+    M = 1234
+    X = np.random.default_rng(M).standard_normal((128, 768)).astype(np.float32)
+    W = (np.random.default_rng(M + 100).standard_normal((3072, 768)) * 0.02).astype(np.float32)
+    sx, sw = np.float32(cfg1["bench_sx"]), np.float32(cfg1["bench_sw"])
+    assert sx == np.abs(X).max() / np.float32(127.0) and sw == np.abs(W).max() / np.float32(127.0)
+    qx, qw = O.quantize(X, sx), O.quantize(W, sw)
+    assert sha(qx) == cfg1["bench_qx_sha256"] and sha(qw) == cfg1["bench_qw_sha256"]
+    y = O.epilogue(O.gemm_s8(qx, qw), sx, np.full(3072, sw, np.float32), None, "none")
+    assert sha(y) == cfg1["bench_y_sha256"]
