@@ -3,6 +3,7 @@
     python -m zenith_b200.microbench gemm_i8 --m 4096 --n 2304 --k 768 --epilogue f16 [--tile-n 256] [--iters 20]
     python -m zenith_b200.microbench add_ln  --rows 4096 --hidden 768
     python -m zenith_b200.microbench attention --b 32 --h 12 --s 128 --d 64 [--causal]
+    python -m zenith_b200.microbench qkv_attn --b 32 --h 12 --s 128
 
 Prints one JSON line.  The counterpart of the reference's benchmarks/int8_bench.py, wmma_bench.py,
 layernorm_bench.py and flash_attention_benchmark.py; also the small, single-kernel command used for
@@ -37,7 +38,7 @@ def _time(fn, iters, flush):
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["gemm_i8", "gemm_i8_ln", "gemm_f16", "add_ln", "attention", "encoder"])
+    ap.add_argument("case", choices=["gemm_i8", "gemm_i8_ln", "gemm_f16", "add_ln", "attention", "qkv_attn", "encoder"])
     ap.add_argument("--config", choices=["base", "large"], default="base")
     ap.add_argument("--dtype", choices=["int8", "fp16"], default="int8")
     ap.add_argument("--batch", type=int, default=32)
@@ -101,6 +102,17 @@ def main() -> None:
         med, best = _time(lambda: ops.add_layernorm(x, r, g, be, 1e-12, out_scale=0.03), a.iters, flush)
         nbytes = a.rows * a.hidden * 7  # 2 fp16 reads, 1 fp16 write, 1 int8 write
         out.update(rows=a.rows, hidden=a.hidden, us=med, us_min=best, gbs=nbytes / med / 1e3)
+    elif a.case == "qkv_attn":
+        hidden = a.h * 64
+        x = torch.randint(-128, 128, (a.b * a.s, hidden), dtype=torch.int8, device=dev)
+        w = torch.randint(-128, 128, (3 * hidden, hidden), dtype=torch.int8, device=dev)
+        ws = torch.rand(3 * hidden, device=dev) * 1e-4
+        b = torch.randn(3 * hidden, device=dev) * 0.1
+        lens = torch.full((a.b,), max(1, a.s - 16), dtype=torch.int32, device=dev)
+        med, best = _time(lambda: ops.qkv_attention_int8(x, w, 0.02, ws, b, a.b, a.s, a.h, kv_lens=lens, out_scale=0.02),
+                          a.iters, flush)
+        out.update(b=a.b, h=a.h, s=a.s, us=med, us_min=best, projection_tops=2.0 * a.b * a.s * 3 * hidden * hidden / med / 1e6,
+                   attention_tflops=4.0 * a.b * a.h * a.s * a.s * 64 / med / 1e6)
     elif a.case == "encoder":
         import numpy as np
 
