@@ -14,8 +14,10 @@
 //   warp 0       TMA producer of the GEMM operand ring
 //   warp 1       GEMM MMA issuer (one lane)
 //   warps 2, 3   attention MMA issuers (one lane each) for the items of buffer set 0 / 1
-//   warps 4..7   work group 0: one thread per row; QKV epilogue, softmax, output of the items of set 0
-//   warps 8..11  work group 1: the same for set 1
+//   warps 4..11  work group 0: TWO threads per row (each half of the columns / keys); projection epilogue, softmax,
+//                output of the items of set 0.  One thread per row ran its 3000-instruction chain at 0.4 instructions
+//                per clock (7 us per item, measured with timestamps); splitting a row over two warps halves it.
+//   warps 12..19 work group 1: the same for set 1
 // A buffer set = 192 TMEM columns (accumulators, then S over the first 128, O over the last 64) + 48 KB of shared
 // memory (Q, K, V tiles; P later overwrites Q + K, the output staging overwrites them again).  Items alternate
 // between the sets, so two items are in flight per CTA besides the one whose operands are being loaded.
@@ -26,7 +28,8 @@
 
 namespace zen {
 
-constexpr int QA_THREADS = 384;
+constexpr int QA_THREADS = 640;
+constexpr int QA_WG_THREADS = 256;  // one work group: 8 warps, two per TMEM lane quadrant
 constexpr int QA_STAGES = 3;
 constexpr int QA_BN = 192;                                    // Q, K, V columns of one head
 constexpr int QA_STAGE_BYTES = GEMM_BM * 128 + QA_BN * 128;  // 16 KB of activations + 24 KB of weights per k-block
@@ -51,9 +54,9 @@ struct QkvAttnParams {
 };
 
 constexpr size_t qkv_attn_smem_bytes() {
-  // ring + two buffer sets + scale / bias rows (2 sets x 2 item parities x 2 x 192 floats) + barriers and flags +
-  // alignment slack
-  return size_t(QA_STAGES) * QA_STAGE_BYTES + 2 * size_t(QA_SET_BYTES) + 2 * 2 * 2 * QA_BN * 4 + 512 + 1024;
+  // ring + two buffer sets + scale / bias rows (2 sets x 2 x 192 floats) + row maxima and sums exchanged between the
+  // two threads of a row (2 sets x 5 x 128 floats) + barriers and flags + alignment slack
+  return size_t(QA_STAGES) * QA_STAGE_BYTES + 2 * size_t(QA_SET_BYTES) + 2 * 2 * QA_BN * 4 + 2 * 5 * 128 * 4 + 512 + 1024;
 }
 
 __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2) {
@@ -77,8 +80,9 @@ qkv_attn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint8_t* sets = smem + size_t(QA_STAGES) * QA_STAGE_BYTES;  // [2][Q | K | V], 1024-byte aligned
-  float* col_rows = reinterpret_cast<float*>(sets + 2 * QA_SET_BYTES);  // [2 sets][2 item parities][scale 192 | bias 192]
-  uint8_t* ctrl = reinterpret_cast<uint8_t*>(col_rows + 2 * 2 * 2 * QA_BN);
+  float* col_rows = reinterpret_cast<float*>(sets + 2 * QA_SET_BYTES);  // [2 sets][scale 192 | bias 192]
+  float* xch = col_rows + 2 * 2 * QA_BN;                                // [2 sets][max half 0 | max half 1 | sums x 3][128 rows]
+  uint8_t* ctrl = reinterpret_cast<uint8_t*>(xch + 2 * 5 * 128);
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(ctrl);
   uint64_t* empty_bar = full_bar + QA_STAGES;
   uint64_t* acc_full = empty_bar + QA_STAGES;  // [2] projection accumulators of the set are complete
@@ -88,7 +92,8 @@ qkv_attn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   uint64_t* p_ready = s_full + 2;              // [2] P is in shared memory and S has been read
   uint64_t* o_full = p_ready + 2;              // [2] O = P V is complete
   uint64_t* wg_bar = o_full + 2;               // [2] work-group-wide rendezvous (a bounded wait, unlike bar.sync)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(wg_bar + 2);
+  uint64_t* pair_bar = wg_bar + 2;             // [2 sets][4 quadrants][3 uses per item] the two warps that share 32 rows
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pair_bar + 24);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -111,13 +116,14 @@ qkv_attn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&acc_full[i], 1);
-      mbar_init(&acc_empty[i], 128);
-      mbar_init(&qkv_ready[i], 128);
+      mbar_init(&acc_empty[i], QA_WG_THREADS);
+      mbar_init(&qkv_ready[i], QA_WG_THREADS);
       mbar_init(&s_full[i], 1);
-      mbar_init(&p_ready[i], 128);
+      mbar_init(&p_ready[i], QA_WG_THREADS);
       mbar_init(&o_full[i], 1);
-      mbar_init(&wg_bar[i], 128);
+      mbar_init(&wg_bar[i], QA_WG_THREADS);
     }
+    for (int i = 0; i < 24; ++i) mbar_init(&pair_bar[i], 64);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -248,15 +254,22 @@ qkv_attn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       }
     }
   } else {
-    // ------------------------------------------------------------------ work groups: one thread per row
-    const int set = (warp - 4) >> 2;
-    const int quad = warp & 3;
-    const int r = quad * 32 + lane;  // row of the tile == TMEM lane == token of the sequence
+    // ------------------------------------------------------------------ work groups: two threads per row
+    const int wgw = warp - 4;          // 0 .. 15
+    const int set = wgw >> 3;
+    const int half = (wgw >> 2) & 1;   // which half of the row's columns / keys this thread handles
+    const int quad = warp & 3;         // TMEM lane quadrant (== wgw & 3)
+    const int r = quad * 32 + lane;    // row of the tile == TMEM lane == token of the sequence
     const uint32_t lane_sel = uint32_t(quad * 32) << 16;
     const uint32_t region = tmem_base + lane_sel + uint32_t(set * QA_BN);
     uint8_t* sQ = sets + size_t(set) * QA_SET_BYTES;
     uint8_t* sK = sQ + QA_TILE_BYTES;
-    const int gt = int(threadIdx.x) - 128 - set * 128;  // 0 .. 127 within the work group
+    float* s_scale = col_rows + set * 2 * QA_BN;
+    float* s_bias = s_scale + QA_BN;
+    float* x_max = xch + set * 5 * 128;  // [2 halves][128]
+    float* x_sum = x_max + 2 * 128;      // [3][128]: half 0's two chunks added, half 1's chunk 2, half 1's chunk 3
+    uint64_t* my_pair = pair_bar + (set * 4 + quad) * 3;
+    const int gt = int(threadIdx.x) - 128 - set * QA_WG_THREADS;  // 0 .. 255 within the work group
     const float inv_o_scale = p.ctxq ? ZEN_DIV(1.0f, p.ctx_scale) : 1.0f;
     const float2 xs2 = make_float2(p.x_scale, p.x_scale);
     uint32_t it = 0;
@@ -266,99 +279,93 @@ qkv_attn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       int kv_len = p.kv_lens ? p.kv_lens[b] : p.S;
       kv_len = kv_len < 0 ? 0 : (kv_len > p.S ? p.S : kv_len);
       const int k_cols = ((kv_len + 15) / 16) * 16;
-      // Per-column scale and bias of this head's 192 columns (thread gt: columns gt and, below 64, gt + 128), in
-      // the rows of this item's parity: the rows of the other parity may still be read by slower threads.
-      float* s_scale = col_rows + (set * 2 + int(it & 1u)) * 2 * QA_BN;
-      float* s_bias = s_scale + QA_BN;
+      // Per-column scale and bias of this head's 192 columns (thread gt < 192: column gt).  The rows can be
+      // rewritten at once: no thread is still reading the previous item's (its Q K^T product needed every
+      // thread's arrival after the projection epilogue, and this thread has waited for that product).
       {
-        float sv0 = 1.0f, bv0 = 0.0f, sv1 = 1.0f, bv1 = 0.0f;
-        const int c0 = (gt >> 6) * hidden + h * 64 + (gt & 63);  // gt < 128: Q (gt < 64) or K columns
-        const int c1 = 2 * hidden + h * 64 + gt;                 // V columns for gt < 64
-        if (p.w_scale != nullptr) sv0 = __ldg(p.w_scale + c0);
-        if (p.bias != nullptr) bv0 = __ldg(p.bias + c0);
-        if (gt < 64) {
-          if (p.w_scale != nullptr) sv1 = __ldg(p.w_scale + c1);
-          if (p.bias != nullptr) bv1 = __ldg(p.bias + c1);
+        if (gt < QA_BN) {
+          const int c = (gt >> 6) * hidden + h * 64 + (gt & 63);
+          s_scale[gt] = p.w_scale != nullptr ? __ldg(p.w_scale + c) : 1.0f;
+          s_bias[gt] = p.bias != nullptr ? __ldg(p.bias + c) : 0.0f;
         }
-        s_scale[gt] = sv0;
-        s_bias[gt] = bv0;
-        if (gt < 64) {
-          s_scale[128 + gt] = sv1;
-          s_bias[128 + gt] = bv1;
-        }
+        // the previous item of this set: its stores (issued by lane 0 of the half-0 warps) have finished reading
+        // the staging rows of the Q / K tiles before any thread of the group writes Q / K / P rows again
+        if (half == 0 && lane == 0) tma_store_wait_read();
         mbar_arrive(&wg_bar[set]);
-        // the previous item of this set: its stores have finished reading this warp's rows of the Q / K tiles,
-        // which only this warp writes again (Q / K / P rows and the staging blocks are all its own 32 rows)
-        if (lane == 0) tma_store_wait_read();
-        __syncwarp();
         if (!mbar_wait(&wg_bar[set], it & 1u, abort_flag)) break;
       }
-      // ---- projection epilogue: 192 accumulators of this row -> fp16 Q, K, V rows in shared memory
+      // ---- projection epilogue: this thread's 96 of the row's 192 accumulators -> fp16 Q, K, V in shared memory
       if (!mbar_wait(&acc_full[set], it & 1u, abort_flag)) break;
       tc_fence_after_sync();
-      // one step per tile (Q, K, V): 64 accumulator columns in one tensor-memory load, so that the load latency is
-      // paid three times per row instead of twelve and the 32 column pairs of a step overlap one another
 #pragma unroll 1
-      for (int t = 0; t < 3; ++t) {
-        uint32_t a[64];
+      for (int k = 0; k < 6; ++k) {
+        const int i = half * 6 + k;  // 16-column step of the row: tile i / 4 (Q, K, V), units 2 (i % 4) and + 1
+        uint32_t a[16];
         __syncwarp();
-        tmem_ld_32x64(region + uint32_t(t * 64), a);
+        tmem_ld_32x16(region + uint32_t(i * 16), a);
         tmem_wait_ld();
-        uint8_t* trow = sQ + t * QA_TILE_BYTES + r * 128;
-        __half* grow = (p.qkv_out != nullptr && r < p.S)
-                           ? p.qkv_out + (size_t(b) * p.S + r) * (3 * hidden) + t * hidden + h * 64
-                           : nullptr;
+        uint32_t w[8];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {  // 16-byte unit u of the row: columns 8 u .. 8 u + 7
-          uint32_t w[4];
+        for (int j4 = 0; j4 < 4; ++j4) {
+          const float4 s4 = reinterpret_cast<const float4*>(s_scale + i * 16)[j4];
+          const float4 b4 = reinterpret_cast<const float4*>(s_bias + i * 16)[j4];
 #pragma unroll
-          for (int j2 = 0; j2 < 2; ++j2) {
-            const float4 s4 = reinterpret_cast<const float4*>(s_scale + t * 64 + u * 8)[j2];
-            const float4 b4 = reinterpret_cast<const float4*>(s_bias + t * 64 + u * 8)[j2];
-#pragma unroll
-            for (int hh = 0; hh < 2; ++hh) {
-              // zen_det_dequant on a column pair: each product rounded before the bias is added
-              const int e = u * 8 + 4 * j2 + 2 * hh;
-              const float2 v = f2mul_then_add(f2mul(make_float2(float(int32_t(a[e])), float(int32_t(a[e + 1]))), xs2), hh ? make_float2(s4.z, s4.w) : make_float2(s4.x, s4.y),
-                                              hh ? make_float2(b4.z, b4.w) : make_float2(b4.x, b4.y));
-              const __half2 hv = __floats2half2_rn(v.x, v.y);
-              w[2 * j2 + hh] = *reinterpret_cast<const uint32_t*>(&hv);
-            }
+          for (int hh = 0; hh < 2; ++hh) {
+            const int e = 4 * j4 + 2 * hh;
+            const float2 av = make_float2(float(int32_t(a[e])), float(int32_t(a[e + 1])));
+            // zen_det_dequant on a column pair: each product rounded before the bias is added
+            const float2 v = f2mul_then_add(f2mul(av, xs2), hh ? make_float2(s4.z, s4.w) : make_float2(s4.x, s4.y),
+                                            hh ? make_float2(b4.z, b4.w) : make_float2(b4.x, b4.y));
+            const __half2 hv = __floats2half2_rn(v.x, v.y);
+            w[e >> 1] = *reinterpret_cast<const uint32_t*>(&hv);
           }
-          *reinterpret_cast<uint4*>(trow + ((u ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);  // 128-byte swizzle
-          if (grow != nullptr) reinterpret_cast<uint4*>(grow)[u] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+        uint8_t* trow = sQ + (i >> 2) * QA_TILE_BYTES + r * 128;  // 128-byte swizzle
+        *reinterpret_cast<uint4*>(trow + (((2 * (i & 3)) ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        *reinterpret_cast<uint4*>(trow + (((2 * (i & 3) + 1) ^ (r & 7)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
+        if (p.qkv_out != nullptr && r < p.S) {
+          uint4* dst = reinterpret_cast<uint4*>(p.qkv_out + (size_t(b) * p.S + r) * (3 * hidden) + (i >> 2) * hidden + h * 64 +
+                                                (i & 3) * 16);
+          dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+          dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
         }
       }
       tc_fence_before_sync();
       fence_proxy_async_smem();
       mbar_arrive(&qkv_ready[set]);
 
-      // ---- softmax of this row (the arithmetic of flash_attn_kernel)
+      // ---- softmax (the arithmetic of flash_attn_kernel): this thread's 64 of the row's 128 keys
       if (!mbar_wait(&s_full[set], it & 1u, abort_flag)) break;
       tc_fence_after_sync();
       const int lim = kv_len;
-      float l_sum = 0.f;
       float mx = -INFINITY;
 #pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
-        const int rem = lim - c * 64;
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = 2 * half + cc;
+        const int rem = lim - c * 32;
         if (rem <= 0) break;  // uniform: the key length is the same for every row of the sequence
-        uint32_t sv[64];
+        uint32_t sv[32];
         __syncwarp();
-        tmem_ld_32x64(region + uint32_t(c * 64), sv);
+        tmem_ld_32x32(region + uint32_t(c * 32), sv);
         tmem_wait_ld();
-        if (rem >= 64) {
+        if (rem >= 32) {
 #pragma unroll
-          for (int i = 0; i < 64; ++i) mx = fmaxf(mx, __uint_as_float(sv[i]));
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sv[i]));
         } else {
 #pragma unroll
-          for (int i = 0; i < 64; ++i)
+          for (int i = 0; i < 32; ++i)
             if (i < rem) mx = fmaxf(mx, __uint_as_float(sv[i]));
         }
       }
+      x_max[half * 128 + r] = mx;
+      mbar_arrive(&my_pair[0]);
+      if (!mbar_wait(&my_pair[0], it & 1u, abort_flag)) break;
+      mx = fmaxf(mx, x_max[(half ^ 1) * 128 + r]);  // the row maximum over all valid keys, as one thread would find it
       const float m_use = mx == -INFINITY ? 0.f : mx * p.scale_log2;
+      float csum[2] = {0.f, 0.f};  // this thread's two 32-key chunks
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = 2 * half + cc;
         if (c * 32 >= k_cols) break;
         const int rem = lim - c * 32;
         uint32_t pk[16];
@@ -392,7 +399,7 @@ qkv_attn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
               pk[i] = *reinterpret_cast<const uint32_t*>(&hv);
             }
           }
-          l_sum += rs0 + rs1;
+          csum[cc] = rs0 + rs1;
         }
         // P[row, 32 keys of chunk c]: the Q tile holds keys 0..63, the K tile keys 64..127 (both dead by now)
         uint8_t* prow = sQ + (c >> 1) * QA_TILE_BYTES + r * 128;
@@ -402,68 +409,83 @@ qkv_attn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           *reinterpret_cast<uint4*>(prow + unit * 16) = make_uint4(pk[4 * u], pk[4 * u + 1], pk[4 * u + 2], pk[4 * u + 3]);
         }
       }
+      // The row sum in the order one thread would add it, ((c0 + c1) + c2) + c3: half 0 publishes c0 + c1, half 1
+      // its two chunks separately (a chunk without valid keys is 0; adding 0 changes nothing).
+      if (half == 0) {
+        x_sum[r] = csum[0] + csum[1];
+      } else {
+        x_sum[128 + r] = csum[0];
+        x_sum[256 + r] = csum[1];
+      }
       tc_fence_before_sync();
       fence_proxy_async_smem();
       mbar_arrive(&p_ready[set]);
+      mbar_arrive(&my_pair[1]);
 
-      // ---- output: O / rowsum -> fp16 (+ int8 copy), staged in this warp's own rows of the Q / K tiles
+      // ---- output: O / rowsum -> fp16 (+ int8 copy) for this thread's 32 of the 64 columns, staged in the rows of
+      //      the Q / K tiles that belong to this pair of warps
       if (!mbar_wait(&o_full[set], it & 1u, abort_flag)) break;
       tc_fence_after_sync();
+      if (!mbar_wait(&my_pair[1], it & 1u, abort_flag)) break;
+      const float l_sum = (x_sum[r] + x_sum[128 + r]) + x_sum[256 + r];
       const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
       uint8_t* sty = sQ + quad * 4096;  // 32 rows x 128 B, 128-byte swizzle
       uint8_t* stq = sK + quad * 4096;  // 32 rows x 64 B, 64-byte swizzle
-      {
-        uint32_t ov[64];
+#pragma unroll 1
+      for (int k = 0; k < 2; ++k) {
+        const int g = 2 * half + k;  // 16-column step of the output row
+        uint32_t ov[16];
         if (kv_len > 0) {
           __syncwarp();
-          tmem_ld_32x64(region + 128u, ov);
+          tmem_ld_32x16(region + 128u + uint32_t(g * 16), ov);
           tmem_wait_ld();
         } else {
 #pragma unroll
-          for (int i = 0; i < 64; ++i) ov[i] = 0u;  // a sequence without keys yields zeros
+          for (int i = 0; i < 16; ++i) ov[i] = 0u;  // a sequence without keys yields zeros
+        }
+        uint32_t w[8];
+        float2 val[8];  // the fp16 values that are stored: the int8 copy quantizes these
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const __half2 hv = __floats2half2_rn(__uint_as_float(ov[2 * i]) * inv, __uint_as_float(ov[2 * i + 1]) * inv);
+          w[i] = *reinterpret_cast<const uint32_t*>(&hv);
+          val[i] = __half22float2(hv);
         }
         uint8_t* srow = sty + lane * 128;
+        *reinterpret_cast<uint4*>(srow + (((2 * g) ^ (lane & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        *reinterpret_cast<uint4*>(srow + (((2 * g + 1) ^ (lane & 7)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
+        if (p.ctxq) {
+          uint32_t qw[4];
+          const uint32_t risky = quantize_pairs_rn<16>(val, inv_o_scale, qw);
+          if (risky) {
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          uint32_t w[8];
-          float2 val[8];  // the fp16 values that are stored: the int8 copy quantizes these
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const __half2 hv = __floats2half2_rn(__uint_as_float(ov[16 * g + 2 * i]) * inv, __uint_as_float(ov[16 * g + 2 * i + 1]) * inv);
-            w[i] = *reinterpret_cast<const uint32_t*>(&hv);
-            val[i] = __half22float2(hv);
+            for (int e = 0; e < 16; ++e)
+              if (risky & (1u << e))
+                patch_q_byte(qw, e, zen_det_round_clamp_i8(ZEN_DIV((e & 1) ? val[e >> 1].y : val[e >> 1].x, p.ctx_scale), 0));
           }
-          *reinterpret_cast<uint4*>(srow + (((2 * g) ^ (lane & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-          *reinterpret_cast<uint4*>(srow + (((2 * g + 1) ^ (lane & 7)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
-          if (p.ctxq) {
-            uint32_t qw[4];
-            const uint32_t risky = quantize_pairs_rn<16>(val, inv_o_scale, qw);
-            if (risky) {
-#pragma unroll
-              for (int e = 0; e < 16; ++e)
-                if (risky & (1u << e))
-                  patch_q_byte(qw, e, zen_det_round_clamp_i8(ZEN_DIV((e & 1) ? val[e >> 1].y : val[e >> 1].x, p.ctx_scale), 0));
-            }
-            *reinterpret_cast<uint4*>(stq + lane * 64 + ((g ^ ((lane >> 1) & 3)) << 4)) = make_uint4(qw[0], qw[1], qw[2], qw[3]);
-          }
+          *reinterpret_cast<uint4*>(stq + lane * 64 + ((g ^ ((lane >> 1) & 3)) << 4)) = make_uint4(qw[0], qw[1], qw[2], qw[3]);
         }
       }
       tc_fence_before_sync();
       mbar_arrive(&acc_empty[set]);  // the set's TMEM columns may receive the next projection
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0 && quad * 32 < p.S) {
-        int c[4];
-        c[0] = 0;
-        c[p.o_perm[0]] = quad * 32;
-        c[p.o_perm[1]] = h;
-        c[p.o_perm[2]] = b;
-        tma_store_4d(&tmap_o, sty, 0, c[1], c[2], c[3]);
-        if (p.ctxq) tma_store_4d(&tmap_oq, stq, 0, c[1], c[2], c[3]);
-        tma_store_commit();
+      fence_proxy_async_smem();      // this thread's staged bytes -> visible to the TMA engine
+      mbar_arrive(&my_pair[2]);
+      if (half == 0) {
+        // both warps of the pair have staged their halves of the 32 rows
+        if (!mbar_wait(&my_pair[2], it & 1u, abort_flag)) break;
+        if (lane == 0 && quad * 32 < p.S) {
+          int c[4];
+          c[0] = 0;
+          c[p.o_perm[0]] = quad * 32;
+          c[p.o_perm[1]] = h;
+          c[p.o_perm[2]] = b;
+          tma_store_4d(&tmap_o, sty, 0, c[1], c[2], c[3]);
+          if (p.ctxq) tma_store_4d(&tmap_oq, stq, 0, c[1], c[2], c[3]);
+          tma_store_commit();
+        }
       }
     }
-    if (lane == 0) tma_store_wait_all();
+    if (half == 0 && lane == 0) tma_store_wait_all();
   }
 
   tc_fence_before_sync();
