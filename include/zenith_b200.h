@@ -238,6 +238,18 @@ int zen_quantize_f32(const float* x, int8_t* q, int64_t n, float scale, int zero
 int zen_quantize_f16(const void* x, int8_t* q, int64_t n, float scale, int zero_point, int round_mode, void* stream);
 int zen_dequantize_f32(const int8_t* q, float* x, int64_t n, float scale, int zero_point, void* stream);
 
+/* FP8 (e4m3) linear: out = act((float(xq . wq^T) * x_scale) * w_scale[n] + bias[n]) with xq [M,K], wq [N,K] holding
+ * e4m3 bit patterns (x / x_scale and w / w_scale[n] rounded to e4m3), products accumulated in fp32 on the tensor
+ * cores (tcgen05 kind::f8f6f4); out fp32 or fp16.  A tolerance path like the fp16 GEMM: the accumulation order of
+ * the hardware is not specified.  K, ldx, ldw multiples of 16.  flags: ZEN_GEMM_CONST_WEIGHTS, ZEN_GEMM_TILE_N.
+ * zen_quantize_e4m3_*: q = e4m3(x / scale), round to nearest even, saturating at +-448.
+ * The reference has no FP8 kernel; its roadmap sketches one (docs/SPEEDUP_ROADMAP.md:201-210). */
+int zen_linear_f8(const uint8_t* xq, int64_t ldx, const uint8_t* wq, int64_t ldw, int M, int N, int K, float x_scale,
+                  const float* w_scale, const float* bias, int act, int out_dtype, void* out, int64_t ldo, unsigned flags,
+                  void* stream);
+int zen_quantize_e4m3_f32(const float* x, uint8_t* q, int64_t n, float scale, void* stream);
+int zen_quantize_e4m3_f16(const void* x, uint8_t* q, int64_t n, float scale, void* stream);
+
 /* Attention forward, O = softmax(scale * Q K^T  [masked]) V, fp16 in / fp16 out, fp32 softmax.
  * Element (b,h,s,d) of Q sits at q + b*q_sb + h*q_sh + s*q_ss + d (strides in elements, d
  * contiguous; strides multiples of 8) and likewise for K, V, O.  kv_lens[b] (NULL = S for all)
@@ -266,6 +278,35 @@ int zen_qkv_attention_i8(const int8_t* xq, int64_t ldx, const int8_t* wqkv, int6
                          float x_scale, const float* w_scale, const float* bias, const int32_t* kv_lens, float scale,
                          void* ctx, int8_t* ctxq, float ctx_scale, void* qkv_out, const void* next0, size_t next0_bytes,
                          const void* next1, size_t next1_bytes, unsigned flags, void* stream);
+
+/* Unpadded batches.  The reference's encoder drivers pad every sequence to the batch's length and spend GEMM work
+ * on the padding (benchmarks/bert_hybrid.py:88-120 reshapes [B, S, H] to [B * S, H] for every projection).  Here the
+ * valid tokens are packed back to back, sequence b in rows cu_seqlens[b] .. cu_seqlens[b + 1] - 1, every row-wise
+ * kernel and GEMM runs on the packed rows as it is, and attention takes its sequences from the offsets.
+ *
+ * zen_pack_tokens_i32: from padded ids [B, S] (+ optional type ids) and key lengths kv_lens[B] (clamped to [0, S]) to
+ *   cu_seqlens[B + 1], ids_packed / pos_packed / type_packed (may be NULL) of `capacity` rows: a sequence's valid
+ *   tokens with their positions; rows between the total and the capacity get id 0, position 0 (defined values:
+ *   their results are never read).  Rows that would not fit the capacity are dropped.
+ * zen_embed_layernorm_unpadded_f16: zen_embed_layernorm_f16 with the position of each row read from pos_packed.
+ * zen_qkv_attention_unpadded_i8: zen_qkv_attention_i8 on `rows` packed rows; sequences of at most 128 tokens (a
+ *   longer one is cut to its first 128 keys and ZEN_ERR_UNSUPPORTED is recorded in the device status word).  Every
+ *   valid row's result equals, bit for bit, the padded call's result for that token.
+ * zen_unpad_rows_f16: padded[b * S + s] = packed[cu_seqlens[b] + s] for valid positions, zeros for padding.
+ * No counterpart in the reference (its roadmap lists variable-length batching as future work). */
+int zen_pack_tokens_i32(const int32_t* ids, const int32_t* type_ids, const int32_t* kv_lens, int B, int S, int capacity,
+                        int32_t* cu_seqlens, int32_t* ids_packed, int32_t* pos_packed, int32_t* type_packed, void* stream);
+int zen_embed_layernorm_unpadded_f16(const int32_t* ids_packed, const int32_t* pos_packed, const int32_t* type_packed,
+                                     const void* word, const void* pos, const void* type, const void* gamma,
+                                     const void* beta, void* y, int8_t* yq, float out_scale, int round_mode, int rows,
+                                     int max_pos, int hidden, int vocab, float eps, void* stream);
+int zen_qkv_attention_unpadded_i8(const int8_t* xq, int64_t ldx, const int8_t* wqkv, int64_t ldw, int B, int64_t rows,
+                                  const int32_t* cu_seqlens, int heads, int K, float x_scale, const float* w_scale,
+                                  const float* bias, float scale, void* ctx, int8_t* ctxq, float ctx_scale, void* qkv_out,
+                                  const void* next0, size_t next0_bytes, const void* next1, size_t next1_bytes,
+                                  unsigned flags, void* stream);
+int zen_unpad_rows_f16(const void* packed, const int32_t* cu_seqlens, int B, int S, int hidden, int capacity, void* padded,
+                       void* stream);
 
 /* f32 <-> f16 converts (core/src/fp16_kernels.cu:53-77). */
 int zen_convert_f32_to_f16(const float* x, void* y, int64_t n, void* stream);

@@ -189,3 +189,61 @@ def ref_matmul_avx2(a, b):
     c = np.empty((M, N), np.float32)
     lib.ref_matmul_f32_avx2(_p(a), _p(b), _p(c), M, N, K)
     return c
+
+
+# ---------------------------------------------------------------------------------------------
+# FP8 e4m3 (the OCP 8-bit format: 1 sign, 4 exponent (bias 7), 3 mantissa bits; no infinities, 0x7f / 0xff are NaN,
+# largest finite value 448).  The reference has no FP8 kernel (docs/SPEEDUP_ROADMAP.md:201-210 sketches one), so this
+# is the format's published definition restated: "parity unpinned" for this operator.
+# ---------------------------------------------------------------------------------------------
+def _e4m3_table():
+    codes = np.arange(128, dtype=np.int64)
+    e, m = codes >> 3, codes & 7
+    v = np.where(e == 0, m / 8.0 * 2.0 ** -6, (1.0 + m / 8.0) * 2.0 ** (e - 7.0))
+    v[127] = np.nan
+    return v
+
+
+_E4M3 = _e4m3_table()
+
+
+def e4m3_decode(bits):
+    """float32 values of e4m3 bit patterns (uint8)."""
+    b = np.asarray(bits, np.uint8)
+    v = _E4M3[b & 0x7f]
+    return np.where(b & 0x80, -v, v).astype(np.float32)
+
+
+def e4m3_encode(x):
+    """e4m3 bit patterns of float32 values: round to nearest, ties to the even code, saturating at +-448."""
+    x = np.asarray(x, np.float32)
+    a = np.minimum(np.abs(x.astype(np.float64)), 448.0)
+    grid = _E4M3[:127]
+    hi = np.clip(np.searchsorted(grid, a, side="left"), 0, 126)
+    lo = np.maximum(hi - 1, 0)
+    d_lo, d_hi = a - grid[lo], grid[hi] - a
+    code = np.where(d_lo < d_hi, lo, np.where(d_hi < d_lo, hi, np.where(lo % 2 == 0, lo, hi)))
+    code = np.where(grid[hi] == a, hi, code)
+    code = np.where(np.isnan(x), 127, code).astype(np.uint8)
+    return (code | np.where(np.signbit(x), 0x80, 0).astype(np.uint8)).astype(np.uint8)
+
+
+def quantize_e4m3(x, scale):
+    """e4m3(x / scale) with the division in float32."""
+    return e4m3_encode(np.asarray(x, np.float32) / np.float32(scale))
+
+
+def linear_fp8(xq, wq, x_scale, w_scale=None, bias=None, act="none"):
+    """``act((xq . wq^T) * x_scale * w_scale + bias)`` for e4m3 operands, products summed in float64 (exact for any
+    K of interest), scaled in float32 in the order of the int8 epilogue."""
+    acc = (e4m3_decode(xq).astype(np.float64) @ e4m3_decode(wq).astype(np.float64).T).astype(np.float32)
+    y = acc * np.float32(x_scale)
+    if w_scale is not None:
+        y = y * np.asarray(w_scale, np.float32)[None, :]
+    if bias is not None:
+        y = y + np.asarray(bias, np.float32)[None, :]
+    if act == "gelu":
+        y = gelu(y)
+    elif act == "relu":
+        y = np.maximum(y, 0)
+    return y.astype(np.float32)

@@ -156,3 +156,21 @@ def test_oracle_reproduces_the_reference_benchmark_pipeline_on_config1():
     assert sha(qx) == cfg1["bench_qx_sha256"] and sha(qw) == cfg1["bench_qw_sha256"]
     y = O.epilogue(O.gemm_s8(qx, qw), sx, np.full(3072, sw, np.float32), None, "none")
     assert sha(y) == cfg1["bench_y_sha256"]
+
+
+def test_e4m3_restatement_matches_an_independent_conversion():
+    """The oracle's e4m3 encode / decode against torch's float8_e4m3fn conversion on the CPU: all 256 codes, and
+    a million values across the format's range (ties, subnormals, saturation)."""
+    import torch
+    bits = np.arange(256, dtype=np.uint8)
+    t = torch.from_numpy(bits).view(torch.float8_e4m3fn).float().numpy()
+    d = O.e4m3_decode(bits)
+    assert np.array_equal(np.isnan(t), np.isnan(d)) and np.array_equal(t[~np.isnan(t)], d[~np.isnan(d)])
+    r = np.random.default_rng(0)
+    x = np.concatenate([r.standard_normal(200000).astype(np.float32) * np.float32(s) for s in (1e-3, 0.05, 1, 30, 300)] +
+                       [np.array([0, -0.0, 448, 449, 464, 465, 480, 1e9, -1e9, 2**-9, 2**-10, 1.5 * 2**-9, 3 * 2**-10], np.float32)])
+    want = torch.from_numpy(x).clamp(-448, 448).to(torch.float8_e4m3fn).view(torch.uint8).numpy()
+    assert np.array_equal(O.e4m3_encode(x), want)
+    # decode(encode(v)) == v for every finite code
+    finite = ~np.isnan(d)
+    assert np.array_equal(O.e4m3_encode(d[finite]), bits[finite])

@@ -1,0 +1,153 @@
+"""Unpadded batches: the valid tokens of a padded batch packed back to back.
+
+Packing / unpacking are index work (exact).  The packed QKV + attention kernel and the packed W8A8 encoder must give,
+for every valid token, the bits of the padded path (which the other suites pin to the CPU oracle); the attention
+output is also checked against the oracle directly."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as O
+from zenith_b200 import _capi, ops
+from zenith_b200.calibrate import calibrate
+from zenith_b200.encoder import EncoderConfig, Int8Encoder, init_params
+
+pytestmark = pytest.mark.gpu
+
+
+def rng(seed):
+    return np.random.default_rng(seed)
+
+
+def dev(a, cuda):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(cuda)
+
+
+def valid_rows(lens, S):
+    """Row indices of the padded [B * S] layout that hold valid tokens, in packed order."""
+    return np.concatenate([b * S + np.arange(min(max(int(n), 0), S)) for b, n in enumerate(lens)] + [np.zeros(0, np.int64)]).astype(np.int64)
+
+
+@pytest.mark.parametrize("B,S,lens,cap", [
+    (4, 16, [16, 3, 0, 9], 32), (1, 128, [128], 128), (3, 8, [0, 0, 0], 8), (5, 40, [40, 39, 16, 15, 1], 128),
+    (6, 10, [10, 12, -3, 4, 10, 7], 48), (3, 10, [10, 10, 10], 25)])
+def test_pack_tokens_and_unpad_rows(cuda, B, S, lens, cap):
+    ids = rng(B * S).integers(1, 30000, (B, S)).astype(np.int32)
+    types = rng(B).integers(0, 2, (B, S)).astype(np.int32)
+    cu, ids_p, pos_p, type_p = ops.pack_tokens(dev(ids, cuda), dev(np.array(lens, np.int32), cuda), cap, dev(types, cuda))
+    clamped = np.clip(np.array(lens), 0, S)
+    want_cu = np.concatenate([[0], np.cumsum(clamped)]).astype(np.int32)
+    assert np.array_equal(cu.cpu().numpy(), want_cu)
+    rows = valid_rows(lens, S)
+    want_ids = np.zeros(cap, np.int32)
+    want_pos = np.zeros(cap, np.int32)
+    want_type = np.zeros(cap, np.int32)
+    n = min(len(rows), cap)  # rows that do not fit the capacity are dropped
+    want_ids[:n] = ids.reshape(-1)[rows[:n]]
+    want_pos[:n] = (rows % S)[:n]
+    want_type[:n] = types.reshape(-1)[rows[:n]]
+    assert np.array_equal(ids_p.cpu().numpy(), want_ids)
+    assert np.array_equal(pos_p.cpu().numpy(), want_pos)
+    assert np.array_equal(type_p.cpu().numpy(), want_type)
+    # unpad: packed rows back to their padded positions, zeros elsewhere
+    packed = rng(7).standard_normal((cap, 64)).astype(np.float16)
+    got = ops.unpad_rows(dev(packed, cuda), cu, B, S).cpu().numpy()
+    want = np.zeros((B * S, 64), np.float16)
+    want[rows[:n]] = packed[:n]
+    assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
+
+
+@pytest.mark.parametrize("B,S,heads,K,lens", [
+    (2, 128, 2, 256, [128, 77]), (4, 128, 12, 768, [128, 100, 33, 0]), (5, 40, 3, 192, [40, 39, 16, 15, 0]),
+    (3, 96, 4, 256, [1, 96, 1]), (1, 128, 1, 128, [5]), (32, 128, 12, 768, "ragged")])
+def test_packed_attention_equals_padded_on_valid_rows(cuda, B, S, heads, K, lens):
+    H = heads * 64
+    if isinstance(lens, str):
+        lens = (S - rng(5).integers(0, 33, B)).tolist()
+    x = rng(B * S + K).integers(-128, 128, (B * S, K), dtype=np.int8)
+    w = rng(K).integers(-128, 128, (3 * H, K), dtype=np.int8)
+    ws = ((rng(3).random(3 * H) + 0.5) * (0.009 / np.sqrt(K))).astype(np.float32)
+    b = (rng(4).standard_normal(3 * H) * 0.1).astype(np.float32)
+    rows = valid_rows(lens, S)
+    total = len(rows)
+    cap = total + 3  # a few rows that belong to no sequence: they must stay untouched
+    xp = np.zeros((cap, K), np.int8)
+    xp[:total] = x[rows]
+    xp[total:] = 55
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    wd, wsd, bd = dev(w, cuda), dev(ws, cuda), dev(b, cuda)
+    ctx, ctxq, qkv = ops.qkv_attention_int8(dev(x, cuda), wd, 0.02, wsd, bd, B, S, heads, kv_lens=dev(np.array(lens, np.int32), cuda),
+                                            out_scale=0.02, emit_qkv=True)
+    pctx, pctxq, pqkv = ops.qkv_attention_unpadded_int8(dev(xp, cuda), wd, 0.02, wsd, bd, dev(cu, cuda), heads, out_scale=0.02,
+                                                        emit_qkv=True, constant_weights=True)
+    assert _capi.device_status() == 0
+    idx = torch.from_numpy(rows).to(cuda)
+    assert torch.equal(pqkv[:total], qkv[idx])
+    assert torch.equal(pctx[:total], ctx[idx])
+    assert torch.equal(pctxq[:total], ctxq[idx])
+    # rows outside every sequence: never written (the outputs started as zeros)
+    assert not pctx[total:].any() and not pctxq[total:].any() and not pqkv[total:].any()
+    if total * heads <= 4096 and total:
+        q3 = pqkv[:total].float().cpu().numpy()
+        for bi in range(B):
+            r0, r1 = cu[bi], cu[bi + 1]
+            if r1 == r0:
+                continue
+            for h in range(heads):
+                q, k, v = (q3[r0:r1, t * H + h * 64: t * H + (h + 1) * 64][None, None] for t in range(3))
+                want = O.attention(q, k, v)[0, 0]
+                got = pctx[r0:r1, h * 64:(h + 1) * 64].float().cpu().numpy()
+                assert np.max(np.abs(got - want)) <= 1e-2 * max(1.0, np.abs(want).max())
+
+
+def test_packed_attention_flags_a_sequence_longer_than_a_tile(cuda):
+    heads, K = 1, 64
+    x = dev(rng(1).integers(-128, 128, (200, K), dtype=np.int8), cuda)
+    w = dev(rng(2).integers(-128, 128, (192, K), dtype=np.int8), cuda)
+    cu = dev(np.array([0, 200], np.int32), cuda)
+    ops.qkv_attention_unpadded_int8(x, w, 0.02, None, None, cu, heads)
+    torch.cuda.synchronize()
+    try:
+        assert _capi.device_status() == 2  # ZEN_ERR_UNSUPPORTED
+    finally:
+        _capi.device_status(clear=True)
+    assert _capi.device_status() == 0
+
+
+CFG = EncoderConfig(layers=3, hidden=256, heads=4, ffn=512, vocab=2000, max_pos=128)
+
+
+@pytest.mark.parametrize("cfg,B,S", [(CFG, 5, 96), (EncoderConfig(layers=2, hidden=768, heads=12, ffn=3072, vocab=3000, max_pos=128), 8, 128)])
+def test_unpadded_encoder_equals_padded_on_valid_tokens(cuda, cfg, B, S):
+    params = init_params(cfg, 11, random_affine=True)
+    r = rng(21)
+    mk = lambda: (torch.from_numpy(r.integers(0, cfg.vocab, (B, S))).to(cuda),
+                  torch.from_numpy((S - r.integers(0, 33, B)).astype(np.int32)).to(cuda))
+    scales = calibrate(cfg, params, [mk() for _ in range(2)], cuda)
+    enc = Int8Encoder(cfg, params, scales, cuda)
+    ids, lens = mk()
+    padded = enc.forward(ids, lens).clone()
+    got = enc.forward_unpadded(ids, lens).clone()
+    assert _capi.device_status() == 0
+    cap = enc._packed_rows
+    assert cap == Int8Encoder.unpadded_capacity(lens.tolist(), S) and cap < B * S
+    rows = torch.from_numpy(valid_rows(lens.tolist(), S)).to(cuda)
+    assert torch.equal(got[rows], padded[rows])
+    mask = torch.ones(B * S, dtype=torch.bool, device=cuda)
+    mask[rows] = False
+    assert not got[mask].any()  # padding positions: zeros
+    assert torch.equal(enc.out[:len(rows)], padded[rows])  # the packed rows themselves
+    assert enc.launches_per_forward == 2 + cfg.layers * enc.launches_per_layer + 1
+    # one captured graph serves other batches that fit the capacity: shorter sequences, same bits as the padded pass
+    enc.capture_unpadded(B, S, cap)
+    for _ in range(2):
+        ids2, lens2 = mk()
+        lens2 = torch.clamp(lens2 - 7, min=0)
+        lens2[0] = 0
+        enc.set_inputs(ids2, lens2)
+        rep = enc.replay().clone()
+        ref = Int8Encoder(cfg, params, scales, cuda).forward(ids2, lens2)
+        rows2 = torch.from_numpy(valid_rows(lens2.tolist(), S)).to(cuda)
+        assert torch.equal(rep[rows2], ref[rows2])
+    # and the padded form is still there afterwards
+    assert torch.equal(enc.forward(ids, lens), padded)

@@ -74,6 +74,14 @@ SIGNATURES = {
     "zen_absmax_rows_f32": [_p, _i, _i, _i64, _p, _p],
     "zen_quantize_rows_f32": [_p, _p, _i, _i, _i64, _p, _i64, _i, _p],
     "zen_embed_layernorm_f16": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _f, _i, _i, _i, _i, _i, _f, _p],
+    "zen_linear_f8": [_p, _i64, _p, _i64, _i, _i, _i, _f, _p, _p, _i, _i, _p, _i64, _u, _p],
+    "zen_quantize_e4m3_f32": [_p, _p, _i64, _f, _p],
+    "zen_quantize_e4m3_f16": [_p, _p, _i64, _f, _p],
+    "zen_pack_tokens_i32": [_p, _p, _p, _i, _i, _i, _p, _p, _p, _p, _p],
+    "zen_embed_layernorm_unpadded_f16": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _f, _i, _i, _i, _i, _i, _f, _p],
+    "zen_qkv_attention_unpadded_i8": [_p, _i64, _p, _i64, _i, _i64, _p, _i, _i, _f, _p, _p, _f, _p, _p, _f, _p, _p,
+                                      C.c_size_t, _p, C.c_size_t, _u, _p],
+    "zen_unpad_rows_f16": [_p, _p, _i, _i, _i, _i, _p, _p],
 }
 _RESTYPES = {"zen_status_string": C.c_char_p, "zen_matmul_f32_workspace_bytes": C.c_size_t,
              "zen_minmax_workspace_bytes": C.c_size_t}

@@ -452,16 +452,20 @@ extern "C" int zen_flash_attention_f16(const void* q, const void* k, const void*
   return D == 64 ? launch_fa_pipe<64, 2>(tq, tk, tv, p, s) : launch_fa_pipe<128, 1>(tq, tk, tv, p, s);
 }
 
-extern "C" int zen_qkv_attention_i8(const int8_t* xq, int64_t ldx, const int8_t* wqkv, int64_t ldw, int B, int S, int heads,
-                                    int K, float x_scale, const float* w_scale, const float* bias,
-                                    const int32_t* kv_lens, float scale, void* ctx, int8_t* ctxq, float ctx_scale,
-                                    void* qkv_out, const void* next0, size_t next0_bytes, const void* next1,
-                                    size_t next1_bytes, unsigned flags, void* stream) {
-  if (!xq || !wqkv || !ctx || B <= 0 || S <= 0 || heads <= 0 || K <= 0) return ZEN_ERR_INVALID_ARG;
+// Shared body of the padded and the packed entry points.  Padded: S tokens per sequence, kv_lens optional.
+// Packed: `rows` valid tokens back to back, cu_seqlens[B + 1] on the device, sequences of at most 128 tokens.
+static int qkv_attention_launch(bool packed, const int8_t* xq, int64_t ldx, const int8_t* wqkv, int64_t ldw, int B, int S,
+                                int64_t rows, int heads, int K, float x_scale, const float* w_scale, const float* bias,
+                                const int32_t* kv_lens, const int32_t* cu_seqlens, float scale, void* ctx, int8_t* ctxq,
+                                float ctx_scale, void* qkv_out, const void* next0, size_t next0_bytes, const void* next1,
+                                size_t next1_bytes, unsigned flags, void* stream) {
+  if (!xq || !wqkv || !ctx || B <= 0 || S <= 0 || heads <= 0 || K <= 0 || rows <= 0) return ZEN_ERR_INVALID_ARG;
+  if (packed && !cu_seqlens) return ZEN_ERR_INVALID_ARG;
   if ((next0_bytes != 0 && !next0) || (next1_bytes != 0 && !next1)) return ZEN_ERR_INVALID_ARG;
   if (flags & ~unsigned(ZEN_GEMM_CONST_WEIGHTS)) return ZEN_ERR_INVALID_ARG;
   if (ctxq && !(ctx_scale > 0.f)) return ZEN_ERR_INVALID_ARG;
   if (S > 128 || B > 65535 || heads > 65535) return ZEN_ERR_UNSUPPORTED;  // longer sequences: zen_linear_i8 + zen_flash_attention_f16
+  if (rows >= (int64_t(1) << 31)) return ZEN_ERR_UNSUPPORTED;
   if (K % 16 || ldx % 16 || ldw % 16 || ldx < K || ldw < K) return ZEN_ERR_UNSUPPORTED;
   const int hidden = heads * 64;
   if (reinterpret_cast<uintptr_t>(ctx) % 16 || reinterpret_cast<uintptr_t>(ctxq) % 16 ||
@@ -471,6 +475,7 @@ extern "C" int zen_qkv_attention_i8(const int8_t* xq, int64_t ldx, const int8_t*
   p.B = B; p.S = S; p.heads = heads; p.K = K;
   p.num_k_blocks = (K + 127) / 128;
   p.x_scale = x_scale; p.w_scale = w_scale; p.bias = bias; p.kv_lens = kv_lens;
+  p.cu_seqlens = cu_seqlens; p.ctx = static_cast<__half*>(ctx);
   p.scale_log2 = scale * 1.4426950408889634f;
   p.ctxq = ctxq; p.ctx_scale = ctxq ? ctx_scale : 1.0f;
   p.qkv_out = static_cast<__half*>(qkv_out);
@@ -485,10 +490,15 @@ extern "C" int zen_qkv_attention_i8(const int8_t* xq, int64_t ldx, const int8_t*
       p.pf_bytes[i] = uint64_t(hi - lo);
     }
   }
-  // activations as (k, token of the sequence, sequence): rows beyond S read as zero, so a tile never holds a
-  // neighbouring sequence's tokens
   CUtensorMap ta, tb, to, toq;
-  {
+  if (packed) {
+    // activations as (k, row of the packed batch): a tile starts at any row; rows past the end read as zero
+    if (int st = encode_tmap_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, xq, uint64_t(K), uint64_t(rows), uint64_t(ldx), 128, 128);
+        st != ZEN_OK)
+      return st;
+  } else {
+    // activations as (k, token of the sequence, sequence): rows beyond S read as zero, so a tile never holds a
+    // neighbouring sequence's tokens
     const uint64_t dims[3] = {uint64_t(K), uint64_t(S), uint64_t(B)};
     const uint64_t str[2] = {uint64_t(ldx), uint64_t(ldx) * uint64_t(S)};
     const uint32_t box[3] = {128u, 128u, 1u};
@@ -497,18 +507,46 @@ extern "C" int zen_qkv_attention_i8(const int8_t* xq, int64_t ldx, const int8_t*
   if (int st = encode_tmap_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, wqkv, uint64_t(K), uint64_t(3) * hidden, uint64_t(ldw), 128, 64);
       st != ZEN_OK)
     return st;
-  // outputs: ctx[b * S + s, h * 64 + d] seen as (d, seq, head, batch), 32-row boxes (one per softmax warp)
-  int perm_q[3];
-  if (int st = encode_qkv_map(&to, ctx, B, heads, S, 64, int64_t(S) * hidden, 64, hidden, p.o_perm, 32u, 2); st != ZEN_OK)
-    return st;
-  toq = to;
-  if (ctxq)
-    if (int st = encode_qkv_map(&toq, ctxq, B, heads, S, 64, int64_t(S) * hidden, 64, hidden, perm_q, 32u, 1); st != ZEN_OK)
+  to = ta;  // the packed form stores without tensor maps
+  toq = ta;
+  if (!packed) {
+    // outputs: ctx[b * S + s, h * 64 + d] seen as (d, seq, head, batch), 32-row boxes (one per softmax warp)
+    int perm_q[3];
+    if (int st = encode_qkv_map(&to, ctx, B, heads, S, 64, int64_t(S) * hidden, 64, hidden, p.o_perm, 32u, 2); st != ZEN_OK)
       return st;
+    toq = to;
+    if (ctxq)
+      if (int st = encode_qkv_map(&toq, ctxq, B, heads, S, 64, int64_t(S) * hidden, 64, hidden, perm_q, 32u, 1); st != ZEN_OK)
+        return st;
+  }
   constexpr size_t smem = qkv_attn_smem_bytes();
-  if (int st = ensure_dynamic_smem(reinterpret_cast<const void*>(qkv_attn_kernel), smem); st != ZEN_OK) return st;
   const int items = B * heads;
   const int grid = items < num_sms() ? items : num_sms();
-  return launch_pdl(PDL_GEMM, qkv_attn_kernel, dim3(grid), dim3(QA_THREADS), smem, static_cast<cudaStream_t>(stream), ta, tb,
-                    to, toq, p);
+  if (packed) {
+    if (int st = ensure_dynamic_smem(reinterpret_cast<const void*>(qkv_attn_kernel<true>), smem); st != ZEN_OK) return st;
+    return launch_pdl(PDL_GEMM, qkv_attn_kernel<true>, dim3(grid), dim3(QA_THREADS), smem, static_cast<cudaStream_t>(stream), ta,
+                      tb, to, toq, p);
+  }
+  if (int st = ensure_dynamic_smem(reinterpret_cast<const void*>(qkv_attn_kernel<false>), smem); st != ZEN_OK) return st;
+  return launch_pdl(PDL_GEMM, qkv_attn_kernel<false>, dim3(grid), dim3(QA_THREADS), smem, static_cast<cudaStream_t>(stream), ta,
+                    tb, to, toq, p);
+}
+
+extern "C" int zen_qkv_attention_i8(const int8_t* xq, int64_t ldx, const int8_t* wqkv, int64_t ldw, int B, int S, int heads,
+                                    int K, float x_scale, const float* w_scale, const float* bias,
+                                    const int32_t* kv_lens, float scale, void* ctx, int8_t* ctxq, float ctx_scale,
+                                    void* qkv_out, const void* next0, size_t next0_bytes, const void* next1,
+                                    size_t next1_bytes, unsigned flags, void* stream) {
+  return qkv_attention_launch(false, xq, ldx, wqkv, ldw, B, S, int64_t(B) * S, heads, K, x_scale, w_scale, bias, kv_lens,
+                              nullptr, scale, ctx, ctxq, ctx_scale, qkv_out, next0, next0_bytes, next1, next1_bytes, flags,
+                              stream);
+}
+
+extern "C" int zen_qkv_attention_unpadded_i8(const int8_t* xq, int64_t ldx, const int8_t* wqkv, int64_t ldw, int B,
+                                             int64_t rows, const int32_t* cu_seqlens, int heads, int K, float x_scale,
+                                             const float* w_scale, const float* bias, float scale, void* ctx, int8_t* ctxq,
+                                             float ctx_scale, void* qkv_out, const void* next0, size_t next0_bytes,
+                                             const void* next1, size_t next1_bytes, unsigned flags, void* stream) {
+  return qkv_attention_launch(true, xq, ldx, wqkv, ldw, B, 128, rows, heads, K, x_scale, w_scale, bias, nullptr, cu_seqlens,
+                              scale, ctx, ctxq, ctx_scale, qkv_out, next0, next0_bytes, next1, next1_bytes, flags, stream);
 }

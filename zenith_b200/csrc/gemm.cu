@@ -112,7 +112,7 @@ static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const 
 
 template <int KIND>
 static CUtensorMapDataType tmap_dtype() {
-  return KIND == KIND_I8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+  return (KIND == KIND_I8 || KIND == KIND_F8) ? CU_TENSOR_MAP_DATA_TYPE_UINT8
          : KIND == KIND_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
                             : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
 }
@@ -325,6 +325,29 @@ int zen_linear_f16_ex(const void* x, int64_t ldx, const void* w, int64_t ldw, in
     case 128: return run_gemm<KIND_F16, 128, 5, false>(x, ldx, w, ldw, p, s);
     case 192: return run_gemm<KIND_F16, 192, 4, false>(x, ldx, w, ldw, p, s);
     default: return run_gemm<KIND_F16, 256, 3, false>(x, ldx, w, ldw, p, s);
+  }
+}
+
+int zen_linear_f8(const uint8_t* xq, int64_t ldx, const uint8_t* wq, int64_t ldw, int M, int N, int K, float x_scale,
+                  const float* w_scale, const float* bias, int act, int out_dtype, void* out, int64_t ldo, unsigned flags,
+                  void* stream) {
+  if (!xq || !wq || !out || M <= 0 || N <= 0 || K <= 0) return ZEN_ERR_INVALID_ARG;
+  if (!flags_ok(flags) || (flags & ZEN_GEMM_PAIR)) return ZEN_ERR_INVALID_ARG;
+  if ((out_dtype != ZEN_DT_F32 && out_dtype != ZEN_DT_F16) || act < ZEN_ACT_NONE || act > ZEN_ACT_RELU)
+    return ZEN_ERR_INVALID_ARG;
+  if (K % 16 || ldx % 16 || ldw % 16 || ldx < K || ldw < K || ldo < N) return ZEN_ERR_UNSUPPORTED;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K;
+  p.out = out; p.ldo = ldo; p.out_dtype = out_dtype; p.act = act;
+  p.x_scale = x_scale; p.out_scale = 1.0f; p.w_scale = w_scale; p.bias = bias;
+  p.early_b = (flags & ZEN_GEMM_CONST_WEIGHTS) ? 1 : 0;
+  static const int allowed[] = {64, 128, 192, 256};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (pick_bn(M, N, allowed, 4, flags)) {
+    case 64: return run_gemm<KIND_F8, 64, 7, false>(xq, ldx, wq, ldw, p, s);
+    case 128: return run_gemm<KIND_F8, 128, 5, false>(xq, ldx, wq, ldw, p, s);
+    case 192: return run_gemm<KIND_F8, 192, 4, false>(xq, ldx, wq, ldw, p, s);
+    default: return run_gemm<KIND_F8, 256, 3, false>(xq, ldx, wq, ldw, p, s);
   }
 }
 

@@ -22,7 +22,7 @@
 
 namespace zen {
 
-enum { KIND_I8 = 0, KIND_F16 = 1, KIND_TF32 = 2 };
+enum { KIND_I8 = 0, KIND_F16 = 1, KIND_TF32 = 2, KIND_F8 = 3 };  // F8: e4m3 operands, fp32 accumulation
 
 struct GemmParams {
   int M, N, K;
@@ -71,6 +71,10 @@ template <>
 struct GemmKind<KIND_TF32> {
   static constexpr int ELEM = 4;
 };
+template <>
+struct GemmKind<KIND_F8> {
+  static constexpr int ELEM = 1;
+};
 
 constexpr int GEMM_BM = 128;
 constexpr int GEMM_EPI_WARPS = 16;
@@ -93,6 +97,7 @@ template <int KIND>
 __device__ __forceinline__ void issue_mma(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
   if constexpr (KIND == KIND_I8) mma_i8_ss(d, a, b, idesc, acc);
   else if constexpr (KIND == KIND_F16) mma_f16_ss(d, a, b, idesc, acc);
+  else if constexpr (KIND == KIND_F8) mma_f8_ss(d, a, b, idesc, acc);
   else mma_tf32_ss(d, a, b, idesc, acc);
 }
 
@@ -208,6 +213,18 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[GEMM_CW], con
         for (int h = 0; h < 2; ++h) {
           const int j = 4 * j4 + 2 * h;
           const float2 a = make_float2(float(int32_t(r[j])), float(int32_t(r[j + 1])));
+          const float2 v = f2mul_then_add(f2mul(a, xs2), make_float2(ss[2 * h], ss[2 * h + 1]),
+                                          make_float2(bb[2 * h], bb[2 * h + 1]));
+          y[j] = v.x;
+          y[j + 1] = v.y;
+        }
+      } else if constexpr (KIND == KIND_F8) {
+        // operands were scaled into the e4m3 range: (acc * x_scale) * w_scale[n] + bias, as on the int8 path
+        const float2 xs2 = make_float2(p.x_scale, p.x_scale);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int j = 4 * j4 + 2 * h;
+          const float2 a = make_float2(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
           const float2 v = f2mul_then_add(f2mul(a, xs2), make_float2(ss[2 * h], ss[2 * h + 1]),
                                           make_float2(bb[2 * h], bb[2 * h + 1]));
           y[j] = v.x;
@@ -576,6 +593,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   constexpr uint32_t IDESC =
       KIND == KIND_I8 ? make_idesc(IDESC_C_S32, IDESC_S8, IDESC_S8, 0, B_MN ? 1 : 0, GEMM_BM, BN)
       : KIND == KIND_F16 ? make_idesc(IDESC_C_F32, IDESC_F16, IDESC_F16, 0, B_MN ? 1 : 0, GEMM_BM, BN)
+      : KIND == KIND_F8  ? make_idesc(IDESC_C_F32, IDESC_E4M3, IDESC_E4M3, 0, B_MN ? 1 : 0, GEMM_BM, BN)
                          : make_idesc(IDESC_C_F32, IDESC_TF32, IDESC_TF32, 0, B_MN ? 1 : 0, GEMM_BM, BN);
   static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "BN");
   static_assert(!B_MN || BN % BK == 0, "MN-major B is loaded in 128-byte wide boxes");

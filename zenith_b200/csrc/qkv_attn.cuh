@@ -23,6 +23,12 @@
 // between the sets, so two items are in flight per CTA besides the one whose operands are being loaded.
 //
 // Results are bit-identical to zen_linear_i8 (fp16 output) followed by zen_flash_attention_f16.
+//
+// PACKED form (unpadded batches): the valid tokens of all sequences lie back to back, sequence b in rows
+// cu_seqlens[b] .. cu_seqlens[b + 1] - 1.  The 128-row activation tile of an item starts at the sequence's first row
+// and runs on into its successors' rows (or past the end of the tensor, which reads as zero): those rows are keys
+// beyond the key length (masked as padding is) and queries whose outputs are never written, because the outputs go
+// from registers to global memory with a row guard instead of through box-shaped TMA stores.
 #pragma once
 #include "gemm_tc.cuh"
 
@@ -43,6 +49,8 @@ struct QkvAttnParams {
   const float* w_scale;  // [3 * heads * 64] or null
   const float* bias;     // [3 * heads * 64] or null
   const int32_t* kv_lens;
+  const int32_t* cu_seqlens;  // PACKED: [B + 1] row offsets; the key length of sequence b is their difference
+  __half* ctx;                // PACKED: output rows are written with plain stores (ld = heads * 64)
   float scale_log2;  // softmax scale * log2(e)
   int8_t* ctxq;      // int8 copy of the output (may be null)
   float ctx_scale;
@@ -66,6 +74,7 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
       : "memory");
 }
 
+template <bool PACKED>
 __global__ void __launch_bounds__(QA_THREADS, 1)
 qkv_attn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                 const __grid_constant__ CUtensorMap tmap_o, const __grid_constant__ CUtensorMap tmap_oq,
@@ -104,12 +113,20 @@ qkv_attn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   // items of this CTA: blockIdx.x + j * gridDim.x, j = 0 .. n_mine - 1; item -> (sequence, head), heads fastest,
   // so that neighbouring CTAs read the same activation rows at the same time
   const int n_mine = int(blockIdx.x) < items ? (items - 1 - int(blockIdx.x)) / int(gridDim.x) + 1 : 0;
+  // first row of sequence b in a packed batch; key length of sequence b (clamped to what one tile holds)
+  auto first_row = [&](int b) -> int { return PACKED ? p.cu_seqlens[b] : b * p.S; };
+  auto key_len = [&](int b) -> int {
+    const int n = PACKED ? p.cu_seqlens[b + 1] - p.cu_seqlens[b] : (p.kv_lens ? p.kv_lens[b] : p.S);
+    return n < 0 ? 0 : (n > p.S ? p.S : n);
+  };
 
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
-    tma_prefetch_desc(&tmap_o);
-    if (p.ctxq) tma_prefetch_desc(&tmap_oq);
+    if (!PACKED) {
+      tma_prefetch_desc(&tmap_o);
+      if (p.ctxq) tma_prefetch_desc(&tmap_oq);
+    }
     for (int i = 0; i < QA_STAGES; ++i) {
       mbar_init(&full_bar[i], 1);
       mbar_init(&empty_bar[i], 1);
@@ -164,17 +181,22 @@ qkv_attn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       for (int j = 0; j < n_mine && ok; ++j) {
         const int item = int(blockIdx.x) + j * int(gridDim.x);
         const int b = item / p.heads, h = item % p.heads;
+        const int row0 = PACKED ? first_row(b) : 0;
+        auto load_a = [&](uint8_t* dst, uint64_t* bar, int kb) {
+          if (PACKED) tma_load_2d(dst, &tmap_a, bar, kb * BK, row0);
+          else tma_load_3d(dst, &tmap_a, bar, kb * BK, 0, b);
+        };
         for (int kb = 0; kb < nkb; ++kb) {
           uint8_t* sa = smem + size_t(stage) * QA_STAGE_BYTES;
           if (j == 0 && kb < pre) {
-            tma_load_3d(sa, &tmap_a, &full_bar[stage], kb * BK, 0, b);
+            load_a(sa, &full_bar[stage], kb);
           } else {
             if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) {
               ok = false;
               break;
             }
             mbar_arrive_expect_tx(&full_bar[stage], QA_STAGE_BYTES);
-            tma_load_3d(sa, &tmap_a, &full_bar[stage], kb * BK, 0, b);
+            load_a(sa, &full_bar[stage], kb);
 #pragma unroll
             for (int t = 0; t < 3; ++t)
               tma_load_2d(sa + A_BYTES + t * (64 * 128), &tmap_b, &full_bar[stage], kb * BK, t * hidden + h * 64);
@@ -233,8 +255,7 @@ qkv_attn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       uint32_t it = 0;
       for (int j = set; j < n_mine; j += 2, ++it) {
         const int item = int(blockIdx.x) + j * int(gridDim.x);
-        int kv_len = p.kv_lens ? p.kv_lens[item / p.heads] : p.S;
-        kv_len = kv_len < 0 ? 0 : (kv_len > p.S ? p.S : kv_len);
+        const int kv_len = key_len(item / p.heads);
         const int k_cols = ((kv_len + 15) / 16) * 16;
         if (!mbar_wait(&qkv_ready[set], it & 1u, abort_flag)) break;
         tc_fence_after_sync();
@@ -276,8 +297,10 @@ qkv_attn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     for (int j = set; j < n_mine; j += 2, ++it) {
       const int item = int(blockIdx.x) + j * int(gridDim.x);
       const int b = item / p.heads, h = item % p.heads;
-      int kv_len = p.kv_lens ? p.kv_lens[b] : p.S;
-      kv_len = kv_len < 0 ? 0 : (kv_len > p.S ? p.S : kv_len);
+      const int kv_len = key_len(b);
+      if (PACKED && gt == 0 && p.cu_seqlens[b + 1] - p.cu_seqlens[b] > p.S) record_status(ZEN_ERR_UNSUPPORTED);  // longer than a tile
+      const int64_t grow = int64_t(first_row(b)) + r;  // this thread's row of the global tensors
+      const bool row_live = PACKED ? r < kv_len : r < p.S;
       const int k_cols = ((kv_len + 15) / 16) * 16;
       // Per-column scale and bias of this head's 192 columns (thread gt < 192: column gt).  The rows can be
       // rewritten at once: no thread is still reading the previous item's (its Q K^T product needed every
@@ -290,7 +313,7 @@ qkv_attn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         }
         // the previous item of this set: its stores (issued by lane 0 of the half-0 warps) have finished reading
         // the staging rows of the Q / K tiles before any thread of the group writes Q / K / P rows again
-        if (half == 0 && lane == 0) tma_store_wait_read();
+        if (!PACKED && half == 0 && lane == 0) tma_store_wait_read();
         mbar_arrive(&wg_bar[set]);
         if (!mbar_wait(&wg_bar[set], it & 1u, abort_flag)) break;
       }
@@ -323,9 +346,8 @@ qkv_attn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         uint8_t* trow = sQ + (i >> 2) * QA_TILE_BYTES + r * 128;  // 128-byte swizzle
         *reinterpret_cast<uint4*>(trow + (((2 * (i & 3)) ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
         *reinterpret_cast<uint4*>(trow + (((2 * (i & 3) + 1) ^ (r & 7)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
-        if (p.qkv_out != nullptr && r < p.S) {
-          uint4* dst = reinterpret_cast<uint4*>(p.qkv_out + (size_t(b) * p.S + r) * (3 * hidden) + (i >> 2) * hidden + h * 64 +
-                                                (i & 3) * 16);
+        if (p.qkv_out != nullptr && row_live) {
+          uint4* dst = reinterpret_cast<uint4*>(p.qkv_out + grow * (3 * hidden) + (i >> 2) * hidden + h * 64 + (i & 3) * 16);
           dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
           dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
         }
@@ -451,9 +473,17 @@ qkv_attn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           w[i] = *reinterpret_cast<const uint32_t*>(&hv);
           val[i] = __half22float2(hv);
         }
-        uint8_t* srow = sty + lane * 128;
-        *reinterpret_cast<uint4*>(srow + (((2 * g) ^ (lane & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-        *reinterpret_cast<uint4*>(srow + (((2 * g + 1) ^ (lane & 7)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
+        if (PACKED) {
+          if (row_live) {
+            uint4* dst = reinterpret_cast<uint4*>(p.ctx + grow * hidden + h * 64 + g * 16);
+            dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+            dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+          }
+        } else {
+          uint8_t* srow = sty + lane * 128;
+          *reinterpret_cast<uint4*>(srow + (((2 * g) ^ (lane & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+          *reinterpret_cast<uint4*>(srow + (((2 * g + 1) ^ (lane & 7)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
+        }
         if (p.ctxq) {
           uint32_t qw[4];
           const uint32_t risky = quantize_pairs_rn<16>(val, inv_o_scale, qw);
@@ -463,11 +493,16 @@ qkv_attn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
               if (risky & (1u << e))
                 patch_q_byte(qw, e, zen_det_round_clamp_i8(ZEN_DIV((e & 1) ? val[e >> 1].y : val[e >> 1].x, p.ctx_scale), 0));
           }
-          *reinterpret_cast<uint4*>(stq + lane * 64 + ((g ^ ((lane >> 1) & 3)) << 4)) = make_uint4(qw[0], qw[1], qw[2], qw[3]);
+          if (PACKED) {
+            if (row_live) *reinterpret_cast<uint4*>(p.ctxq + grow * hidden + h * 64 + g * 16) = make_uint4(qw[0], qw[1], qw[2], qw[3]);
+          } else {
+            *reinterpret_cast<uint4*>(stq + lane * 64 + ((g ^ ((lane >> 1) & 3)) << 4)) = make_uint4(qw[0], qw[1], qw[2], qw[3]);
+          }
         }
       }
       tc_fence_before_sync();
       mbar_arrive(&acc_empty[set]);  // the set's TMEM columns may receive the next projection
+      if (PACKED) continue;          // the rows went to global memory directly
       fence_proxy_async_smem();      // this thread's staged bytes -> visible to the TMA engine
       mbar_arrive(&my_pair[2]);
       if (half == 0) {
@@ -485,7 +520,7 @@ qkv_attn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         }
       }
     }
-    if (half == 0 && lane == 0) tma_store_wait_all();
+    if (!PACKED && half == 0 && lane == 0) tma_store_wait_all();
   }
 
   tc_fence_before_sync();

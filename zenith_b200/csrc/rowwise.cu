@@ -7,6 +7,7 @@
 #include "zen_common.cuh"
 #include "det_math.h"
 #include "tma_host.cuh"
+#include <cuda_fp8.h>
 #include <type_traits>
 
 namespace zen {
@@ -161,6 +162,7 @@ struct RowParams {
   // embedding source
   const int32_t* ids;
   const int32_t* type_ids;
+  const int32_t* pos_ids;  // position of each row in its sequence; null: row % seq
   const void* pos;
   const void* type;
   int seq, vocab;
@@ -184,7 +186,7 @@ __global__ void __launch_bounds__(ROW_WARPS * 32) ln_warp_kernel(const RowParams
     int id = p.ids[row];
     id = id < 0 ? 0 : (id >= p.vocab ? p.vocab - 1 : id);
     x += int64_t(id) * H;
-    pos = static_cast<const T*>(p.pos) + int64_t(row % p.seq) * H;
+    pos = static_cast<const T*>(p.pos) + int64_t(p.pos_ids ? min(max(p.pos_ids[row], 0), p.seq - 1) : row % p.seq) * H;
     const int tid = p.type_ids ? p.type_ids[row] : 0;
     typ = static_cast<const T*>(p.type) + int64_t(tid != 0 ? 1 : 0) * H;
   } else {
@@ -278,7 +280,7 @@ __global__ void __launch_bounds__(256) ln_block_kernel(const RowParams p) {
     int id = p.ids[row];
     id = id < 0 ? 0 : (id >= p.vocab ? p.vocab - 1 : id);
     x += int64_t(id) * H;
-    pos = static_cast<const T*>(p.pos) + int64_t(row % p.seq) * H;
+    pos = static_cast<const T*>(p.pos) + int64_t(p.pos_ids ? min(max(p.pos_ids[row], 0), p.seq - 1) : row % p.seq) * H;
     const int tid = p.type_ids ? p.type_ids[row] : 0;
     typ = static_cast<const T*>(p.type) + int64_t(tid != 0 ? 1 : 0) * H;
   } else {
@@ -357,7 +359,7 @@ static int launch_ln(const RowParams& p, cudaStream_t s) {
 // ------------------------------------------------------------------------------------------
 // elementwise
 // ------------------------------------------------------------------------------------------
-enum { EW_GELU = 0, EW_RELU = 1, EW_BIAS_GELU = 2, EW_QUANT = 3, EW_DEQUANT = 4, EW_CONVERT = 5, EW_TANH = 6 };
+enum { EW_GELU = 0, EW_RELU = 1, EW_BIAS_GELU = 2, EW_QUANT = 3, EW_DEQUANT = 4, EW_CONVERT = 5, EW_TANH = 6, EW_QUANT_F8 = 7 };
 
 struct EwParams {
   const void* x;
@@ -381,6 +383,8 @@ __device__ __forceinline__ TO ew_apply(TI xin, const EwParams& p, int64_t idx) {
     else if constexpr (OP == EW_TANH) return TO(zen_det_tanh(x));
     else if constexpr (OP == EW_BIAS_GELU) return TO(zen_det_gelu(ZEN_ADD(x, __ldg(p.bias + (idx % p.features)))));
     else if constexpr (OP == EW_QUANT) return TO(quantize_value(x, p.scale, p.zero_point, p.round_mode));
+    // e4m3 bits of x / scale: round to nearest even, saturate to +-448 (NaN stays NaN)
+    else if constexpr (OP == EW_QUANT_F8) return TO(__nv_cvt_float_to_fp8(ZEN_DIV(x, p.scale), __NV_SATFINITE, __NV_E4M3));
     else return TO(x);
   }
 }
@@ -439,6 +443,64 @@ static int launch_ew(const EwParams& p, cudaStream_t s) {
   return cudaGetLastError() == cudaSuccess ? ZEN_OK : ZEN_ERR_LAUNCH;
 }
 
+
+// ------------------------------------------------------------------------------------------
+// Unpadded batches: the valid tokens of a padded [B, S] batch packed back to back
+// ------------------------------------------------------------------------------------------
+// Block b < B: the offset of sequence b (sum of the clamped lengths before it), then its ids / positions / types.
+// Block B: the total, and defined values (id 0, position 0) for the rows between the total and the capacity.
+__global__ void __launch_bounds__(128) pack_tokens_kernel(const int32_t* __restrict__ ids, const int32_t* __restrict__ type_ids,
+                                                          const int32_t* __restrict__ kv_lens, int B, int S, int capacity,
+                                                          int32_t* __restrict__ cu_seqlens, int32_t* __restrict__ ids_packed,
+                                                          int32_t* __restrict__ pos_packed, int32_t* __restrict__ type_packed) {
+  __shared__ int red[4];
+  const int b = blockIdx.x;
+  int part = 0;
+  for (int i = threadIdx.x; i < b; i += blockDim.x) part += min(max(kv_lens[i], 0), S);
+  part = __reduce_add_sync(0xffffffffu, part);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = part;
+  __syncthreads();
+  const int start = red[0] + red[1] + red[2] + red[3];
+  if (b < B) {
+    const int len = min(max(kv_lens[b], 0), S);
+    if (threadIdx.x == 0) cu_seqlens[b] = start;
+    for (int s = threadIdx.x; s < len; s += blockDim.x) {
+      const int dst = start + s;
+      if (dst < capacity) {
+        ids_packed[dst] = ids[int64_t(b) * S + s];
+        pos_packed[dst] = s;
+        if (type_packed) type_packed[dst] = type_ids ? type_ids[int64_t(b) * S + s] : 0;
+      }
+    }
+  } else {
+    if (threadIdx.x == 0) cu_seqlens[B] = start;
+    for (int t = start + int(threadIdx.x); t < capacity; t += blockDim.x) {
+      ids_packed[t] = 0;
+      pos_packed[t] = 0;
+      if (type_packed) type_packed[t] = 0;
+    }
+  }
+}
+
+// One warp per padded row: its packed row, or zeros for a padding position.
+template <typename T>
+__global__ void __launch_bounds__(ROW_WARPS * 32) unpad_rows_kernel(const T* __restrict__ packed, const int32_t* __restrict__ cu_seqlens,
+                                                                   int B, int S, int hidden, int capacity, T* __restrict__ padded) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * ROW_WARPS + (threadIdx.x >> 5);
+  grid_launch_dependents();
+  grid_dependency_wait();
+  if (row >= B * S) return;
+  const int b = row / S, s = row - b * S;
+  const int start = cu_seqlens[b];
+  const int len = cu_seqlens[b + 1] - start;
+  const bool valid = s < len && start + s < capacity;
+  constexpr int N = 16 / int(sizeof(T));
+  const uint4* src = reinterpret_cast<const uint4*>(packed + int64_t(valid ? start + s : 0) * hidden);
+  uint4* dst = reinterpret_cast<uint4*>(padded + int64_t(row) * hidden);
+  for (int c = lane; c < hidden / N; c += 32) dst[c] = valid ? src[c] : make_uint4(0u, 0u, 0u, 0u);
+}
+
 }  // namespace zen
 
 using namespace zen;
@@ -488,6 +550,16 @@ int zen_quantize_f16(const void* x, int8_t* q, int64_t n, float scale, int zero_
     return ZEN_ERR_INVALID_ARG;
   EwParams p{x, q, nullptr, n, 1, scale, zero_point, round_mode};
   return launch_ew<EW_QUANT, __half, int8_t>(p, static_cast<cudaStream_t>(stream));
+}
+int zen_quantize_e4m3_f32(const float* x, uint8_t* q, int64_t n, float scale, void* stream) {
+  if (n < 0 || (n > 0 && (!x || !q)) || !(scale > 0.f)) return ZEN_ERR_INVALID_ARG;
+  EwParams p{x, q, nullptr, n, 1, scale, 0, 0};
+  return launch_ew<EW_QUANT_F8, float, uint8_t>(p, static_cast<cudaStream_t>(stream));
+}
+int zen_quantize_e4m3_f16(const void* x, uint8_t* q, int64_t n, float scale, void* stream) {
+  if (n < 0 || (n > 0 && (!x || !q)) || !(scale > 0.f)) return ZEN_ERR_INVALID_ARG;
+  EwParams p{x, q, nullptr, n, 1, scale, 0, 0};
+  return launch_ew<EW_QUANT_F8, __half, uint8_t>(p, static_cast<cudaStream_t>(stream));
 }
 int zen_dequantize_f32(const int8_t* q, float* x, int64_t n, float scale, int zero_point, void* stream) {
   if (n < 0 || (n > 0 && (!x || !q))) return ZEN_ERR_INVALID_ARG;
@@ -561,6 +633,46 @@ int zen_embed_layernorm_f16(const int32_t* ids, const int32_t* type_ids, const v
   p.x = word; p.pos = pos; p.type = type; p.ids = ids; p.type_ids = type_ids; p.gamma = gamma; p.beta = beta;
   p.y = y; p.yq = yq; p.q_scale = out_scale; p.round_mode = round_mode; p.rows = tokens; p.hidden = hidden;
   p.eps = eps; p.seq = seq; p.vocab = vocab;
+  return launch_ln<__half, 2>(p, static_cast<cudaStream_t>(stream));
+}
+
+int zen_pack_tokens_i32(const int32_t* ids, const int32_t* type_ids, const int32_t* kv_lens, int B, int S, int capacity,
+                        int32_t* cu_seqlens, int32_t* ids_packed, int32_t* pos_packed, int32_t* type_packed, void* stream) {
+  if (B < 0 || S <= 0 || capacity < 0) return ZEN_ERR_INVALID_ARG;
+  if (B == 0) return ZEN_OK;
+  if (!ids || !kv_lens || !cu_seqlens || !ids_packed || !pos_packed) return ZEN_ERR_INVALID_ARG;
+  if (int64_t(B) * S >= (int64_t(1) << 31) || B > 65535) return ZEN_ERR_UNSUPPORTED;
+  pack_tokens_kernel<<<B + 1, 128, 0, static_cast<cudaStream_t>(stream)>>>(ids, type_ids, kv_lens, B, S, capacity, cu_seqlens,
+                                                                            ids_packed, pos_packed, type_packed);
+  return cudaGetLastError() == cudaSuccess ? ZEN_OK : ZEN_ERR_LAUNCH;
+}
+
+int zen_unpad_rows_f16(const void* packed, const int32_t* cu_seqlens, int B, int S, int hidden, int capacity, void* padded,
+                       void* stream) {
+  if (B < 0 || S <= 0 || hidden <= 0 || capacity < 0) return ZEN_ERR_INVALID_ARG;
+  if (B == 0) return ZEN_OK;
+  if (!packed || !cu_seqlens || !padded) return ZEN_ERR_INVALID_ARG;
+  if (hidden % 8 || reinterpret_cast<uintptr_t>(packed) % 16 || reinterpret_cast<uintptr_t>(padded) % 16) return ZEN_ERR_UNSUPPORTED;
+  const int64_t rows = int64_t(B) * S;
+  if (rows > (int64_t(1) << 30)) return ZEN_ERR_UNSUPPORTED;
+  const int grid = int((rows + ROW_WARPS - 1) / ROW_WARPS);
+  return launch_pdl(PDL_ROW, unpad_rows_kernel<__half>, dim3(grid), dim3(ROW_WARPS * 32), 0, static_cast<cudaStream_t>(stream),
+                    static_cast<const __half*>(packed), cu_seqlens, B, S, hidden, capacity, static_cast<__half*>(padded));
+}
+
+int zen_embed_layernorm_unpadded_f16(const int32_t* ids_packed, const int32_t* pos_packed, const int32_t* type_packed,
+                                     const void* word, const void* pos, const void* type, const void* gamma,
+                                     const void* beta, void* y, int8_t* yq, float out_scale, int round_mode, int rows,
+                                     int max_pos, int hidden, int vocab, float eps, void* stream) {
+  int st = check_ln(word, gamma, beta, y, rows, hidden);
+  if (st == ZEN_OK && (max_pos <= 0 || vocab <= 0)) st = ZEN_ERR_INVALID_ARG;
+  if (st == ZEN_OK && rows > 0 && (!ids_packed || !pos_packed || !pos || !type)) st = ZEN_ERR_INVALID_ARG;
+  if (st == ZEN_OK && yq && (!(out_scale > 0.f) || (round_mode != 0 && round_mode != 1))) st = ZEN_ERR_INVALID_ARG;
+  if (st != ZEN_OK || rows == 0) return st;
+  RowParams p{};
+  p.x = word; p.pos = pos; p.type = type; p.ids = ids_packed; p.pos_ids = pos_packed; p.type_ids = type_packed;
+  p.gamma = gamma; p.beta = beta; p.y = y; p.yq = yq; p.q_scale = out_scale; p.round_mode = round_mode; p.rows = rows;
+  p.hidden = hidden; p.eps = eps; p.seq = max_pos; p.vocab = vocab;
   return launch_ln<__half, 2>(p, static_cast<cudaStream_t>(stream));
 }
 

@@ -291,6 +291,18 @@ __device__ __forceinline__ void mma_f16_ss(uint32_t d_tmem, uint64_t a_desc, uin
       "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// 8-bit floating point operands (e4m3 / e5m2, chosen in the instruction descriptor), fp32 accumulation
+__device__ __forceinline__ void mma_f8_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t"
+      "}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 __device__ __forceinline__ void mma_tf32_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                             uint32_t accumulate) {
   asm volatile(
@@ -542,6 +554,7 @@ __device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr, uin
 enum : uint32_t { IDESC_C_F16 = 0, IDESC_C_F32 = 1, IDESC_C_S32 = 2 };
 enum : uint32_t { IDESC_F16 = 0, IDESC_BF16 = 1, IDESC_TF32 = 2 };
 enum : uint32_t { IDESC_U8 = 0, IDESC_S8 = 1 };
+enum : uint32_t { IDESC_E4M3 = 0, IDESC_E5M2 = 1 };  // kind::f8f6f4
 
 __host__ __device__ constexpr uint32_t make_idesc(uint32_t c_fmt, uint32_t a_fmt, uint32_t b_fmt, uint32_t a_mn_major,
                                                   uint32_t b_mn_major, uint32_t M, uint32_t N) {

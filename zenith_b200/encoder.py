@@ -93,6 +93,8 @@ def _dev(a, dtype, device):
 class _EncoderBase:
     """Shared plumbing: embedding tables, per-shape buffers, the launch list, CUDA-graph capture."""
 
+    supports_unpadded = False
+
     def __init__(self, cfg: EncoderConfig, params: dict, device, micro_batches: int = 1, gemm_pair: bool | None = None):
         """``gemm_pair``: force the plain GEMMs onto the CTA-pair kernel (True) or the one-CTA kernel (False);
         None lets the library choose by shape."""
@@ -109,17 +111,26 @@ class _EncoderBase:
         self.emb_g = _dev(params["emb_ln_g"], torch.float16, d)
         self.emb_b = _dev(params["emb_ln_b"], torch.float16, d)
         self._shape = None
+        self._packed_rows = None  # row capacity of the packed (unpadded) form, None in the padded form
         self._launches: list = []
         self._graph = None
         self.launches_per_forward = 0
 
     # -- per-shape state --------------------------------------------------------------------
-    def _prepare(self, B: int, S: int) -> None:
-        if self._shape == (B, S):
+    def _prepare(self, B: int, S: int, packed_rows: int | None = None) -> None:
+        if self._shape == (B, S, packed_rows):
             return
         if S > self.cfg.max_pos:
             raise RuntimeError("sequence longer than the position table")
-        self._shape = (B, S)
+        if packed_rows is not None:
+            if not self.supports_unpadded:
+                raise RuntimeError("unpadded batches are implemented for the W8A8 encoder only")
+            if self.micro_batches != 1:
+                raise RuntimeError("unpadded batches need micro_batches == 1")
+            if packed_rows <= 0 or packed_rows > B * S:
+                raise RuntimeError("packed row capacity must lie in 1 .. B * S")
+        self._shape = (B, S, packed_rows)
+        self._packed_rows = packed_rows
         self._graph = None
         d = self.device
         # token ids and key lengths share one allocation, so that a host can feed both with one copy
@@ -127,6 +138,11 @@ class _EncoderBase:
         self.ids = self.inputs[:B * S]
         self.kv_lens = self.inputs[B * S:]
         self.kv_lens.fill_(S)
+        if packed_rows is not None:
+            # offsets, then packed ids and positions: written by the first launch of every pass
+            self.cu_seqlens = torch.zeros(B + 1, dtype=torch.int32, device=d)
+            self.ids_packed = torch.zeros(packed_rows, dtype=torch.int32, device=d)
+            self.pos_packed = torch.zeros(packed_rows, dtype=torch.int32, device=d)
         self._alloc(B, S)
         # Sequences are independent through the whole encoder, so the batch may be cut into micro-batches
         # whose launch sequences run side by side (separate streams / graph branches): the fill and
@@ -172,7 +188,8 @@ class _EncoderBase:
     def set_inputs(self, ids, kv_lens=None) -> None:
         """Copy token ids ([B,S] integer tensor, any device) and key lengths into the static buffers."""
         B, S = ids.shape
-        self._prepare(B, S)
+        same = self._shape is not None and self._shape[:2] == (B, S)
+        self._prepare(B, S, self._packed_rows if same else None)
         self.ids.copy_(ids.reshape(-1), non_blocking=True)
         if kv_lens is not None:
             self.kv_lens.copy_(kv_lens, non_blocking=True)
@@ -188,13 +205,43 @@ class _EncoderBase:
 
     def forward(self, ids, kv_lens=None) -> torch.Tensor:
         """Hidden states ``[B*S, hidden]`` fp16 (a static buffer, overwritten by the next call)."""
+        self._prepare(*ids.shape, None)
         self.set_inputs(ids, kv_lens)
         self._run()
         return self.out
 
+    # Unpadded form: the valid tokens of the batch are packed back to back (sequence b in rows cu_seqlens[b] ..),
+    # the row-wise kernels and GEMMs run on ``capacity`` rows instead of B * S, attention takes its sequences
+    # from the offsets, and the last launch spreads the rows back out (zeros at padding positions).  Every
+    # valid token's result equals the padded pass's, bit for bit.
+    @staticmethod
+    def unpadded_capacity(kv_lens, S: int) -> int:
+        """Rows needed for these key lengths (host values), rounded up to a whole 128-row tile."""
+        total = int(sum(min(max(int(n), 0), S) for n in kv_lens))
+        return max(128, -(-total // 128) * 128)
+
+    def forward_unpadded(self, ids, kv_lens, capacity: int | None = None) -> torch.Tensor:
+        """Padded-layout hidden states ``[B*S, hidden]`` fp16 computed on the packed rows (a static buffer);
+        ``self.out`` holds the packed rows, ``self.cu_seqlens`` their offsets.  ``capacity`` defaults to what
+        ``kv_lens`` needs (read on the host)."""
+        B, S = ids.shape
+        cap = min(B * S, self.unpadded_capacity(kv_lens.tolist(), S) if capacity is None else int(capacity))
+        self._prepare(B, S, cap)
+        self.set_inputs(ids, kv_lens)
+        self._run()
+        return self.out_padded
+
+    def capture_unpadded(self, B: int, S: int, capacity: int) -> None:
+        """``capture`` for the unpadded form with a fixed row capacity: batches whose valid tokens fit it replay the
+        same graph (feed with ``set_inputs`` + ``replay``; the result is ``self.out_padded``)."""
+        self._capture(B, S, min(B * S, int(capacity)))
+
     def capture(self, B: int, S: int) -> None:
         """Capture one pass for shape (B, S) into a CUDA graph; feed it with ``set_inputs`` + ``replay``."""
-        self._prepare(B, S)
+        self._capture(B, S, None)
+
+    def _capture(self, B: int, S: int, packed_rows) -> None:
+        self._prepare(B, S, packed_rows)
         side = torch.cuda.Stream(device=self.device)
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
@@ -211,7 +258,7 @@ class _EncoderBase:
             raise RuntimeError("capture() first")
         self._graph.replay()
         ops.launch_count += len(self._launches)
-        return self.out
+        return self.out if self._packed_rows is None else self.out_padded
 
 
 class Fp16Encoder(_EncoderBase):
@@ -363,6 +410,8 @@ class Int8Scales:
 class Int8Encoder(_EncoderBase):
     """W8A8 encoder: int8 GEMM operands, int32 accumulation, fp16 residual stream / LayerNorm / softmax."""
 
+    supports_unpadded = True
+
     def __init__(self, cfg: EncoderConfig, params: dict, scales: Int8Scales, device="cuda:0", micro_batches: int = 1,
                  fuse_layernorm: bool | None = None, prefetch_weights: bool = True, gemm_pair: bool | None = None,
                  fuse_attention: bool | None = None, keep_qkv: bool = False):
@@ -398,9 +447,11 @@ class Int8Encoder(_EncoderBase):
 
     def _alloc(self, B: int, S: int) -> None:
         cfg, d = self.cfg, self.device
-        T, H, F = B * S, cfg.hidden, cfg.ffn
+        T, H, F = self._packed_rows or B * S, cfg.hidden, cfg.ffn
         f16 = dict(dtype=torch.float16, device=d)
         s8 = dict(dtype=torch.int8, device=d)
+        if self._packed_rows is not None:
+            self.out_padded = torch.empty((B * S, H), **f16)
         self.x = [torch.empty((T, H), **f16) for _ in range(2)]
         self.xq = [torch.empty((T, H), **s8) for _ in range(2)]
         self.qkv = torch.empty((T, 3 * H), **f16)
@@ -416,7 +467,8 @@ class Int8Encoder(_EncoderBase):
     def _build(self, b0: int, B: int, S: int) -> None:
         """Launch list for sequences [b0, b0 + B) of the batch (rows b0*S .. of every buffer)."""
         cfg = self.cfg
-        T, H, F, nh, hd = B * S, cfg.hidden, cfg.ffn, cfg.heads, cfg.head_dim
+        packed = self._packed_rows is not None
+        T, H, F, nh, hd = self._packed_rows or B * S, cfg.hidden, cfg.ffn, cfg.heads, cfg.head_dim
         r0 = b0 * S
         P = lambda t: _row_ptr(t, r0)
         # the weights of this object are written once, in __init__: every GEMM of the launch list carries the
@@ -425,13 +477,24 @@ class Int8Encoder(_EncoderBase):
         GF = self.gemm_flags  # the plain GEMMs also carry the kernel choice
         sc = self.act_scales
         can_fuse = S <= 128 and hd == 64
-        if self.fuse_attention and not can_fuse:
+        if (self.fuse_attention or packed) and not can_fuse:
             raise RuntimeError("the fused QKV + attention kernel needs seq <= 128 and head_dim == 64")
         fused_attn = can_fuse if self.fuse_attention is None else bool(self.fuse_attention)
+        if packed and not fused_attn:
+            raise RuntimeError("unpadded batches run through the fused QKV + attention kernel")
         self.launches_per_layer = (5 if self.fuse_layernorm else 7) - (1 if fused_attn else 0)
-        self._add("zen_embed_layernorm_f16", P(self.ids), None, self.word.data_ptr(), self.pos.data_ptr(),
-                  self.type.data_ptr(), self.emb_g.data_ptr(), self.emb_b.data_ptr(), P(self.x[0]), P(self.xq[0]),
-                  sc[0]["x"], ROUND_NEAREST_EVEN, T, S, H, cfg.vocab, cfg.eps)
+        self.lead_launches = 2 if packed else 1
+        if packed:
+            self._add("zen_pack_tokens_i32", self.ids.data_ptr(), None, self.kv_lens.data_ptr(), B, S, T,
+                      self.cu_seqlens.data_ptr(), self.ids_packed.data_ptr(), self.pos_packed.data_ptr(), None)
+            self._add("zen_embed_layernorm_unpadded_f16", self.ids_packed.data_ptr(), self.pos_packed.data_ptr(), None,
+                      self.word.data_ptr(), self.pos.data_ptr(), self.type.data_ptr(), self.emb_g.data_ptr(),
+                      self.emb_b.data_ptr(), P(self.x[0]), P(self.xq[0]), sc[0]["x"], ROUND_NEAREST_EVEN, T, cfg.max_pos, H,
+                      cfg.vocab, cfg.eps)
+        else:
+            self._add("zen_embed_layernorm_f16", P(self.ids), None, self.word.data_ptr(), self.pos.data_ptr(),
+                      self.type.data_ptr(), self.emb_g.data_ptr(), self.emb_b.data_ptr(), P(self.x[0]), P(self.xq[0]),
+                      sc[0]["x"], ROUND_NEAREST_EVEN, T, S, H, cfg.vocab, cfg.eps)
         qs = (S * 3 * H, hd, 3 * H)
         os_ = (S * H, hd, H)
         kv = self.kv_lens.data_ptr() + 4 * b0
@@ -444,7 +507,12 @@ class Int8Encoder(_EncoderBase):
             nbytes = lambda t: t.numel() * t.element_size()
             pf = lambda *ts: [v for t in ts for v in ((t.data_ptr(), nbytes(t)) if self.prefetch_weights and t is not None
                                                        else (None, 0))]
-            if fused_attn:
+            if packed:
+                self._add("zen_qkv_attention_unpadded_i8", P(xq), H, L["wqkv"].data_ptr(), H, B, T,
+                          self.cu_seqlens.data_ptr(), nh, H, a["x"], L["wqkv_s"].data_ptr(), L["bqkv"].data_ptr(),
+                          1.0 / math.sqrt(hd), P(self.ctx), P(self.ctxq), a["ctx"], P(self.qkv) if self.keep_qkv else None,
+                          *pf(L["wo"], L["w1"]), CW)
+            elif fused_attn:
                 self._add("zen_qkv_attention_i8", P(xq), H, L["wqkv"].data_ptr(), H, B, S, nh, H, a["x"],
                           L["wqkv_s"].data_ptr(), L["bqkv"].data_ptr(), kv, 1.0 / math.sqrt(hd), P(self.ctx), P(self.ctxq),
                           a["ctx"], P(self.qkv) if self.keep_qkv else None, *pf(L["wo"], L["w1"]), CW)
@@ -480,6 +548,9 @@ class Int8Encoder(_EncoderBase):
                           P(xn), None if last else P(xqn), 1.0 if last else sc[li + 1]["x"], ROUND_NEAREST_EVEN, T, H,
                           cfg.eps)
             cur ^= 1
+        if packed:
+            self._add("zen_unpad_rows_f16", self.x[cur].data_ptr(), self.cu_seqlens.data_ptr(), B, S, H, T,
+                      self.out_padded.data_ptr())
 
     def forward_layerwise(self, ids, kv_lens=None):
         """Generator for tests: runs the pass one layer at a time and yields ``(layer, buffers)`` after
@@ -489,12 +560,13 @@ class Int8Encoder(_EncoderBase):
         if len(self._micro) != 1:
             raise RuntimeError("forward_layerwise needs micro_batches == 1")
         stream = torch.cuda.current_stream().cuda_stream
-        f, name, args = self._launches[0]
-        _capi.check(name, f(*args, stream))
+        lead = self.lead_launches
+        for f, name, args in self._launches[:lead]:
+            _capi.check(name, f(*args, stream))
         cur = 0
         for li in range(len(self.layers)):
             n = self.launches_per_layer
-            for f, name, args in self._launches[1 + li * n: 1 + (li + 1) * n]:
+            for f, name, args in self._launches[lead + li * n: lead + (li + 1) * n]:
                 _capi.check(name, f(*args, stream))
             torch.cuda.synchronize()
             yield li, {"x": self.x[cur], "xq": self.xq[cur], "qkv": self.qkv, "ctx": self.ctx, "ctxq": self.ctxq,

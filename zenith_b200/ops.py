@@ -553,3 +553,133 @@ def embed_layernorm(ids, type_ids, word, pos, typ, gamma, beta, eps: float, seq:
               typ.data_ptr(), gamma.data_ptr(), beta.data_ptr(), y.data_ptr(), _ptr(yq), float(out_scale or 1.0),
               _ROUND[round], tokens, int(seq), hidden, word.shape[0], float(eps), _stream())
     return y if yq is None else (y, yq)
+
+
+# --------------------------------------------------------------------------------------------
+# unpadded batches: the valid tokens packed back to back
+# --------------------------------------------------------------------------------------------
+def pack_tokens(ids, kv_lens, capacity: int, type_ids=None):
+    """From padded ``ids [B, S]`` (int32) and key lengths ``kv_lens [B]`` to ``(cu_seqlens [B+1], ids_packed,
+    pos_packed, type_packed or None)`` of ``capacity`` rows (``zen_pack_tokens_i32``); rows beyond the total
+    carry id 0 / position 0."""
+    _require(ids, "ids", torch.int32, 2)
+    _require(kv_lens, "kv_lens", torch.int32, 1)
+    if type_ids is not None:
+        _require(type_ids, "type_ids", torch.int32, 2)
+    B, S = ids.shape
+    d = ids.device
+    cu = torch.empty(B + 1, dtype=torch.int32, device=d)
+    ids_p = torch.empty(capacity, dtype=torch.int32, device=d)
+    pos_p = torch.empty(capacity, dtype=torch.int32, device=d)
+    type_p = torch.empty(capacity, dtype=torch.int32, device=d) if type_ids is not None else None
+    _call("zen_pack_tokens_i32", ids.data_ptr(), _ptr(type_ids), kv_lens.data_ptr(), B, S, int(capacity), cu.data_ptr(),
+          ids_p.data_ptr(), pos_p.data_ptr(), _ptr(type_p), _stream())
+    return cu, ids_p, pos_p, type_p
+
+
+def unpad_rows(packed, cu_seqlens, B: int, S: int):
+    """Padded ``[B*S, hidden]`` fp16 copy of packed rows: zeros at padding positions (``zen_unpad_rows_f16``)."""
+    _require(packed, "packed", torch.float16, 2)
+    _require(cu_seqlens, "cu_seqlens", torch.int32, 1)
+    if cu_seqlens.numel() != B + 1:
+        raise RuntimeError("cu_seqlens must hold B + 1 offsets")
+    out = torch.empty((B * S, packed.shape[1]), dtype=torch.float16, device=packed.device)
+    _call("zen_unpad_rows_f16", packed.data_ptr(), cu_seqlens.data_ptr(), B, S, packed.shape[1], packed.shape[0],
+          out.data_ptr(), _stream())
+    return out
+
+
+def embed_layernorm_unpadded(ids_packed, pos_packed, type_packed, word, pos, typ, gamma, beta, eps: float, *,
+                             out_scale=None, round="nearest_even"):
+    """``embed_layernorm`` on packed rows: the position of each row comes from ``pos_packed``."""
+    _require(ids_packed, "ids_packed", torch.int32, 1)
+    _require(pos_packed, "pos_packed", torch.int32, 1)
+    if type_packed is not None:
+        _require(type_packed, "type_packed", torch.int32, 1)
+    for name, t in (("word", word), ("pos", pos), ("type", typ)):
+        _require(t, name, torch.float16, 2)
+    _require(gamma, "gamma", torch.float16, 1)
+    _require(beta, "beta", torch.float16, 1)
+    rows = ids_packed.numel()
+    hidden = word.shape[1]
+    y = torch.empty((rows, hidden), dtype=torch.float16, device=word.device)
+    yq = torch.empty((rows, hidden), dtype=torch.int8, device=word.device) if out_scale is not None else None
+    if rows:
+        _call("zen_embed_layernorm_unpadded_f16", ids_packed.data_ptr(), pos_packed.data_ptr(), _ptr(type_packed),
+              word.data_ptr(), pos.data_ptr(), typ.data_ptr(), gamma.data_ptr(), beta.data_ptr(), y.data_ptr(), _ptr(yq),
+              float(out_scale or 1.0), _ROUND[round], rows, pos.shape[0], hidden, word.shape[0], float(eps), _stream())
+    return y if yq is None else (y, yq)
+
+
+def qkv_attention_unpadded_int8(xq, wqkv, x_scale: float, w_scale, bias, cu_seqlens, heads: int, *,
+                                scale: float | None = None, out_scale: float | None = None, emit_qkv: bool = False,
+                                constant_weights=False):
+    """``qkv_attention_int8`` on packed rows (``zen_qkv_attention_unpadded_i8``): ``xq`` int8 ``[rows, K]``, sequence b
+    in rows ``cu_seqlens[b] .. cu_seqlens[b+1]-1`` (at most 128 each).  Rows that belong to no sequence are left
+    unwritten in the outputs (which start as zeros here)."""
+    _require(xq, "xq", torch.int8, 2)
+    _require(wqkv, "wqkv", torch.int8, 2)
+    _require(cu_seqlens, "cu_seqlens", torch.int32, 1)
+    hidden = heads * 64
+    T, K = xq.shape
+    if tuple(wqkv.shape) != (3 * hidden, K):
+        raise RuntimeError("shape mismatch")
+    if w_scale is not None:
+        _require(w_scale, "w_scale", torch.float32, 1)
+    if bias is not None:
+        _require(bias, "bias", torch.float32, 1)
+    B = cu_seqlens.numel() - 1
+    ctx = torch.zeros((T, hidden), dtype=torch.float16, device=xq.device)
+    ctxq = torch.zeros((T, hidden), dtype=torch.int8, device=xq.device) if out_scale is not None else None
+    qkv = torch.zeros((T, 3 * hidden), dtype=torch.float16, device=xq.device) if emit_qkv else None
+    _call("zen_qkv_attention_unpadded_i8", xq.data_ptr(), K, wqkv.data_ptr(), K, B, T, cu_seqlens.data_ptr(), heads, K,
+          float(x_scale), _ptr(w_scale), _ptr(bias), float(1.0 / math.sqrt(64) if scale is None else scale),
+          ctx.data_ptr(), _ptr(ctxq), float(out_scale or 1.0), _ptr(qkv), None, 0, None, 0,
+          _capi.GEMM_CONST_WEIGHTS if constant_weights else 0, _stream())
+    out = [ctx]
+    if ctxq is not None:
+        out.append(ctxq)
+    if qkv is not None:
+        out.append(qkv)
+    return out[0] if len(out) == 1 else tuple(out)
+
+
+# --------------------------------------------------------------------------------------------
+# FP8 (e4m3) operands
+# --------------------------------------------------------------------------------------------
+def quantize_e4m3(x, scale: float):
+    """e4m3 bit patterns (uint8) of ``x / scale``: round to nearest even, saturating at +-448."""
+    if x.dtype not in (torch.float32, torch.float16):
+        raise RuntimeError("input must be fp32 or fp16")
+    _require(x, "input", x.dtype)
+    q = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
+    fn = "zen_quantize_e4m3_f32" if x.dtype == torch.float32 else "zen_quantize_e4m3_f16"
+    if x.numel():
+        _call(fn, x.data_ptr(), q.data_ptr(), x.numel(), float(scale), _stream())
+    return q
+
+
+def linear_fp8(xq, wq, x_scale: float, w_scale=None, bias=None, *, act="none", out_dtype=torch.float16, out=None,
+               constant_weights=False, tile_n: int = 0):
+    """``act((xq @ wq.T) * x_scale * w_scale + bias)`` with e4m3 operands (uint8 bit patterns) and fp32 accumulation on
+    the tensor cores (``zen_linear_f8``); a tolerance path like ``linear_fp16``."""
+    _require(xq, "xq", torch.uint8, 2, rows_may_be_strided=True)
+    _require(wq, "wq", torch.uint8, 2)
+    M, K = xq.shape
+    N, K2 = wq.shape
+    if K != K2:
+        raise RuntimeError(f"inner dimensions differ: xq {tuple(xq.shape)} vs wq {tuple(wq.shape)}")
+    if w_scale is not None:
+        _require(w_scale, "w_scale", torch.float32, 1)
+    if bias is not None:
+        _require(bias, "bias", torch.float32, 1)
+    if out_dtype not in (torch.float16, torch.float32):
+        raise RuntimeError(f"unsupported out_dtype {out_dtype}")
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=xq.device)
+    if M == 0 or N == 0:
+        return out
+    _call("zen_linear_f8", xq.data_ptr(), xq.stride(0) if M > 1 else K, wq.data_ptr(), K, M, N, K, float(x_scale), _ptr(w_scale),
+          _ptr(bias), _ACT[act], _OUT[out_dtype], out.data_ptr(), out.stride(0),
+          (_capi.GEMM_CONST_WEIGHTS if constant_weights else 0) | _capi.gemm_tile_n(tile_n), _stream())
+    return out
