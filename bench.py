@@ -427,6 +427,32 @@ def secondary_metrics(torch, ops, dev, flush, peaks, cfg_base, params_base) -> d
     out["add_layernorm_98304x1024"] = {"gb_per_s": round(gbs, 1), "frac_of_hbm": round(gbs / peaks["hbm_gbs"], 3),
                                        "hbm_gbs": peaks["hbm_gbs"], "bytes_per_row": hidden * 7}
     del x, r
+    # unpadded batches where they pay: 128 sequences x 128 tokens (the headline's 32 x 128 needs the same number of
+    # tile rounds packed or padded, so packing gains nothing there)
+    try:
+        from zenith_b200.calibrate import calibrate as _cal
+        calb = [make_batch(MASTER_SEED + 1 + i, cfg_base.vocab) for i in range(2)]
+        sc_b = _cal(cfg_base, params_base, [(torch.from_numpy(i).to(dev), torch.from_numpy(l).to(dev)) for i, l in calb], dev)
+        ids, lens = make_batch(MASTER_SEED + 3000, cfg_base.vocab, batch=128, seq=SEQ)
+        ids_d, lens_d = torch.from_numpy(ids).to(dev), torch.from_numpy(lens).to(dev)
+        res = {}
+        for form in ("padded", "unpadded"):
+            enc = Int8Encoder(cfg_base, params_base, sc_b, dev)
+            if form == "padded":
+                enc.capture(128, SEQ)
+            else:
+                enc.capture_unpadded(128, SEQ, Int8Encoder.unpadded_capacity(lens.tolist(), SEQ))
+            enc.set_inputs(ids_d, lens_d)
+            for _ in range(3):
+                enc.replay()
+            us = _event_us(torch, enc.replay, 9, flush)
+            res[form] = {"ms_per_step": round(us / 1e3, 4), "sequences_per_s": round(128 / us * 1e6, 1)}
+            del enc
+        res["valid_tokens"] = int(lens.sum())
+        res["padded_tokens"] = int(ids.size)
+        out["bert_base_int8_batch128_unpadded"] = res
+    except Exception as exc:
+        out["bert_base_int8_batch128_unpadded"] = {"error": str(exc)}
     # configs[4]: one GPU's shard of the BERT-large run at 8 GPUs (32 sequences x 384 tokens)
     cfg = BERT_LARGE
     params = init_params(cfg, MASTER_SEED)

@@ -445,7 +445,9 @@ __device__ __forceinline__ void gemm_ln_body(const CUtensorMap& tmap_a, const CU
 
   tc_fence_before_sync();
   __syncthreads();
-  cluster_sync_all();  // no CTA leaves while a peer may still store into its shared memory
+  // No cluster-wide rendezvous here: the only accesses a peer makes to this CTA's shared memory are the partial
+  // statistics of a tile and the arrival that follows them, and this CTA has waited for all of them (stats_bar of
+  // its last tile) before it got here; a peer publishes nothing after its last tile.
   if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 

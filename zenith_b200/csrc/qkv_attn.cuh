@@ -473,17 +473,9 @@ qkv_attn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           w[i] = *reinterpret_cast<const uint32_t*>(&hv);
           val[i] = __half22float2(hv);
         }
-        if (PACKED) {
-          if (row_live) {
-            uint4* dst = reinterpret_cast<uint4*>(p.ctx + grow * hidden + h * 64 + g * 16);
-            dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
-            dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
-          }
-        } else {
-          uint8_t* srow = sty + lane * 128;
-          *reinterpret_cast<uint4*>(srow + (((2 * g) ^ (lane & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-          *reinterpret_cast<uint4*>(srow + (((2 * g + 1) ^ (lane & 7)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
-        }
+        uint8_t* srow = sty + lane * 128;
+        *reinterpret_cast<uint4*>(srow + (((2 * g) ^ (lane & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        *reinterpret_cast<uint4*>(srow + (((2 * g + 1) ^ (lane & 7)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
         if (p.ctxq) {
           uint32_t qw[4];
           const uint32_t risky = quantize_pairs_rn<16>(val, inv_o_scale, qw);
@@ -493,22 +485,38 @@ qkv_attn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
               if (risky & (1u << e))
                 patch_q_byte(qw, e, zen_det_round_clamp_i8(ZEN_DIV((e & 1) ? val[e >> 1].y : val[e >> 1].x, p.ctx_scale), 0));
           }
-          if (PACKED) {
-            if (row_live) *reinterpret_cast<uint4*>(p.ctxq + grow * hidden + h * 64 + g * 16) = make_uint4(qw[0], qw[1], qw[2], qw[3]);
-          } else {
-            *reinterpret_cast<uint4*>(stq + lane * 64 + ((g ^ ((lane >> 1) & 3)) << 4)) = make_uint4(qw[0], qw[1], qw[2], qw[3]);
-          }
+          *reinterpret_cast<uint4*>(stq + lane * 64 + ((g ^ ((lane >> 1) & 3)) << 4)) = make_uint4(qw[0], qw[1], qw[2], qw[3]);
         }
       }
       tc_fence_before_sync();
       mbar_arrive(&acc_empty[set]);  // the set's TMEM columns may receive the next projection
-      if (PACKED) continue;          // the rows went to global memory directly
       fence_proxy_async_smem();      // this thread's staged bytes -> visible to the TMA engine
       mbar_arrive(&my_pair[2]);
       if (half == 0) {
         // both warps of the pair have staged their halves of the 32 rows
         if (!mbar_wait(&my_pair[2], it & 1u, abort_flag)) break;
-        if (lane == 0 && quad * 32 < p.S) {
+        if (PACKED) {
+          // Box-shaped stores would write the rows of the next sequence: the valid rows leave with plain stores,
+          // consecutive lanes taking consecutive 16-byte pieces of a row (whole 128-byte lines per row).
+          const int live = kv_len - quad * 32;  // rows of this quadrant that belong to the sequence
+          const int64_t base_row = int64_t(first_row(b)) + quad * 32;
+#pragma unroll 2
+          for (int idx = lane; idx < 32 * 8; idx += 32) {
+            const int rw = idx >> 3, c = idx & 7;
+            if (rw < live)
+              *(reinterpret_cast<uint4*>(p.ctx + (base_row + rw) * hidden + h * 64) + c) =
+                  *reinterpret_cast<const uint4*>(sty + rw * 128 + ((c ^ (rw & 7)) << 4));
+          }
+          if (p.ctxq) {
+#pragma unroll 2
+            for (int idx = lane; idx < 32 * 4; idx += 32) {
+              const int rw = idx >> 2, c = idx & 3;
+              if (rw < live)
+                *(reinterpret_cast<uint4*>(p.ctxq + (base_row + rw) * hidden + h * 64) + c) =
+                    *reinterpret_cast<const uint4*>(stq + rw * 64 + ((c ^ ((rw >> 1) & 3)) << 4));
+            }
+          }
+        } else if (lane == 0 && quad * 32 < p.S) {
           int c[4];
           c[0] = 0;
           c[p.o_perm[0]] = quad * 32;
