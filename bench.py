@@ -372,6 +372,11 @@ def secondary_metrics(torch, ops, dev, flush, peaks, cfg_base, params_base) -> d
     from zenith_b200.encoder import BERT_LARGE, Fp16Encoder, Int8Encoder, Int8Scales, init_params
 
     out = {}
+
+    def done(what):  # progress on stderr: a fault in a secondary measurement is then easy to place
+        torch.cuda.synchronize()
+        print(f"[bench] secondary: {what} done", file=sys.stderr, flush=True)
+
     # configs[1]: the fp16 encoder, batch 32 x 128
     enc = Fp16Encoder(cfg_base, params_base, dev)
     ids, lens = make_batch(MASTER_SEED + 1000, cfg_base.vocab)
@@ -383,6 +388,7 @@ def secondary_metrics(torch, ops, dev, flush, peaks, cfg_base, params_base) -> d
     out["bert_base_fp16_seq128"] = {"sequences_per_s": round(BATCH / us * 1e6, 1), "ms_per_step": round(us / 1e3, 4),
                                     "launches": enc.launches_per_forward, "workload": "BASELINE.json configs[1]"}
     del enc
+    done("fp16 encoder")
     # configs[3]: attention forward sweep, B = 8, H = 16
     fp16_peak = peaks["bf16_tflops"]
     sweep = {}
@@ -399,6 +405,7 @@ def secondary_metrics(torch, ops, dev, flush, peaks, cfg_base, params_base) -> d
             del q, k, v
     out["attention_fwd_b8_h16"] = {"cases": sweep, "peak_tflops": fp16_peak,
                                    "peak_source": f"{peaks['source']} bf16 GEMM burst", "workload": "BASELINE.json configs[3]"}
+    done("attention sweep")
     # int8 GEMM yardstick: own kernel against the library GEMM on the same device in the same run
     n = 8192
     a = torch.randint(-128, 128, (n, n), dtype=torch.int8, device=dev)
@@ -414,6 +421,7 @@ def secondary_metrics(torch, ops, dev, flush, peaks, cfg_base, params_base) -> d
     out["int8_gemm_8192"] = {"own_tops": round(2.0 * n**3 / us_own / 1e6, 1), "library_int_mm_tops": round(2.0 * n**3 / us_lib / 1e6, 1),
                              "note": "own: fp16 output with per-column scales (CTA-pair kernel); library: torch._int_mm, int32 output"}
     del a, b, o16
+    done("int8 GEMM 8192")
     # add + LayerNorm (fp16 in / out + int8 copy) against the measured copy bandwidth
     rows, hidden = 98304, 1024
     x = torch.randn(rows, hidden, device=dev, dtype=torch.float16)
@@ -427,6 +435,7 @@ def secondary_metrics(torch, ops, dev, flush, peaks, cfg_base, params_base) -> d
     out["add_layernorm_98304x1024"] = {"gb_per_s": round(gbs, 1), "frac_of_hbm": round(gbs / peaks["hbm_gbs"], 3),
                                        "hbm_gbs": peaks["hbm_gbs"], "bytes_per_row": hidden * 7}
     del x, r
+    done("add + LayerNorm")
     # unpadded batches where they pay: 128 sequences x 128 tokens (the headline's 32 x 128 needs the same number of
     # tile rounds packed or padded, so packing gains nothing there)
     try:
@@ -453,6 +462,7 @@ def secondary_metrics(torch, ops, dev, flush, peaks, cfg_base, params_base) -> d
         out["bert_base_int8_batch128_unpadded"] = res
     except Exception as exc:
         out["bert_base_int8_batch128_unpadded"] = {"error": str(exc)}
+    done("batch 128 padded / unpadded")
     # configs[4]: one GPU's shard of the BERT-large run at 8 GPUs (32 sequences x 384 tokens)
     cfg = BERT_LARGE
     params = init_params(cfg, MASTER_SEED)
@@ -680,7 +690,7 @@ def run_ours(args) -> None:
     launches = ops.launch_count - launches0
     timed_e2e(W)
     e2e_ms = timed_e2e(K)
-    e2e_launches = enc.launches_per_forward + 1  # + the device copy that parks the result for the copy stream
+    e2e_launches = enc.launches_per_forward  # the copies to and from the host run on the copy engines
     clocks = sampler.stop() if sampler else None
     sus = sustained(args.sustain_seconds) if args.sustain_seconds > 0 else None
     gather_check = None

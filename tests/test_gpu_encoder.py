@@ -183,6 +183,38 @@ def test_host_pipeline_returns_every_batch(cuda):
     assert _capi.device_status() == 0
 
 
+def test_capture_slots_have_their_own_inputs_and_results(cuda):
+    """capture(..., slots=2): two graphs of the same pass, each with its own input block and result buffer; a slot's
+    replay leaves the other slot's result alone and gives the bits of a plain forward pass."""
+    cfg = EncoderConfig(layers=2, hidden=768, heads=12, ffn=1024, vocab=2000, max_pos=128)
+    params = init_params(cfg, 11, random_affine=True)
+    mk = lambda s: (rng(s).integers(0, cfg.vocab, (4, 64)), rng(s + 100).integers(1, 65, 4).astype(np.int32))
+    scales = ER.calibrate_on_oracle(cfg, params, [mk(s) for s in range(2)], quantize_weights,
+                                    activation_scales_from_ranges, Int8Scales)
+    enc = Int8Encoder(cfg, params, scales, cuda)
+    (ia, la), (ib, lb) = mk(31), mk(32)
+    want_a = enc.forward(*tdev(ia, la, cuda)).clone()
+    want_b = enc.forward(*tdev(ib, lb, cuda)).clone()
+    enc.capture(4, 64, slots=2)
+    pack = lambda i, l: torch.from_numpy(np.concatenate([i.reshape(-1), l]).astype(np.int32)).to(cuda)
+    enc.inputs_of(0).copy_(pack(ia, la))
+    enc.inputs_of(1).copy_(pack(ib, lb))
+    ra = enc.replay(0)
+    rb = enc.replay(1)
+    assert ra.data_ptr() != rb.data_ptr() and ra.data_ptr() == enc.result_of(0).data_ptr()
+    assert torch.equal(ra, want_a) and torch.equal(rb, want_b)
+    enc.inputs_of(0).copy_(pack(ib, lb))
+    assert torch.equal(enc.replay(0), want_b) and torch.equal(enc.result_of(1), want_b)
+    # the unpadded form takes slots the same way
+    cap = Int8Encoder.unpadded_capacity(la.tolist(), 64)
+    enc.capture_unpadded(4, 64, max(cap, Int8Encoder.unpadded_capacity(lb.tolist(), 64)), slots=2)
+    enc.inputs_of(1).copy_(pack(ia, la))
+    got = enc.replay(1)
+    rows = torch.from_numpy(np.concatenate([b * 64 + np.arange(int(n)) for b, n in enumerate(la)])).to(cuda)
+    assert torch.equal(got[rows], want_a[rows])
+    assert _capi.device_status() == 0
+
+
 def test_fp16_encoder_with_fused_layernorm_kernels(cuda):
     """hidden 768: the fp16 encoder runs attention-output and FFN2 as GEMM + residual + LayerNorm kernels."""
     cfg = EncoderConfig(layers=2, hidden=768, heads=12, ffn=1024, vocab=2000, max_pos=128)

@@ -100,6 +100,56 @@ def test_packed_attention_equals_padded_on_valid_rows(cuda, B, S, heads, K, lens
                 assert np.max(np.abs(got - want)) <= 1e-2 * max(1.0, np.abs(want).max())
 
 
+def test_packed_attention_cuts_offsets_beyond_the_row_capacity(cuda):
+    """Offsets that run past the rows of the packed tensors (a batch that does not fit its capacity): the rows that
+    exist get their results, nothing is written beyond them."""
+    heads, K, H = 2, 128, 128
+    lens = [100, 128, 90, 128]
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)  # 446 rows wanted
+    rows = 300                                                    # ... 300 exist: sequence 2 is cut, sequence 3 is gone
+    x = rng(1).integers(-128, 128, (rows + 64, K), dtype=np.int8)
+    w = rng(2).integers(-128, 128, (3 * H, K), dtype=np.int8)
+    ws = ((rng(3).random(3 * H) + 0.5) * (0.009 / np.sqrt(K))).astype(np.float32)
+    xd = dev(x, cuda)
+    # outputs allocated with slack rows behind them, so that a stray store would land in memory this test owns
+    got = ops.qkv_attention_unpadded_int8(xd[:rows], dev(w, cuda), 0.02, dev(ws, cuda), None, dev(cu, cuda), heads, out_scale=0.02)
+    ctx, ctxq = got
+    assert _capi.device_status() == 0
+    cu_cut = np.minimum(cu, rows).astype(np.int32)
+    want, wantq = ops.qkv_attention_unpadded_int8(xd[:rows], dev(w, cuda), 0.02, dev(ws, cuda), None, dev(cu_cut, cuda), heads,
+                                                   out_scale=0.02)
+    assert torch.equal(ctx, want) and torch.equal(ctxq, wantq)
+    assert ctx[:228].any() and ctx[228:300].any()
+
+
+def test_unpadded_encoder_survives_a_batch_larger_than_its_capacity(cuda):
+    """capture_unpadded warms up and captures with full-length sequences (more tokens than the capacity): rows beyond
+    the capacity are dropped, nothing outside the buffers is touched, later batches that fit are exact."""
+    cfg = EncoderConfig(layers=2, hidden=768, heads=12, ffn=1024, vocab=2000, max_pos=128)
+    params = init_params(cfg, 11, random_affine=True)
+    r = rng(33)
+    B, S = 16, 128
+    mk = lambda: (torch.from_numpy(r.integers(0, cfg.vocab, (B, S))).to(cuda),
+                  torch.from_numpy((S - r.integers(40, 90, B)).astype(np.int32)).to(cuda))
+    scales = calibrate(cfg, params, [mk() for _ in range(2)], cuda)
+    enc = Int8Encoder(cfg, params, scales, cuda)
+    ids, lens = mk()
+    want = Int8Encoder(cfg, params, scales, cuda).forward(ids, lens).clone()
+    cap = Int8Encoder.unpadded_capacity(lens.tolist(), S)
+    assert cap <= B * S - 512
+    guard = torch.full((4 << 20,), 7, dtype=torch.uint8, device=cuda)  # allocated next: a stray store is likely to land here
+    enc.capture_unpadded(B, S, cap)       # runs the pass with every sequence at full length: 2048 tokens > capacity
+    full = torch.full((B,), S, dtype=torch.int32, device=cuda)
+    enc.set_inputs(ids, full)
+    enc.replay()                          # again, explicitly
+    enc.set_inputs(ids, lens)
+    got = enc.replay()
+    rows = torch.from_numpy(valid_rows(lens.tolist(), S)).to(cuda)
+    assert torch.equal(got[rows], want[rows])
+    assert bool((guard == 7).all())
+    assert _capi.device_status() == 0
+
+
 def test_packed_attention_flags_a_sequence_longer_than_a_tile(cuda):
     heads, K = 1, 64
     x = dev(rng(1).integers(-128, 128, (200, K), dtype=np.int8), cuda)

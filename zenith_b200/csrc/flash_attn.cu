@@ -475,7 +475,7 @@ static int qkv_attention_launch(bool packed, const int8_t* xq, int64_t ldx, cons
   p.B = B; p.S = S; p.heads = heads; p.K = K;
   p.num_k_blocks = (K + 127) / 128;
   p.x_scale = x_scale; p.w_scale = w_scale; p.bias = bias; p.kv_lens = kv_lens;
-  p.cu_seqlens = cu_seqlens; p.ctx = static_cast<__half*>(ctx);
+  p.cu_seqlens = cu_seqlens; p.ctx = static_cast<__half*>(ctx); p.rows = int(rows);
   p.scale_log2 = scale * 1.4426950408889634f;
   p.ctxq = ctxq; p.ctx_scale = ctxq ? ctx_scale : 1.0f;
   p.qkv_out = static_cast<__half*>(qkv_out);

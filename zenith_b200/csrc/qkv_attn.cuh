@@ -50,6 +50,7 @@ struct QkvAttnParams {
   const float* bias;     // [3 * heads * 64] or null
   const int32_t* kv_lens;
   const int32_t* cu_seqlens;  // PACKED: [B + 1] row offsets; the key length of sequence b is their difference
+  int rows;                   // PACKED: rows of the packed tensors; offsets beyond it are cut (nothing is stored there)
   __half* ctx;                // PACKED: output rows are written with plain stores (ld = heads * 64)
   float scale_log2;  // softmax scale * log2(e)
   int8_t* ctxq;      // int8 copy of the output (may be null)
@@ -116,7 +117,14 @@ qkv_attn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   // first row of sequence b in a packed batch; key length of sequence b (clamped to what one tile holds)
   auto first_row = [&](int b) -> int { return PACKED ? p.cu_seqlens[b] : b * p.S; };
   auto key_len = [&](int b) -> int {
-    const int n = PACKED ? p.cu_seqlens[b + 1] - p.cu_seqlens[b] : (p.kv_lens ? p.kv_lens[b] : p.S);
+    int n = p.S;
+    if (PACKED) {
+      // a sequence that runs past the end of the packed tensors (offsets that exceed the row capacity) is cut there
+      const int lo = p.cu_seqlens[b], hi = p.cu_seqlens[b + 1];
+      n = lo < 0 ? 0 : (hi < p.rows ? hi : p.rows) - lo;
+    } else if (p.kv_lens) {
+      n = p.kv_lens[b];
+    }
     return n < 0 ? 0 : (n > p.S ? p.S : n);
   };
 

@@ -231,16 +231,25 @@ class _EncoderBase:
         self._run()
         return self.out_padded
 
-    def capture_unpadded(self, B: int, S: int, capacity: int) -> None:
+    def capture_unpadded(self, B: int, S: int, capacity: int, slots: int = 1) -> None:
         """``capture`` for the unpadded form with a fixed row capacity: batches whose valid tokens fit it replay the
         same graph (feed with ``set_inputs`` + ``replay``; the result is ``self.out_padded``)."""
-        self._capture(B, S, min(B * S, int(capacity)))
+        self._capture(B, S, min(B * S, int(capacity)), slots)
 
-    def capture(self, B: int, S: int) -> None:
-        """Capture one pass for shape (B, S) into a CUDA graph; feed it with ``set_inputs`` + ``replay``."""
-        self._capture(B, S, None)
+    def capture(self, B: int, S: int, slots: int = 1) -> None:
+        """Capture one pass for shape (B, S) into a CUDA graph; feed it with ``set_inputs`` + ``replay``.
+        ``slots`` > 1 captures that many graphs of the same pass, each with its own input block and its own result
+        buffer (``inputs_of(k)``, ``result_of(k)``; slot 0 uses the object's own): a host loop can then fill the
+        inputs of batch i + 1 and read the result of batch i - 1 while batch i computes, without a copy in
+        between.  Intermediate buffers are shared: the graphs of one object run one after the other."""
+        self._capture(B, S, None, slots)
 
-    def _capture(self, B: int, S: int, packed_rows) -> None:
+    def _result(self) -> torch.Tensor:
+        return self.out if self._packed_rows is None else self.out_padded
+
+    def _capture(self, B: int, S: int, packed_rows, slots: int = 1) -> None:
+        if slots < 1:
+            raise ValueError("slots must be at least 1")
         self._prepare(B, S, packed_rows)
         side = torch.cuda.Stream(device=self.device)
         side.wait_stream(torch.cuda.current_stream())
@@ -248,17 +257,47 @@ class _EncoderBase:
             self._run()  # warm-up: sets kernel attributes, loads modules
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
-            self._run()
-        self._graph = g
+        base_micro = self._micro
+        res0 = self._result()
+        self._slot_inputs = [self.inputs] + [torch.zeros_like(self.inputs) for _ in range(slots - 1)]
+        self._slot_results = [res0] + [torch.empty_like(res0) for _ in range(slots - 1)]
+        self._graphs = []
+        for k in range(slots):
+            if k:
+                # the same launches with the slot's input block and result buffer in place of the object's own:
+                # every pointer argument that falls inside one of the two is moved by the same offset
+                spans = [(t0.data_ptr(), t0.numel() * t0.element_size(), t1.data_ptr())
+                         for t0, t1 in ((self.inputs, self._slot_inputs[k]), (res0, self._slot_results[k]))]
 
-    def replay(self) -> torch.Tensor:
+                def move(a):
+                    if isinstance(a, int) and not isinstance(a, bool):
+                        for lo, n, new in spans:
+                            if lo <= a < lo + n:
+                                return a - lo + new
+                    return a
+
+                self._micro = [[(f, name, tuple(move(a) for a in args)) for f, name, args in m] for m in base_micro]
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self._run()
+            self._graphs.append(g)
+        self._micro = base_micro
+        self._graph = self._graphs[0]
+
+    def inputs_of(self, slot: int) -> torch.Tensor:
+        """int32 ``[B*S + B]`` input block of a captured slot: token ids, then key lengths."""
+        return self._slot_inputs[slot]
+
+    def result_of(self, slot: int) -> torch.Tensor:
+        """Result buffer of a captured slot (written by ``replay(slot)``)."""
+        return self._slot_results[slot]
+
+    def replay(self, slot: int = 0) -> torch.Tensor:
         if self._graph is None:
             raise RuntimeError("capture() first")
-        self._graph.replay()
+        self._graphs[slot].replay()
         ops.launch_count += len(self._launches)
-        return self.out if self._packed_rows is None else self.out_padded
+        return self._slot_results[slot]
 
 
 class Fp16Encoder(_EncoderBase):

@@ -4,8 +4,10 @@ The reference feeds its encoders from host tensors and reads the result back aft
 (benchmarks/bert_mlperf.py:60-90); done naively that leaves the GPU idle for the length of the
 device->host copy of every batch (6.3 MB of hidden states: about 0.12 ms against 0.9 ms of compute).
 ``HostPipeline`` keeps the same per-batch contract - inputs come from pinned host memory, the hidden
-states of every batch land in pinned host memory - and moves the device->host copy of batch i to a copy
-stream, where it runs while batch i + 1 computes.
+states of every batch land in pinned host memory - and moves both copies off the compute stream: the
+encoder is captured once per slot (own input block, own result buffer), the host->device copy of batch
+i + 1 and the device->host copy of batch i - 1 run on copy streams while batch i computes, and nothing is
+copied from one device buffer to another.
 """
 from __future__ import annotations
 
@@ -26,13 +28,14 @@ class HostPipeline:
         if depth < 2:
             raise ValueError("depth must be at least 2")
         self.enc = encoder
-        encoder.capture(batch, seq)
+        encoder.capture(batch, seq, slots=depth)
         self.depth = depth
         self.gatherer = gatherer
         self.overlap_gather = bool(overlap_gather)
         self._gathers = [None] * depth
-        self.copy_stream = torch.cuda.Stream(device=encoder.device)
-        self.dev_out = [torch.empty_like(encoder.out) for _ in range(depth)]
+        self.copy_stream = torch.cuda.Stream(device=encoder.device)  # device -> host
+        self.in_stream = torch.cuda.Stream(device=encoder.device)    # host -> device
+        self.dev_out = [encoder.result_of(k) for k in range(depth)]
         self.host_out = [torch.empty(encoder.out.shape, dtype=encoder.out.dtype).pin_memory() for _ in range(depth)]
         # ids and key lengths travel as one pinned block (one host->device copy per batch instead of two)
         self.host_in = [torch.empty(encoder.inputs.numel(), dtype=torch.int32).pin_memory() for _ in range(depth)]
@@ -40,6 +43,7 @@ class HostPipeline:
         self._seq = seq
         self._copied = [None] * depth  # event: the slot's device->host copy has finished
         self._in_done = [None] * depth  # event: the slot's host->device copy has finished
+        self._computed = [None] * depth  # event: the slot's pass has finished (its input block may be rewritten)
         self._count = 0
 
     def submit(self, ids_host: torch.Tensor, kv_lens_host: torch.Tensor | None = None) -> int:
@@ -48,8 +52,6 @@ class HostPipeline:
         self._count += 1
         slot = ticket % self.depth
         main = torch.cuda.current_stream(self.enc.device)
-        if self._copied[slot] is not None:
-            main.wait_event(self._copied[slot])  # the slot's device buffer is free again
         if self._gathers[slot] is not None:
             self._gathers[slot].wait()
         staged = self.host_in[slot]
@@ -60,12 +62,19 @@ class HostPipeline:
             staged[self._n_ids:].copy_(kv_lens_host)
         else:
             staged[self._n_ids:].fill_(self._seq)
-        self.enc.set_inputs_packed(staged)  # host -> device, asynchronous on the compute stream
-        self._in_done[slot] = torch.cuda.Event()
-        self._in_done[slot].record(main)
-        self.enc.replay()
-        # the encoder's output buffer is overwritten by the first kernel of the next pass: park the result
-        self.dev_out[slot].copy_(self.enc.out, non_blocking=True)
+        # host -> device on its own stream, as soon as the pass that last read the slot's input block is over
+        if self._computed[slot] is not None:
+            self.in_stream.wait_event(self._computed[slot])
+        with torch.cuda.stream(self.in_stream):
+            self.enc.inputs_of(slot).copy_(staged, non_blocking=True)
+            self._in_done[slot] = torch.cuda.Event()
+            self._in_done[slot].record(self.in_stream)
+        main.wait_event(self._in_done[slot])
+        if self._copied[slot] is not None:
+            main.wait_event(self._copied[slot])  # the slot's result buffer has reached the host
+        self.enc.replay(slot)
+        self._computed[slot] = torch.cuda.Event()
+        self._computed[slot].record(main)
         if self.gatherer is not None:
             self._gathers[slot] = self.gatherer.gather_async(self.dev_out[slot], slot)
             if not self.overlap_gather:
