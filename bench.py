@@ -568,6 +568,7 @@ def run_ours(args) -> None:
         peer = PeerGatherer(wl["global_batch"], S, cfg.hidden, torch.float16, dev, root=0, depth=3)
         parked = [torch.empty_like(enc.out) for _ in range(peer.depth)]
     ticket = [0]
+    collected = [0]  # rank 0: tickets below this one have been waited for and released (each exactly once)
 
     l2_flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # 2 x the 126 MB L2
 
@@ -594,18 +595,19 @@ def run_ours(args) -> None:
                 # the previous step's push is part of this step's timed region: it must have finished by now
                 torch.cuda.current_stream().wait_event(peer.pushed(t - 1))
             lag = peer.depth - 1
-            if rank == 0 and t >= lag:
-                peer.wait(t - lag)  # host-side: every shard of that ticket has landed in rank 0's buffer
-                peer.release(t - lag)
+            while rank == 0 and collected[0] <= t - lag:
+                peer.wait(collected[0])  # host-side: every shard of that ticket has landed in rank 0's buffer
+                peer.release(collected[0])
+                collected[0] += 1
 
     def finish_gathers():
         """Rank 0 collects the tickets still in flight; every rank's queued copies complete."""
         if peer is None:
             return
-        if rank == 0:
-            for t in range(max(0, ticket[0] - (peer.depth - 1)), ticket[0]):
-                peer.wait(t)
-                peer.release(t)
+        while rank == 0 and collected[0] < ticket[0]:
+            peer.wait(collected[0])
+            peer.release(collected[0])
+            collected[0] += 1
         peer.drain()
 
     # End to end through the public host API (zenith_b200.serve.HostPipeline): every step copies its ids /

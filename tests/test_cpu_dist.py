@@ -101,6 +101,15 @@ def _peer_worker(rank, world, port, gb, silent_rank, out):
                     full = pg.wait(t)
                     ok = ok and bool(torch.equal(full, want + 100 * t))
                     pg.release(t)
+            if rank == 0:
+                # a ticket is collected once: its slot may hold a later ticket afterwards, so a second wait is refused
+                # (it would never return) and so is a release out of order
+                for bad in (lambda: pg.wait(steps - 1), lambda: pg.release(steps - 1), lambda: pg.release(steps + 1)):
+                    try:
+                        bad()
+                        ok = False
+                    except RuntimeError as e:
+                        ok = ok and ("released" in str(e))
             out[rank] = ok
         else:
             # one rank never pushes: the root's wait runs out on the host and raises instead of hanging

@@ -213,6 +213,7 @@ class PeerGatherer:
         self._aux_stream = torch.cuda.Stream(device=raw.device) if self.cuda else None  # polling reads of the root's memory
         self._pushed = [None] * self.depth
         self._seen_consumed = [0] * self.depth
+        self._released = -1  # root: the last ticket released (tickets are waited for and released in order, once each)
         self._mine = slice(self.bounds[self.rank][0] * seq, (self.bounds[self.rank][0] + self.bounds[self.rank][1]) * seq)
 
     def _seq_of(self, ticket: int) -> int:
@@ -281,6 +282,9 @@ class PeerGatherer:
         ``[global_batch * seq, hidden]``, valid until ``release(ticket)``."""
         if self.rank != self.root:
             raise RuntimeError("only the root waits for a gathered ticket")
+        if ticket <= self._released:
+            # its slot may already hold a later ticket: the flags would never match again
+            raise RuntimeError(f"ticket {ticket} has been released already (last released: {self._released})")
         slot, want = ticket % self.depth, self._seq_of(ticket)
         self._poll(f"the shards of ticket {ticket}", lambda: all(v == want for v in self._read(self.flags[slot])))
         return self.data[slot]
@@ -289,6 +293,9 @@ class PeerGatherer:
         """Root only: the slot of ``ticket`` may be overwritten (ordered after the calling stream's reads of it)."""
         if self.rank != self.root:
             raise RuntimeError("only the root releases a ticket")
+        if ticket != self._released + 1:
+            raise RuntimeError(f"tickets are released in order, once each: expected {self._released + 1}, got {ticket}")
+        self._released = ticket
         slot, seq_no = ticket % self.depth, self._seq_of(ticket)
         if self.cuda:
             main = torch.cuda.current_stream(self.device)
