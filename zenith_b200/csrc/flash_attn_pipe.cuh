@@ -6,7 +6,15 @@
 //   warps 6..9  : softmax group B (query rows 128..255)
 //
 // K and V are loaded once for 256 queries, and while one group runs its softmax the tensor core
-// works for the other (S = Q K^T of the next block, O += P V of the current one).  O accumulates in
+// works for the other (S = Q K^T of the next block, O += P V of the current one).  A softmax thread
+// takes its whole row of S (128 values) into registers in one trip through tensor memory and
+// releases the S columns at once, so that Q K^T of the group's next block runs under the softmax
+// of this one; the issuer serves both groups' events (S read, P ready) in the order they occur.
+// Moving a share of the exponentials from the special-function unit to a cubic on the FMA / integer pipes
+// (round-to-nearest split, 2^f on [-0.5, 0.5], exponent add: about ten issue slots per column pair against
+// two) was measured at 25 / 50 / 75 / 100 % of the pairs and lost at every share (head size 64, S = 8192:
+// 563 TFLOP/s without it, 533 / 545 / 457 / 409 with it): with two softmax warps per scheduler the loop is
+// bound by instruction issue and dependent-instruction latency, not by the unit's 16 results per clock.  O accumulates in
 // TMEM across key blocks (tcgen05.mma with the accumulate flag); the running maximum used for
 // scaling is only moved, and O rescaled in TMEM by tcgen05.ld / st, when the row maximum has grown
 // by more than 2^8 since the last move, so that the rescale is rare after the first blocks and P
@@ -52,7 +60,8 @@ flash_attn_pipe_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
   uint64_t* s_full = v_empty + KV_STAGES;          // [2] per group
   uint64_t* p_full = s_full + 2;                   // [2]
   uint64_t* o_full = p_full + 2;                   // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 2);
+  uint64_t* s_free = o_full + 2;                   // [2] the group has taken S into registers
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_free + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -82,6 +91,7 @@ flash_attn_pipe_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       mbar_init(&s_full[g], 1);
       mbar_init(&p_full[g], 128);
       mbar_init(&o_full[g], 1);
+      mbar_init(&s_free[g], 128);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -170,33 +180,58 @@ flash_attn_pipe_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         if (nblk[1] > 0) issue_qk(1, 0);
         tc_commit(&k_empty[0]);
       }
-      for (int j = 0; j < n_blocks && ok; ++j) {
-        const int st = j % KV_STAGES;
-        const bool next = j + 1 < n_blocks;
-        bool k_next_ready = false;
+      // Both groups' events are served in the order they occur: "S(j) has been read" lets Q K^T of block j + 1 go
+      // (its K tile permitting), "P(j) is ready" lets P V of block j go (its V tile permitting).  A K / V stage is
+      // released when every group that needs the block has issued its product.
+      int qk_next[2] = {1, 1};  // block whose Q K^T is issued next (block 0 went out above)
+      int pv_next[2] = {0, 0};
+      uint32_t qk_half = 0, pv_half = 0;  // bit (j & 3): one of the two groups that need block j has been served
+      auto needed = [&](int j) { return (j < nblk[0] ? 1 : 0) + (j < nblk[1] ? 1 : 0); };
+      // true when every group that needs block j has been served (the groups never drift 4 blocks apart: a K / V
+      // stage is refilled only after both have used it)
+      auto all_served = [&](uint32_t& mask, int j) -> bool {
+        if (needed(j) == 1) return true;
+        const uint32_t bit = 1u << (j & 3);
+        mask ^= bit;
+        return (mask & bit) == 0;
+      };
+      uint64_t t_last = global_timer_ns();  // time of the last product issued: the wait for the next event is bounded
+      uint32_t spins = 0;
+      while (ok && (pv_next[0] < nblk[0] || pv_next[1] < nblk[1])) {
+        bool progress = false;
 #pragma unroll
         for (int g = 0; g < 2; ++g) {
-          if (j < nblk[g]) {
-            // P_g(j) is in shared memory; S_g(j) has been read; O_g has been rescaled if it had to be
-            if (!mbar_wait(&p_full[g], j & 1, abort_flag)) { ok = false; break; }
-            if (g == 0 || nblk[0] <= j) {
-              if (!mbar_wait(&v_full[st], (j / KV_STAGES) & 1, abort_flag)) { ok = false; break; }
-            }
+          const int jn = qk_next[g];
+          if (jn < nblk[g] && mbar_try_wait(&s_free[g], (jn - 1) & 1) &&
+              mbar_try_wait(&k_full[jn % KV_STAGES], (jn / KV_STAGES) & 1)) {
             tc_fence_after_sync();
-            issue_pv(g, j);
+            issue_qk(g, jn);
+            qk_next[g] = jn + 1;
+            if (all_served(qk_half, jn)) tc_commit(&k_empty[jn % KV_STAGES]);  // K(jn) consumed by every group that needs it
+            progress = true;
           }
-          if (next && j + 1 < nblk[g]) {
-            if (!k_next_ready) {
-              if (!mbar_wait(&k_full[(j + 1) % KV_STAGES], ((j + 1) / KV_STAGES) & 1, abort_flag)) { ok = false; break; }
-              tc_fence_after_sync();
-              k_next_ready = true;
-            }
-            issue_qk(g, j + 1);
+          const int jp = pv_next[g];
+          if (jp < nblk[g] && mbar_try_wait(&p_full[g], jp & 1) &&
+              mbar_try_wait(&v_full[jp % KV_STAGES], (jp / KV_STAGES) & 1)) {
+            // P_g(jp) is in shared memory; O_g has been rescaled if it had to be
+            tc_fence_after_sync();
+            issue_pv(g, jp);
+            pv_next[g] = jp + 1;
+            if (all_served(pv_half, jp)) tc_commit(&v_empty[jp % KV_STAGES]);  // V(jp) consumed
+            progress = true;
           }
         }
-        if (!ok) break;
-        tc_commit(&v_empty[st]);                                  // V(j) consumed by both groups' P V
-        if (next) tc_commit(&k_empty[(j + 1) % KV_STAGES]);       // K(j+1) consumed by both groups' Q K^T
+        if (progress) {
+          t_last = global_timer_ns();
+          spins = 0;
+        } else if ((++spins & 0x3f) == 0) {
+          if (*abort_flag) ok = false;
+          else if (global_timer_ns() - t_last > ZEN_WAIT_LIMIT_NS) {
+            *abort_flag = 1;
+            record_status(ZEN_ERR_TIMEOUT);
+            ok = false;
+          }
+        }
       }
     }
   } else {
@@ -220,24 +255,29 @@ flash_attn_pipe_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       const int key0 = j * 128;
       int lim = kv_len - key0;
       if (p.causal && q + 1 - key0 < lim) lim = q + 1 - key0;
-      // pass 1: row maximum of this block (four independent chains; no predicates when the block is
-      // entirely valid for this row)
+      // the whole row of S in registers, in one trip through tensor memory; the S columns are then free for
+      // Q K^T of the group's next block
       const bool full_blk = lim >= 128;
-      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t sv[32];
-        __syncwarp();
-        tmem_ld_32x32(tmem_s + lane_sel + c * 32, sv);
-        tmem_wait_ld();
-        if (full_blk) {
+      uint32_t sv[4][32];
+      __syncwarp();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[i]));
-        } else {
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32(tmem_s + lane_sel + c * 32, sv[c]);
+      tmem_wait_ld();
+      tc_fence_before_sync();
+      mbar_arrive(&s_free[g]);
+      // row maximum of this block (four independent chains; no predicates when the block is entirely valid)
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      if (full_blk) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[c][i]));
+      } else {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
 #pragma unroll
           for (int i = 0; i < 32; ++i)
-            if (c * 32 + i < lim) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[i]));
-        }
+            if (c * 32 + i < lim) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[c][i]));
       }
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       const float m_blk = mx * p.scale_log2;
@@ -251,58 +291,52 @@ flash_attn_pipe_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         if (!mbar_wait(&o_full[g], (j - 1) & 1, abort_flag)) { ok = false; break; }
         tc_fence_after_sync();
         if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+          // (16 columns at a time: the row of S occupies most of the thread's registers)
 #pragma unroll 1
-          for (int c = 0; c < D / 32; ++c) {
-            uint32_t ov[32];
+          for (int c = 0; c < D / 16; ++c) {
+            uint32_t ov[16];
             __syncwarp();
-            tmem_ld_32x32(tmem_o + lane_sel + c * 32, ov);
+            tmem_ld_32x16(tmem_o + lane_sel + c * 16, ov);
             tmem_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
-            tmem_st_32x32(tmem_o + lane_sel + c * 32, ov);
+            for (int i = 0; i < 16; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+            tmem_st_32x16(tmem_o + lane_sel + c * 16, ov);
           }
           tmem_wait_st();
           l_run *= alpha;
         }
       }
       m_ref = m_new;
-      // pass 2: probabilities -> shared memory (fp16, swizzled K-major), row sum
-      float rs4[4] = {0.f, 0.f, 0.f, 0.f};
-      const float neg_m = -m_use;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t sv[32];
-        __syncwarp();
-        tmem_ld_32x32(tmem_s + lane_sel + c * 32, sv);
-        tmem_wait_ld();
-        uint32_t pk[16];
-        if (full_blk) {
+      // probabilities -> shared memory (fp16, swizzled K-major), row sum; column pairs on the packed fp32x2
+      // instructions
+      float2 rs2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+      const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
+      const float2 nm2 = make_float2(-m_use, -m_use);
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const float a = fast_exp2(fmaf(__uint_as_float(sv[2 * i]), p.scale_log2, neg_m));
-            const float bq = fast_exp2(fmaf(__uint_as_float(sv[2 * i + 1]), p.scale_log2, neg_m));
-            rs4[i & 3] += a + bq;
-            const __half2 hh = __floats2half2_rn(a, bq);
-            pk[i] = *reinterpret_cast<const uint32_t*>(&hh);
-          }
-        } else {
+      for (int hc = 0; hc < 8; ++hc) {  // 16 columns (8 pairs, two 16-byte units of the P row) at a time
+        const int c = hc >> 1;          // 32-column chunk of S
+        uint32_t pk[8];
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const float a = (c * 32 + 2 * i < lim) ? fast_exp2(fmaf(__uint_as_float(sv[2 * i]), p.scale_log2, neg_m)) : 0.f;
-            const float bq =
-                (c * 32 + 2 * i + 1 < lim) ? fast_exp2(fmaf(__uint_as_float(sv[2 * i + 1]), p.scale_log2, neg_m)) : 0.f;
-            rs4[i & 3] += a + bq;
-            const __half2 hh = __floats2half2_rn(a, bq);
-            pk[i] = *reinterpret_cast<const uint32_t*>(&hh);
+        for (int ii = 0; ii < 8; ++ii) {
+          const int i = (hc & 1) * 8 + ii;  // pair within the chunk
+          const float2 x = f2fma(make_float2(__uint_as_float(sv[c][2 * i]), __uint_as_float(sv[c][2 * i + 1])), sc2, nm2);
+          float2 e = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+          if (!full_blk) {
+            e.x = (c * 32 + 2 * i < lim) ? e.x : 0.f;
+            e.y = (c * 32 + 2 * i + 1 < lim) ? e.y : 0.f;
           }
+          rs2[i & 1] = f2add(rs2[i & 1], e);
+          const __half2 hh = __floats2half2_rn(e.x, e.y);
+          pk[ii] = *reinterpret_cast<const uint32_t*>(&hh);
         }
         uint8_t* prow = myP + (c >> 1) * CHUNK_BYTES + r * 128;
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int unit = ((c & 1) * 4 + u) ^ (r & 7);
+        for (int u = 0; u < 2; ++u) {
+          const int unit = ((c & 1) * 4 + (hc & 1) * 2 + u) ^ (r & 7);
           *reinterpret_cast<uint4*>(prow + unit * 16) = make_uint4(pk[4 * u], pk[4 * u + 1], pk[4 * u + 2], pk[4 * u + 3]);
         }
       }
+      const float rs4[4] = {rs2[0].x, rs2[0].y, rs2[1].x, rs2[1].y};
       const float rowsum = (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
       l_run += rowsum;
       tc_fence_before_sync();
