@@ -14,7 +14,11 @@
 // (round-to-nearest split, 2^f on [-0.5, 0.5], exponent add: about ten issue slots per column pair against
 // two) was measured at 25 / 50 / 75 / 100 % of the pairs and lost at every share (head size 64, S = 8192:
 // 563 TFLOP/s without it, 533 / 545 / 457 / 409 with it): with two softmax warps per scheduler the loop is
-// bound by instruction issue and dependent-instruction latency, not by the unit's 16 results per clock.  O accumulates in
+// bound by instruction issue and dependent-instruction latency, not by the unit's 16 results per clock.
+// Two threads per row (16 softmax warps per CTA, block maximum and row sum exchanged through shared memory,
+// as in the fused QKV + attention kernel) was also built and measured: 561 / 957 TFLOP/s at head size 64 /
+// 128 against 563 / 1002 with one thread per row; profiler counters of that form: issue slots 48 % busy,
+// special-function unit 50 %, ALU 47 %, tensor pipe 24 %, 7.7 thread-instructions per score.  O accumulates in
 // TMEM across key blocks (tcgen05.mma with the accumulate flag); the running maximum used for
 // scaling is only moved, and O rescaled in TMEM by tcgen05.ld / st, when the row maximum has grown
 // by more than 2^8 since the last move, so that the rescale is rare after the first blocks and P
