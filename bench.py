@@ -735,8 +735,9 @@ def run_ours(args) -> None:
         "e2e": {"value": e2e_value, "unit": "sequences/s", "ms_per_step": e2e_ms / K,
                 "h2d_bytes_per_step": int(ids_h.numel() * ids_h.element_size() + lens_h.numel() * lens_h.element_size()),
                 "d2h_bytes_per_step": int(pipe.host_out[0].numel() * 2),
-                "how": "zenith_b200.serve.HostPipeline: one event pair around all steps; per step pinned-host ids -> device, "
-                       "graph replay, hidden states -> pinned host on a copy stream that overlaps the next step's compute; "
+                "how": "zenith_b200.serve.HostPipeline: one event pair around all steps; per step pinned-host ids -> device on an "
+                       "input stream, replay of the slot's graph (own inputs, own result buffer), hidden states -> pinned host "
+                       "on a copy stream; both copies overlap the neighbouring steps' compute; "
                        "no L2 flush in this loop (a step's working set of weights + activations exceeds the 126 MB L2); "
                        "with several GPUs every rank delivers its own shard to host memory (bytes are per rank)",
                 "launches_per_step": e2e_launches},
