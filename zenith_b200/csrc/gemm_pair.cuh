@@ -24,7 +24,7 @@ __host__ __device__ constexpr size_t gemm_pair_smem_bytes() {
   // ring (A 16 KB + B BN/2 x 128 B per stage) + output staging (4 KB per active epilogue warp) + barriers / flags
   // (256 B) + per-epilogue-warp scale and bias entries + alignment slack
   return size_t(STAGES) * (GEMM_BM * 128 + (BN / 2) * 128) + size_t((BN + 63) / 64) * 4 * 4096 + 256 +
-         size_t(GEMM_EPI_WARPS) * 2 * 64 * 4 + 1024;
+         size_t(GEMM_EPI_WARPS) * 3 * 64 * 4 + 1024;
 }
 
 template <int KIND>

@@ -90,7 +90,7 @@ __host__ __device__ constexpr size_t gemm_smem_bytes() {
   // ring + output staging (4 KB per active epilogue warp) + barriers/flags (256 B) + per-epilogue-warp
   // scale and bias entries + alignment slack
   return size_t(STAGES) * (GEMM_BM * 128 + BN * 128) + size_t((BN + 63) / 64) * 4 * 4096 + 256 +
-         size_t(GEMM_EPI_WARPS) * 2 * 64 * 4 + 1024;
+         size_t(GEMM_EPI_WARPS) * 3 * 64 * 4 + 1024;
 }
 
 template <int KIND>
@@ -310,19 +310,40 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[GEMM_CW], con
 // ---------------------------------------------------------------------------------------------
 // The FP32 arithmetic runs on column pairs with the packed fp32x2 instructions of sm_100 (individually
 // rounded, so bit-identical to the scalar forms): one issue slot for two operations.
+// The fast path differs from the definition in two places, both covered by the boundary test:
+// * it dequantises with ONE fused multiply-add, y' = fl(acc * c + b), c = fl(x_scale * w_scale[n]), instead of the
+//   definition's three rounded operations y = fl(fl(fl(acc * x_scale) * w_scale) + b): with u = 2^-24,
+//   |y' - y| <= 3u |acc x_scale w_scale| + 2u |y| <= 3.0e-7 |y| + 1.8e-7 |b|; through the activation (|gelu'| <= 1.13,
+//   |y gelu'(y)| <= 0.2 for y < 0, |y| <= gelu(y) + 0.17 for y > 0) and the output scale that is at most
+//   3.4e-7 |t| + inv_scale (6e-8 + 2.1e-7 |b|) in t = act(y) / out_scale.  The test flags every element whose t lies
+//   within 5e-6 |t| + 2e-6 + inv_scale (1.6e-7 + 4.2e-7 max|b|) of a rounding boundary (the first two terms cover the
+//   approximate exponential / reciprocal and the reciprocal multiply; the last is the bound above, doubled);
+// * it does not clamp in floating point: the rounded integers are saturated when they are packed.  rint(t) through
+//   the 1.5 * 2^23 constant is exact for |t| < 2^22, and any larger |t| fails the test (5e-6 |t| alone exceeds 0.5
+//   from |t| = 100000 on), as does a NaN (the comparison counts an unordered result as "near a boundary").  Values far
+//   outside the int8 range are flagged more often than values inside it: a cost only for an output scale chosen far
+//   too small.
+// Flagged elements are recomputed with the definition itself (requant_i8_fixup).
+//
+// four 32-bit integers -> four int8 with saturation, byte k = value k (two cvt.pack instructions)
+__device__ __forceinline__ uint32_t pack_sat_s8x4(uint32_t i0, uint32_t i1, uint32_t i2, uint32_t i3) {
+  uint32_t hi, w;
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(i3), "r"(i2), "r"(0u));
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(w) : "r"(i1), "r"(i0), "r"(hi));
+  return w;
+}
 template <int ACT>
-__device__ __forceinline__ uint32_t requant_i8_step(const uint32_t (&r)[GEMM_CW], const float* sc, const float* bi,
-                                                    float x_scale, float inv_scale, uint32_t (&w)[GEMM_CW / 4]) {
+__device__ __forceinline__ uint32_t requant_i8_step(const uint32_t (&r)[GEMM_CW], const float* fold, const float* bi,
+                                                    float risk_thr, float inv_scale, uint32_t (&w)[GEMM_CW / 4]) {
   constexpr float MAGIC = 12582912.0f;  // 1.5 * 2^23
   const float2 neg_magic = make_float2(-MAGIC, -MAGIC);
   const float2 pos_magic = make_float2(MAGIC, MAGIC);
-  const float2 xs2 = make_float2(x_scale, x_scale);
   const float2 inv2 = make_float2(inv_scale, inv_scale);
   uint32_t span = 0;
   uint32_t risky = 0;
 #pragma unroll
   for (int j4 = 0; j4 < GEMM_CW / 4; ++j4) {
-    const float4 s4 = reinterpret_cast<const float4*>(sc)[j4];
+    const float4 s4 = reinterpret_cast<const float4*>(fold)[j4];
     const float4 b4 = reinterpret_cast<const float4*>(bi)[j4];
     uint32_t mb[4];
 #pragma unroll
@@ -334,7 +355,7 @@ __device__ __forceinline__ uint32_t requant_i8_step(const uint32_t (&r)[GEMM_CW]
       const float2 a = f2add(make_float2(__uint_as_float(t0), __uint_as_float(t1)), neg_magic);  // == float(acc), exact
       const float2 ss = h ? make_float2(s4.z, s4.w) : make_float2(s4.x, s4.y);
       const float2 bb = h ? make_float2(b4.z, b4.w) : make_float2(b4.x, b4.y);
-      float2 g = f2mul_then_add(f2mul(a, xs2), ss, bb);  // == zen_det_dequant (product rounded before the bias add)
+      float2 g = f2fma(a, ss, bb);  // one rounding instead of zen_det_dequant's three
       if constexpr (ACT == ZEN_ACT_GELU) {
         // gelu_fast on both halves: x / (1 + 2^(v * c)), v = x (1 + 0.044715 x^2)
         const float2 x2 = f2mul(g, g);
@@ -347,16 +368,15 @@ __device__ __forceinline__ uint32_t requant_i8_step(const uint32_t (&r)[GEMM_CW]
       if constexpr (ACT == ZEN_ACT_RELU) g = make_float2(fmaxf(g.x, 0.0f), fmaxf(g.y, 0.0f));
       const float2 t = f2mul(g, inv2);
       // NaN -> -128, as in the exact definition
-      const float2 tc = make_float2(fminf(fmaxf(t.x, -128.0f), 127.0f), fminf(fmaxf(t.y, -128.0f), 127.0f));
-      const float2 m = f2add(tc, pos_magic);  // low mantissa byte == int8 bits of rint(tc)
-      const float2 d = f2fma(f2add(m, neg_magic), make_float2(-1.0f, -1.0f), tc);  // tc - rint(tc), exact
-      // |tc - rint(tc)| close to 0.5 <=> close to a rounding boundary (a clamped value has distance 0)
-      if (fmaf(fabsf(tc.x), 4e-6f, fabsf(d.x)) > 0.5f - 2e-6f) risky |= 1u << j;
-      if (fmaf(fabsf(tc.y), 4e-6f, fabsf(d.y)) > 0.5f - 2e-6f) risky |= 1u << (j + 1);
-      mb[2 * h] = __float_as_uint(m.x);
-      mb[2 * h + 1] = __float_as_uint(m.y);
+      const float2 m = f2add(t, pos_magic);  // mantissa == 2^22 + rint(t) in two's complement
+      const float2 d = f2fma(f2add(m, neg_magic), make_float2(-1.0f, -1.0f), t);  // t - rint(t), exact
+      // |t - rint(t)| close to 0.5 <=> close to a rounding boundary
+      if (!(fmaf(fabsf(t.x), 5e-6f, fabsf(d.x)) <= risk_thr)) risky |= 1u << j;
+      if (!(fmaf(fabsf(t.y), 5e-6f, fabsf(d.y)) <= risk_thr)) risky |= 1u << (j + 1);
+      mb[2 * h] = __float_as_uint(m.x) - 0x4B400000u;  // rint(t) as a 32-bit integer
+      mb[2 * h + 1] = __float_as_uint(m.y) - 0x4B400000u;
     }
-    w[j4] = __byte_perm(__byte_perm(mb[0], mb[1], 0x0040), __byte_perm(mb[2], mb[3], 0x0040), 0x5410);
+    w[j4] = pack_sat_s8x4(mb[0], mb[1], mb[2], mb[3]);
   }
   return span >= 0x00800000u ? (1u << GEMM_CW) - 1u : risky;
 }
@@ -384,10 +404,11 @@ __device__ __noinline__ void requant_i8_fixup(uint32_t taddr, const float* sc, c
 // One step of the int8 -> int8 nearest-even epilogue (all 32 lanes must call it).
 template <int ACT>
 __device__ __forceinline__ void epilogue_step_s8(const uint32_t (&r)[GEMM_CW], uint32_t taddr, const float* sc,
-                                                 const float* bi, const GemmParams& p, int row, int col0, bool row_ok,
-                                                 bool vec_ok, float inv_scale, uint8_t* stage, int lane, int istep) {
+                                                 const float* bi, const float* fold, float risk_thr, const GemmParams& p,
+                                                 int row, int col0, bool row_ok, bool vec_ok, float inv_scale,
+                                                 uint8_t* stage, int lane, int istep) {
   uint32_t w[GEMM_CW / 4];
-  uint32_t redo = requant_i8_step<ACT>(r, sc, bi, p.x_scale, inv_scale, w);
+  uint32_t redo = requant_i8_step<ACT>(r, fold, bi, risk_thr, inv_scale, w);
   const int nvalid = p.N - col0;
   int8_t* dst;
   bool live;
@@ -459,8 +480,9 @@ __device__ __forceinline__ void gemm_epilogue_role(const GemmParams& p, const CU
   const int sub = (warp - 2) >> 2;  // 64-column slab of the tile owned by this warp
   constexpr int STEPS = 64 / GEMM_CW;
   if (sub * 64 < BN) {
-    float* s_scale = epi_rows + (warp - 2) * 2 * 64;
+    float* s_scale = epi_rows + (warp - 2) * 3 * 64;
     float* s_bias = s_scale + 64;
+    float* s_fold = s_bias + 64;  // fl(x_scale * w_scale[n]): the one-multiply form of the int8 -> int8 fast path
     const int slab_cols = (BN - sub * 64) < 64 ? (BN - sub * 64) : 64;
     const int elem = p.out_dtype == ZEN_DT_S8 ? 1 : p.out_dtype == ZEN_DT_F16 ? 2 : 4;
     const bool vec_ok = (reinterpret_cast<uintptr_t>(p.out) % 16 == 0) && ((p.ldo * elem) % 16 == 0);
@@ -494,7 +516,12 @@ __device__ __forceinline__ void gemm_epilogue_role(const GemmParams& p, const CU
       for (int u = 0; u < 2; ++u) {
         s_scale[lane + 32 * u] = sv[u];
         s_bias[lane + 32 * u] = bv[u];
+        s_fold[lane + 32 * u] = ZEN_MUL(p.x_scale, sv[u]);
       }
+      // Rounding-boundary test of the int8 -> int8 fast path (see requant_i8_step): the largest |bias| of the slab
+      // (non-negative floats order like their bit patterns) bounds what the folded dequantisation can be off by.
+      const float bmax = __int_as_float(__reduce_max_sync(0xffffffffu, max(__float_as_int(fabsf(bv[0])), __float_as_int(fabsf(bv[1])))));
+      const float risk_thr = 0.5f - 2e-6f - inv_scale * fmaf(4.2e-7f, bmax, 1.6e-7f);
       if (tile + tile_step < num_tiles) fetch_cols(tile + tile_step, sv, bv);
       if (staged) {
         if (lane == 0) tma_store_wait_read();  // the previous tile's store has finished reading the block
@@ -520,13 +547,14 @@ __device__ __forceinline__ void gemm_epilogue_role(const GemmParams& p, const CU
           if (p.out_dtype == ZEN_DT_S8 && p.round_mode == 0) {
             const float* sc = s_scale + i * GEMM_CW;
             const float* bi = s_bias + i * GEMM_CW;
+            const float* fo = s_fold + i * GEMM_CW;
             const uint32_t ta = tacc + uint32_t(i * GEMM_CW);
             if (p.act == ZEN_ACT_GELU)
-              epilogue_step_s8<ZEN_ACT_GELU>(r, ta, sc, bi, p, row, col0, row_ok, vec_ok, inv_scale, stage, lane, i);
+              epilogue_step_s8<ZEN_ACT_GELU>(r, ta, sc, bi, fo, risk_thr, p, row, col0, row_ok, vec_ok, inv_scale, stage, lane, i);
             else if (p.act == ZEN_ACT_RELU)
-              epilogue_step_s8<ZEN_ACT_RELU>(r, ta, sc, bi, p, row, col0, row_ok, vec_ok, inv_scale, stage, lane, i);
+              epilogue_step_s8<ZEN_ACT_RELU>(r, ta, sc, bi, fo, risk_thr, p, row, col0, row_ok, vec_ok, inv_scale, stage, lane, i);
             else
-              epilogue_step_s8<ZEN_ACT_NONE>(r, ta, sc, bi, p, row, col0, row_ok, vec_ok, inv_scale, stage, lane, i);
+              epilogue_step_s8<ZEN_ACT_NONE>(r, ta, sc, bi, fo, risk_thr, p, row, col0, row_ok, vec_ok, inv_scale, stage, lane, i);
             continue;
           }
         }
