@@ -325,13 +325,6 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[GEMM_CW], con
 //   too small.
 // Flagged elements are recomputed with the definition itself (requant_i8_fixup).
 //
-// four 32-bit integers -> four int8 with saturation, byte k = value k (two cvt.pack instructions)
-__device__ __forceinline__ uint32_t pack_sat_s8x4(uint32_t i0, uint32_t i1, uint32_t i2, uint32_t i3) {
-  uint32_t hi, w;
-  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(i3), "r"(i2), "r"(0u));
-  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(w) : "r"(i1), "r"(i0), "r"(hi));
-  return w;
-}
 template <int ACT>
 __device__ __forceinline__ uint32_t requant_i8_step(const uint32_t (&r)[GEMM_CW], const float* fold, const float* bi,
                                                     float risk_thr, float inv_scale, uint32_t (&w)[GEMM_CW / 4]) {

@@ -469,9 +469,19 @@ __device__ __forceinline__ float2 f2mul_then_add(float2 a, float2 b, float2 c) {
   return make_float2(__fadd_rn(p.x, c.x), __fadd_rn(p.y, c.y));
 }
 
+// four 32-bit integers -> four int8 with saturation, byte k = value k (two cvt.pack instructions)
+__device__ __forceinline__ uint32_t pack_sat_s8x4(uint32_t i0, uint32_t i1, uint32_t i2, uint32_t i3) {
+  uint32_t hi, w;
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(i3), "r"(i2), "r"(0u));
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(w) : "r"(i1), "r"(i0), "r"(hi));
+  return w;
+}
+
 // quantize_fast_rn on column pairs with the packed fp32x2 instructions, packed straight to bytes: w[] receives
-// the int8 values four to a word (the low mantissa byte of t + 1.5 * 2^23 is the two's-complement byte),
-// the returned mask flags the values to recompute with the true division (patch them with patch_q_byte).
+// the int8 values four to a word, the returned mask flags the values to recompute with the true division (patch
+// them with patch_q_byte).  t = x * inv_scale is rounded through the 1.5 * 2^23 constant (exact for |t| < 2^22) and
+// saturated when it is packed; there is no clamp in floating point: any |t| >= 125000 fails the boundary test by
+// its relative term alone, and a NaN fails it because the comparison counts an unordered result as flagged.
 template <int N>
 __device__ __forceinline__ uint32_t quantize_pairs_rn(const float2 (&x)[N / 2], float inv_scale, uint32_t (&w)[N / 4]) {
   constexpr float MAGIC = 12582912.0f;
@@ -482,18 +492,15 @@ __device__ __forceinline__ uint32_t quantize_pairs_rn(const float2 (&x)[N / 2], 
 #pragma unroll
   for (int j = 0; j < N / 2; ++j) {
     const float2 t = f2mul(x[j], inv2);
-    // NaN -> -128, as in the definition
-    const float2 tc = make_float2(fminf(fmaxf(t.x, -128.0f), 127.0f), fminf(fmaxf(t.y, -128.0f), 127.0f));
-    const float2 m = f2add(tc, pm);
-    const float2 d = f2fma(f2add(m, nm), neg1, tc);  // tc - rint(tc), exact
-    if (fmaf(fabsf(tc.x), 4e-6f, fabsf(d.x)) > 0.5f - 2e-6f) risky |= 1u << (2 * j);
-    if (fmaf(fabsf(tc.y), 4e-6f, fabsf(d.y)) > 0.5f - 2e-6f) risky |= 1u << (2 * j + 1);
-    mb[2 * j] = __float_as_uint(m.x);
-    mb[2 * j + 1] = __float_as_uint(m.y);
+    const float2 m = f2add(t, pm);
+    const float2 d = f2fma(f2add(m, nm), neg1, t);  // t - rint(t), exact
+    if (!(fmaf(fabsf(t.x), 4e-6f, fabsf(d.x)) <= 0.5f - 2e-6f)) risky |= 1u << (2 * j);
+    if (!(fmaf(fabsf(t.y), 4e-6f, fabsf(d.y)) <= 0.5f - 2e-6f)) risky |= 1u << (2 * j + 1);
+    mb[2 * j] = __float_as_uint(m.x) - 0x4B400000u;  // rint(t) as a 32-bit integer
+    mb[2 * j + 1] = __float_as_uint(m.y) - 0x4B400000u;
   }
 #pragma unroll
-  for (int k = 0; k < N / 4; ++k)
-    w[k] = __byte_perm(__byte_perm(mb[4 * k], mb[4 * k + 1], 0x0040), __byte_perm(mb[4 * k + 2], mb[4 * k + 3], 0x0040), 0x5410);
+  for (int k = 0; k < N / 4; ++k) w[k] = pack_sat_s8x4(mb[4 * k], mb[4 * k + 1], mb[4 * k + 2], mb[4 * k + 3]);
   return risky;
 }
 // replaces byte j of the packed int8 words by q
