@@ -350,11 +350,11 @@ __device__ __forceinline__ uint32_t requant_i8_step(const uint32_t (&r)[GEMM_CW]
       const float2 bb = h ? make_float2(b4.z, b4.w) : make_float2(b4.x, b4.y);
       float2 g = f2fma(a, ss, bb);  // one rounding instead of zen_det_dequant's three
       if constexpr (ACT == ZEN_ACT_GELU) {
-        // gelu_fast on both halves: x / (1 + 2^(v * c)), v = x (1 + 0.044715 x^2)
+        // gelu_fast on both halves: x / (1 + 2^(x (c + 0.044715 c x^2))), c = -2 * 0.79788456 * log2(e) folded into
+        // the polynomial's coefficients
         const float2 x2 = f2mul(g, g);
-        const float2 wv = f2fma(make_float2(0.044715f, 0.044715f), x2, make_float2(1.0f, 1.0f));
-        const float2 v = f2mul(g, wv);
-        const float2 arg = f2mul(v, make_float2(-2.302208198144325f, -2.302208198144325f));
+        const float2 wv = f2fma(make_float2(-0.10294324f, -0.10294324f), x2, make_float2(-2.3022082f, -2.3022082f));
+        const float2 arg = f2mul(g, wv);
         const float2 den = f2add(make_float2(1.0f, 1.0f), make_float2(ex2_approx(arg.x), ex2_approx(arg.y)));
         g = f2mul(g, make_float2(rcp_approx(den.x), rcp_approx(den.y)));
       }
