@@ -294,6 +294,14 @@ int zen_qkv_attention_i8(const int8_t* xq, int64_t ldx, const int8_t* wqkv, int6
  *   valid row's result equals, bit for bit, the padded call's result for that token.
  * zen_unpad_rows_f16: padded[b * S + s] = packed[cu_seqlens[b] + s] for valid positions, zeros for padding.
  * No counterpart in the reference (its roadmap lists variable-length batching as future work). */
+/* zen_flash_attention_unpadded_f16: zen_flash_attention_f16 on packed tensors: token t of Q sits at q + t*q_st + h*q_sh + d
+ * (likewise K, V, O), sequence b owns tokens cu_seqlens[b] .. cu_seqlens[b + 1] - 1 (cut at `rows`; at most max_seqlen
+ * each: a longer one is cut to its first max_seqlen tokens), causal counts positions within the sequence.  Any
+ * sequence length; rows that belong to no sequence are left unwritten. */
+int zen_flash_attention_unpadded_f16(const void* q, const void* k, const void* v, void* o, int8_t* oq, float o_scale, int B,
+                                     int H, int max_seqlen, int D, int64_t rows, int64_t q_st, int64_t q_sh, int64_t k_st,
+                                     int64_t k_sh, int64_t v_st, int64_t v_sh, int64_t o_st, int64_t o_sh,
+                                     const int32_t* cu_seqlens, int causal, float scale, void* stream);
 int zen_pack_tokens_i32(const int32_t* ids, const int32_t* type_ids, const int32_t* kv_lens, int B, int S, int capacity,
                         int32_t* cu_seqlens, int32_t* ids_packed, int32_t* pos_packed, int32_t* type_packed, void* stream);
 int zen_embed_layernorm_unpadded_f16(const int32_t* ids_packed, const int32_t* pos_packed, const int32_t* type_packed,

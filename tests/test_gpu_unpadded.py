@@ -201,3 +201,45 @@ def test_unpadded_encoder_equals_padded_on_valid_tokens(cuda, cfg, B, S):
         assert torch.equal(rep[rows2], ref[rows2])
     # and the padded form is still there afterwards
     assert torch.equal(enc.forward(ids, lens), padded)
+
+
+@pytest.mark.parametrize("heads,D,lens,causal", [
+    (2, 64, [300, 128, 1, 257], False), (2, 64, [300, 128, 1, 257], True), (1, 128, [384, 200], False),
+    (3, 64, [100, 0, 64], False), (1, 128, [513], True), (4, 64, [40, 39, 16, 15, 1], False)])
+def test_packed_long_sequence_attention(cuda, heads, D, lens, causal):
+    """zen_flash_attention_unpadded_f16: sequences of any length back to back; every row against the fp32 oracle, and for
+    sequences longer than one key block bit-equal to the padded call (the same kernel on the same rows)."""
+    H = heads * D
+    S = max(max(lens), 1)
+    B = len(lens)
+    r = rng(sum(lens) + D)
+    qkv_pad = (r.standard_normal((B, S, 3 * H)) * 0.7).astype(np.float16)
+    rows = np.concatenate([b * S + np.arange(n) for b, n in enumerate(lens)]).astype(np.int64)
+    total = len(rows)
+    packed = np.zeros((total + 5, 3 * H), np.float16)
+    packed[:total] = qkv_pad.reshape(B * S, 3 * H)[rows]
+    packed[total:] = 3.0
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    ctx, ctxq = ops.flash_attention_unpadded(dev(packed, cuda), dev(cu, cuda), heads, D, S, causal=causal, out_scale=0.02)
+    assert _capi.device_status() == 0
+    got = ctx.float().cpu().numpy()
+    assert not got[total:].any() and not ctxq[total:].any()
+    f = packed.astype(np.float32)
+    for b in range(B):
+        r0, r1 = cu[b], cu[b + 1]
+        if r1 == r0:
+            continue
+        split = lambda t: t[r0:r1].reshape(r1 - r0, heads, D).transpose(1, 0, 2)[None]
+        want = O.attention(split(f[:, :H]), split(f[:, H:2 * H]), split(f[:, 2 * H:]), causal=causal)[0]  # [heads, n, D]
+        g = got[r0:r1].reshape(r1 - r0, heads, D).transpose(1, 0, 2)
+        assert np.max(np.abs(g - want)) <= 1e-2 * max(1.0, np.abs(want).max())
+    # the int8 copy is the quantization of the fp16 rows beside it
+    assert np.array_equal(ctxq[:total].cpu().numpy(), O.quantize(got[:total], 0.02))
+    if S > 128:
+        # the padded call runs the same kernel: valid rows carry the same bits
+        qp = dev(qkv_pad.reshape(B * S, 3 * H), cuda)
+        out = torch.empty((B * S, H), dtype=torch.float16, device=cuda)
+        st = (S * 3 * H, D, 3 * H)
+        ops.flash_attention_strided(qp, qp[:, H:], qp[:, 2 * H:], out, B, heads, S, D, st, st, st, (S * H, D, H),
+                                    kv_lens=dev(np.array(lens, np.int32), cuda), causal=causal)
+        assert torch.equal(ctx[:total], out[torch.from_numpy(rows).to(cuda)])

@@ -77,6 +77,8 @@ SIGNATURES = {
     "zen_linear_f8": [_p, _i64, _p, _i64, _i, _i, _i, _f, _p, _p, _i, _i, _p, _i64, _u, _p],
     "zen_quantize_e4m3_f32": [_p, _p, _i64, _f, _p],
     "zen_quantize_e4m3_f16": [_p, _p, _i64, _f, _p],
+    "zen_flash_attention_unpadded_f16": [_p, _p, _p, _p, _p, _f, _i, _i, _i, _i, _i64, _i64, _i64, _i64, _i64, _i64, _i64,
+                                         _i64, _i64, _p, _i, _f, _p],
     "zen_pack_tokens_i32": [_p, _p, _p, _i, _i, _i, _p, _p, _p, _p, _p],
     "zen_embed_layernorm_unpadded_f16": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _f, _i, _i, _i, _i, _i, _f, _p],
     "zen_qkv_attention_unpadded_i8": [_p, _i64, _p, _i64, _i, _i64, _p, _i, _i, _f, _p, _p, _f, _p, _p, _f, _p, _p,

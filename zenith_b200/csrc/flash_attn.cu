@@ -31,6 +31,8 @@ struct FaParams {
   int B, H, S;
   int64_t o_sb, o_sh, o_ss;
   const int32_t* kv_lens;
+  const int32_t* cu_seqlens;  // unpadded batches (long-sequence kernel only): [B + 1] row offsets, null otherwise
+  int rows;                   // ... rows of the packed tensors
   int causal;
   float scale_log2;  // softmax scale * log2(e)
   // position of the (seq, head, batch) coordinates in each rank-4 tensor map (dim 0 is d)
@@ -449,6 +451,33 @@ extern "C" int zen_flash_attention_f16(const void* q, const void* k, const void*
   if (st != ZEN_OK) return st;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (S <= FA_BKV) return D == 64 ? launch_fa<64>(tq, tk, tv, p, s) : launch_fa<128>(tq, tk, tv, p, s);
+  return D == 64 ? launch_fa_pipe<64, 2>(tq, tk, tv, p, s) : launch_fa_pipe<128, 1>(tq, tk, tv, p, s);
+}
+
+extern "C" int zen_flash_attention_unpadded_f16(const void* q, const void* k, const void* v, void* o, int8_t* oq, float o_scale,
+                                                int B, int H, int max_seqlen, int D, int64_t rows, int64_t q_st, int64_t q_sh,
+                                                int64_t k_st, int64_t k_sh, int64_t v_st, int64_t v_sh, int64_t o_st,
+                                                int64_t o_sh, const int32_t* cu_seqlens, int causal, float scale,
+                                                void* stream) {
+  if (!q || !k || !v || !o || !cu_seqlens || B <= 0 || H <= 0 || max_seqlen <= 0 || rows <= 0) return ZEN_ERR_INVALID_ARG;
+  if (D != 64 && D != 128) return ZEN_ERR_UNSUPPORTED;
+  if (H > 65535 || B > 65535 || rows >= (int64_t(1) << 31)) return ZEN_ERR_UNSUPPORTED;
+  if (oq && !(o_scale > 0.f)) return ZEN_ERR_INVALID_ARG;
+  if (reinterpret_cast<uintptr_t>(o) % 16 || o_sh % 8 || o_st % 8) return ZEN_ERR_UNSUPPORTED;
+  if (oq && (reinterpret_cast<uintptr_t>(oq) % 16 || o_sh % 16 || o_st % 16)) return ZEN_ERR_UNSUPPORTED;
+  FaParams p{};
+  p.o = o; p.oq = oq; p.o_scale = o_scale; p.B = B; p.H = H; p.S = max_seqlen;
+  p.o_sb = 0; p.o_sh = o_sh; p.o_ss = o_st; p.kv_lens = nullptr; p.cu_seqlens = cu_seqlens; p.rows = int(rows);
+  p.causal = causal ? 1 : 0;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  // the packed tensors as ONE batch of `rows` tokens: a tile may start at any row
+  CUtensorMap tq, tk, tv;
+  const int R = int(rows);
+  int st = encode_qkv_map(&tq, q, 1, H, R, D, int64_t(R) * q_st, q_sh, q_st, p.q_perm);
+  if (st == ZEN_OK) st = encode_qkv_map(&tk, k, 1, H, R, D, int64_t(R) * k_st, k_sh, k_st, p.k_perm);
+  if (st == ZEN_OK) st = encode_qkv_map(&tv, v, 1, H, R, D, int64_t(R) * v_st, v_sh, v_st, p.v_perm);
+  if (st != ZEN_OK) return st;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
   return D == 64 ? launch_fa_pipe<64, 2>(tq, tk, tv, p, s) : launch_fa_pipe<128, 1>(tq, tk, tv, p, s);
 }
 

@@ -113,14 +113,27 @@ flash_attn_pipe_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
   if constexpr (kAttentionLaunchesEarly) {
     if (p.kv_lens) kv_len = p.kv_lens[b];
   }
+  // Unpadded batches: the sequences lie back to back in one [rows, ...] tensor, sequence b in rows cu_seqlens[b] ..
+  // cu_seqlens[b + 1] - 1 (cut at the tensor's rows).  A tile then starts at the sequence's first row and may run on
+  // into the next sequence's rows: as keys they lie beyond the key length and are masked like padding, as queries
+  // their rows are not stored.  The tensor maps see one batch of `rows` tokens.
+  int row_base = 0;  // first row of this sequence in the packed tensors
+  int tma_b = b;
+  if (p.cu_seqlens != nullptr) {
+    const int lo = p.cu_seqlens[b], hi = p.cu_seqlens[b + 1];
+    kv_len = lo < 0 ? 0 : (hi < p.rows ? hi : p.rows) - lo;
+    row_base = lo < 0 ? 0 : lo;
+    tma_b = 0;
+  }
   kv_len = kv_len < 0 ? 0 : (kv_len > p.S ? p.S : kv_len);
+  const int q_len = p.cu_seqlens != nullptr ? kv_len : p.S;  // query rows of this sequence
   // key blocks needed by each group (group B has no rows if the sequence ends before its tile)
   int nblk[2];
 #pragma unroll
   for (int g = 0; g < 2; ++g) {
     int end = kv_len;
     if (p.causal && q0 + g * 128 + 128 < end) end = q0 + g * 128 + 128;
-    nblk[g] = (q0 + g * 128 < p.S) ? (end + 127) / 128 : 0;
+    nblk[g] = (q0 + g * 128 < q_len) ? (end + 127) / 128 : 0;
   }
   const int n_blocks = nblk[0] > nblk[1] ? nblk[0] : nblk[1];
 
@@ -133,7 +146,7 @@ flash_attn_pipe_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       for (int g = 0; g < 2; ++g)
 #pragma unroll
         for (int dc = 0; dc < DC; ++dc)
-          fa_tma_tile(sQ + g * TILE_BYTES + dc * CHUNK_BYTES, &tmap_q, q_full, p.q_perm, dc * 64, q0 + g * 128, h, b);
+          fa_tma_tile(sQ + g * TILE_BYTES + dc * CHUNK_BYTES, &tmap_q, q_full, p.q_perm, dc * 64, row_base + q0 + g * 128, h, tma_b);
       for (int j = 0; j < n_blocks && ok; ++j) {
         const int st = j % KV_STAGES;
         const uint32_t ph = (j / KV_STAGES) & 1;
@@ -141,12 +154,12 @@ flash_attn_pipe_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         mbar_arrive_expect_tx(&k_full[st], TILE_BYTES);
 #pragma unroll
         for (int dc = 0; dc < DC; ++dc)
-          fa_tma_tile(sK + st * TILE_BYTES + dc * CHUNK_BYTES, &tmap_k, &k_full[st], p.k_perm, dc * 64, j * 128, h, b);
+          fa_tma_tile(sK + st * TILE_BYTES + dc * CHUNK_BYTES, &tmap_k, &k_full[st], p.k_perm, dc * 64, row_base + j * 128, h, tma_b);
         if (!mbar_wait(&v_empty[st], ph ^ 1u, abort_flag)) { ok = false; break; }
         mbar_arrive_expect_tx(&v_full[st], TILE_BYTES);
 #pragma unroll
         for (int dc = 0; dc < DC; ++dc)
-          fa_tma_tile(sV + st * TILE_BYTES + dc * CHUNK_BYTES, &tmap_v, &v_full[st], p.v_perm, dc * 64, j * 128, h, b);
+          fa_tma_tile(sV + st * TILE_BYTES + dc * CHUNK_BYTES, &tmap_v, &v_full[st], p.v_perm, dc * 64, row_base + j * 128, h, tma_b);
       }
       if (!ok) {
         for (int i = 0; i < 1000; ++i) __nanosleep(1000);
@@ -354,9 +367,10 @@ flash_attn_pipe_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     }
     if (ok) {
       // every lane takes part in the TMEM loads; only rows inside the sequence are stored
-      const bool row_ok = q < p.S;
+      const bool row_ok = q < q_len;
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      const int64_t off = int64_t(b) * p.o_sb + int64_t(h) * p.o_sh + int64_t(q) * p.o_ss;
+      const int64_t off = p.cu_seqlens != nullptr ? int64_t(h) * p.o_sh + (int64_t(row_base) + q) * p.o_ss
+                                                    : int64_t(b) * p.o_sb + int64_t(h) * p.o_sh + int64_t(q) * p.o_ss;
       __half* orow = static_cast<__half*>(p.o) + off;
       const float inv_o_scale = p.oq ? ZEN_DIV(1.0f, p.o_scale) : 1.0f;
 #pragma unroll 1

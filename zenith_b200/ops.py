@@ -683,3 +683,26 @@ def linear_fp8(xq, wq, x_scale: float, w_scale=None, bias=None, *, act="none", o
           _ptr(bias), _ACT[act], _OUT[out_dtype], out.data_ptr(), out.stride(0),
           (_capi.GEMM_CONST_WEIGHTS if constant_weights else 0) | _capi.gemm_tile_n(tile_n), _stream())
     return out
+
+
+def flash_attention_unpadded(qkv, cu_seqlens, heads: int, head_dim: int, max_seqlen: int, *, causal: bool = False,
+                             scale: float | None = None, out_scale: float | None = None):
+    """Attention on packed rows (``zen_flash_attention_unpadded_f16``): ``qkv`` fp16 ``[rows, 3 * heads * head_dim]``
+    (columns Q | K | V, each head's columns together), sequence b in rows ``cu_seqlens[b] .. cu_seqlens[b+1]-1`` (any
+    length up to ``max_seqlen``).  Returns the context ``[rows, heads * head_dim]`` (rows of no sequence stay zero),
+    and with ``out_scale`` its int8 copy."""
+    _require(qkv, "qkv", torch.float16, 2)
+    _require(cu_seqlens, "cu_seqlens", torch.int32, 1)
+    hidden = heads * head_dim
+    rows = qkv.shape[0]
+    if qkv.shape[1] != 3 * hidden:
+        raise RuntimeError("qkv must be [rows, 3 * heads * head_dim]")
+    ctx = torch.zeros((rows, hidden), dtype=torch.float16, device=qkv.device)
+    ctxq = torch.zeros((rows, hidden), dtype=torch.int8, device=qkv.device) if out_scale is not None else None
+    B = cu_seqlens.numel() - 1
+    e = qkv.element_size()
+    _call("zen_flash_attention_unpadded_f16", qkv.data_ptr(), qkv.data_ptr() + hidden * e, qkv.data_ptr() + 2 * hidden * e,
+          ctx.data_ptr(), _ptr(ctxq), float(out_scale or 1.0), B, heads, int(max_seqlen), head_dim, rows, 3 * hidden, head_dim,
+          3 * hidden, head_dim, 3 * hidden, head_dim, hidden, head_dim, cu_seqlens.data_ptr(), 1 if causal else 0,
+          float(1.0 / math.sqrt(head_dim) if scale is None else scale), _stream())
+    return ctx if ctxq is None else (ctx, ctxq)
