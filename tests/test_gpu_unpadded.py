@@ -243,3 +243,47 @@ def test_packed_long_sequence_attention(cuda, heads, D, lens, causal):
         ops.flash_attention_strided(qp, qp[:, H:], qp[:, 2 * H:], out, B, heads, S, D, st, st, st, (S * H, D, H),
                                     kv_lens=dev(np.array(lens, np.int32), cuda), causal=causal)
         assert torch.equal(ctx[:total], out[torch.from_numpy(rows).to(cuda)])
+
+
+@pytest.mark.parametrize("kind,S,exact", [("int8", 160, True), ("fp16", 160, True), ("fp16", 96, False)])
+def test_unpadded_encoders_beyond_the_fused_kernel(cuda, kind, S, exact):
+    """Sequences longer than one key block (W8A8 and fp16 encoders) and the fp16 encoder at any length run the
+    projection as a GEMM on the packed rows and attention from the offsets.  Longer than 128 tokens the padded pass
+    runs the same kernels on the same rows (same bits); at 96 tokens its attention kernel is another one (tolerance)."""
+    from zenith_b200.encoder import Fp16Encoder
+    cfg = EncoderConfig(layers=2, hidden=256, heads=4, ffn=512, vocab=2000, max_pos=256)
+    params = init_params(cfg, 5, random_affine=True)
+    r = rng(77)
+    B = 6
+    mk = lambda: (torch.from_numpy(r.integers(0, cfg.vocab, (B, S))).to(cuda),
+                  torch.from_numpy((S - r.integers(0, S // 2, B)).astype(np.int32)).to(cuda))
+    if kind == "int8":
+        scales = calibrate(cfg, params, [mk() for _ in range(2)], cuda)
+        enc, ref = Int8Encoder(cfg, params, scales, cuda), Int8Encoder(cfg, params, scales, cuda)
+    else:
+        enc, ref = Fp16Encoder(cfg, params, cuda), Fp16Encoder(cfg, params, cuda)
+    ids, lens = mk()
+    lens[1] = 1
+    want = ref.forward(ids, lens).clone()
+    got = enc.forward_unpadded(ids, lens).clone()
+    assert _capi.device_status() == 0
+    rows = torch.from_numpy(valid_rows(lens.tolist(), S)).to(cuda)
+    if exact:
+        assert torch.equal(got[rows], want[rows])
+    else:
+        assert float((got[rows].float() - want[rows].float()).abs().max()) < 3e-2
+    mask = torch.ones(B * S, dtype=torch.bool, device=cuda)
+    mask[rows] = False
+    assert not got[mask].any()
+    # as a graph, fed with another batch
+    enc.capture_unpadded(B, S, enc._packed_rows)
+    ids2, lens2 = mk()
+    lens2 = torch.clamp(lens2 - 9, min=1)
+    enc.set_inputs(ids2, lens2)
+    rep = enc.replay().clone()
+    want2 = ref.forward(ids2, lens2)
+    rows2 = torch.from_numpy(valid_rows(lens2.tolist(), S)).to(cuda)
+    if exact:
+        assert torch.equal(rep[rows2], want2[rows2])
+    else:
+        assert float((rep[rows2].float() - want2[rows2].float()).abs().max()) < 3e-2

@@ -93,7 +93,6 @@ def _dev(a, dtype, device):
 class _EncoderBase:
     """Shared plumbing: embedding tables, per-shape buffers, the launch list, CUDA-graph capture."""
 
-    supports_unpadded = False
 
     def __init__(self, cfg: EncoderConfig, params: dict, device, micro_batches: int = 1, gemm_pair: bool | None = None):
         """``gemm_pair``: force the plain GEMMs onto the CTA-pair kernel (True) or the one-CTA kernel (False);
@@ -123,8 +122,6 @@ class _EncoderBase:
         if S > self.cfg.max_pos:
             raise RuntimeError("sequence longer than the position table")
         if packed_rows is not None:
-            if not self.supports_unpadded:
-                raise RuntimeError("unpadded batches are implemented for the W8A8 encoder only")
             if self.micro_batches != 1:
                 raise RuntimeError("unpadded batches need micro_batches == 1")
             if packed_rows <= 0 or packed_rows > B * S:
@@ -323,8 +320,10 @@ class Fp16Encoder(_EncoderBase):
 
     def _alloc(self, B: int, S: int) -> None:
         cfg, d = self.cfg, self.device
-        T, H, F = B * S, cfg.hidden, cfg.ffn
+        T, H, F = self._packed_rows or B * S, cfg.hidden, cfg.ffn
         f16 = dict(dtype=torch.float16, device=d)
+        if self._packed_rows is not None:
+            self.out_padded = torch.empty((B * S, H), **f16)
         self.x = [torch.empty((T, H), **f16) for _ in range(2)]
         self.qkv = torch.empty((T, 3 * H), **f16)
         self.ctx = torch.empty((T, H), **f16)
@@ -337,16 +336,25 @@ class Fp16Encoder(_EncoderBase):
     def _build(self, b0: int, B: int, S: int) -> None:
         """Launch list for sequences [b0, b0 + B) of the batch (rows b0*S .. of every buffer)."""
         cfg = self.cfg
-        T, H, F, nh, hd = B * S, cfg.hidden, cfg.ffn, cfg.heads, cfg.head_dim
+        packed = self._packed_rows is not None
+        T, H, F, nh, hd = self._packed_rows or B * S, cfg.hidden, cfg.ffn, cfg.heads, cfg.head_dim
         r0 = b0 * S
         P = lambda t: _row_ptr(t, r0)
         # the weights of this object are written once, in __init__: every GEMM of the launch list carries the
         # constant-weights promise for its own call (nothing process-wide is switched)
         CW = GEMM_CONST_WEIGHTS
         GF = self.gemm_flags  # the plain GEMMs also carry the kernel choice
-        self._add("zen_embed_layernorm_f16", P(self.ids), None, self.word.data_ptr(), self.pos.data_ptr(),
-                  self.type.data_ptr(), self.emb_g.data_ptr(), self.emb_b.data_ptr(), P(self.x[0]), None, 1.0,
-                  ROUND_NEAREST_EVEN, T, S, H, cfg.vocab, cfg.eps)
+        self.lead_launches = 2 if packed else 1
+        if packed:
+            self._add("zen_pack_tokens_i32", self.ids.data_ptr(), None, self.kv_lens.data_ptr(), B, S, T,
+                      self.cu_seqlens.data_ptr(), self.ids_packed.data_ptr(), self.pos_packed.data_ptr(), None)
+            self._add("zen_embed_layernorm_unpadded_f16", self.ids_packed.data_ptr(), self.pos_packed.data_ptr(), None,
+                      self.word.data_ptr(), self.pos.data_ptr(), self.type.data_ptr(), self.emb_g.data_ptr(),
+                      self.emb_b.data_ptr(), P(self.x[0]), None, 1.0, ROUND_NEAREST_EVEN, T, cfg.max_pos, H, cfg.vocab, cfg.eps)
+        else:
+            self._add("zen_embed_layernorm_f16", P(self.ids), None, self.word.data_ptr(), self.pos.data_ptr(),
+                      self.type.data_ptr(), self.emb_g.data_ptr(), self.emb_b.data_ptr(), P(self.x[0]), None, 1.0,
+                      ROUND_NEAREST_EVEN, T, S, H, cfg.vocab, cfg.eps)
         qs = (S * 3 * H, hd, 3 * H)
         os_ = (S * H, hd, H)
         kv = self.kv_lens.data_ptr() + 4 * b0
@@ -355,8 +363,13 @@ class Fp16Encoder(_EncoderBase):
             x, xn = self.x[cur], self.x[cur ^ 1]
             self._add("zen_linear_f16_ex", P(x), H, L["wqkv"].data_ptr(), H, T, 3 * H, H, L["bqkv"].data_ptr(),
                       ACT_NONE, DT_F16, P(self.qkv), 3 * H, GF)
-            self._add("zen_flash_attention_f16", P(self.qkv), P(self.qkv) + 2 * H, P(self.qkv) + 4 * H, P(self.ctx), None,
-                      1.0, B, nh, S, hd, *qs, *qs, *qs, *os_, kv, 0, 1.0 / math.sqrt(hd))
+            if packed:
+                self._add("zen_flash_attention_unpadded_f16", P(self.qkv), P(self.qkv) + 2 * H, P(self.qkv) + 4 * H,
+                          P(self.ctx), None, 1.0, B, nh, S, hd, T, 3 * H, hd, 3 * H, hd, 3 * H, hd, H, hd,
+                          self.cu_seqlens.data_ptr(), 0, 1.0 / math.sqrt(hd))
+            else:
+                self._add("zen_flash_attention_f16", P(self.qkv), P(self.qkv) + 2 * H, P(self.qkv) + 4 * H, P(self.ctx), None,
+                          1.0, B, nh, S, hd, *qs, *qs, *qs, *os_, kv, 0, 1.0 / math.sqrt(hd))
             if self.fuse_layernorm:
                 self._add("zen_linear_f16_add_layernorm_ex", P(self.ctx), H, L["wo"].data_ptr(), H, T, H, H,
                           L["bo"].data_ptr(), P(x), H, L["ln1_g"].data_ptr(), L["ln1_b"].data_ptr(), cfg.eps, P(self.h1),
@@ -378,6 +391,9 @@ class Fp16Encoder(_EncoderBase):
                 self._add("zen_add_layernorm_f16", P(self.o), P(self.h1), L["ln2_g"].data_ptr(), L["ln2_b"].data_ptr(),
                           P(xn), None, 1.0, ROUND_NEAREST_EVEN, T, H, cfg.eps)
             cur ^= 1
+        if packed:
+            self._add("zen_unpad_rows_f16", self.x[cur].data_ptr(), self.cu_seqlens.data_ptr(), B, S, H, T,
+                      self.out_padded.data_ptr())
 
     def forward_with_taps(self, ids, kv_lens=None, observers: dict | None = None) -> dict | None:
         """One pass that also observes, per layer, the range of the four tensors that feed a GEMM in the
@@ -386,7 +402,8 @@ class Fp16Encoder(_EncoderBase):
         ``observers``: ``{point: [ops.RangeObserver per layer]}``; the ranges then accumulate on the device
         over any number of passes and nothing is read back here (returns None).  Without it the pass
         creates fresh observers and returns ``{point: [(min, max) per layer]}`` of this batch alone.
-        Cold path used by calibration: runs layer by layer."""
+        Cold path used by calibration: runs layer by layer (padded form)."""
+        self._prepare(*ids.shape, None)
         self.set_inputs(ids, kv_lens)
         if len(self._micro) != 1:
             raise RuntimeError("forward_with_taps needs micro_batches == 1")
@@ -449,7 +466,6 @@ class Int8Scales:
 class Int8Encoder(_EncoderBase):
     """W8A8 encoder: int8 GEMM operands, int32 accumulation, fp16 residual stream / LayerNorm / softmax."""
 
-    supports_unpadded = True
 
     def __init__(self, cfg: EncoderConfig, params: dict, scales: Int8Scales, device="cuda:0", micro_batches: int = 1,
                  fuse_layernorm: bool | None = None, prefetch_weights: bool = True, gemm_pair: bool | None = None,
@@ -516,11 +532,9 @@ class Int8Encoder(_EncoderBase):
         GF = self.gemm_flags  # the plain GEMMs also carry the kernel choice
         sc = self.act_scales
         can_fuse = S <= 128 and hd == 64
-        if (self.fuse_attention or packed) and not can_fuse:
+        if self.fuse_attention and not can_fuse:
             raise RuntimeError("the fused QKV + attention kernel needs seq <= 128 and head_dim == 64")
         fused_attn = can_fuse if self.fuse_attention is None else bool(self.fuse_attention)
-        if packed and not fused_attn:
-            raise RuntimeError("unpadded batches run through the fused QKV + attention kernel")
         self.launches_per_layer = (5 if self.fuse_layernorm else 7) - (1 if fused_attn else 0)
         self.lead_launches = 2 if packed else 1
         if packed:
@@ -546,7 +560,15 @@ class Int8Encoder(_EncoderBase):
             nbytes = lambda t: t.numel() * t.element_size()
             pf = lambda *ts: [v for t in ts for v in ((t.data_ptr(), nbytes(t)) if self.prefetch_weights and t is not None
                                                        else (None, 0))]
-            if packed:
+            if packed and not fused_attn:
+                # longer sequences (or head size 128): projection, then attention on the packed rows from the offsets
+                self._add("zen_linear_i8_ex", P(xq), H, L["wqkv"].data_ptr(), H, T, 3 * H, H, a["x"],
+                          L["wqkv_s"].data_ptr(), L["bqkv"].data_ptr(), ACT_NONE, DT_F16, 1.0, ROUND_NEAREST_EVEN,
+                          P(self.qkv), 3 * H, *pf(L["wo"], L["w1"]), GF)
+                self._add("zen_flash_attention_unpadded_f16", P(self.qkv), P(self.qkv) + 2 * H, P(self.qkv) + 4 * H,
+                          P(self.ctx), P(self.ctxq), a["ctx"], B, nh, S, hd, T, 3 * H, hd, 3 * H, hd, 3 * H, hd, H, hd,
+                          self.cu_seqlens.data_ptr(), 0, 1.0 / math.sqrt(hd))
+            elif packed:
                 self._add("zen_qkv_attention_unpadded_i8", P(xq), H, L["wqkv"].data_ptr(), H, B, T,
                           self.cu_seqlens.data_ptr(), nh, H, a["x"], L["wqkv_s"].data_ptr(), L["bqkv"].data_ptr(),
                           1.0 / math.sqrt(hd), P(self.ctx), P(self.ctxq), a["ctx"], P(self.qkv) if self.keep_qkv else None,
