@@ -479,6 +479,16 @@ def secondary_metrics(torch, ops, dev, flush, peaks, cfg_base, params_base) -> d
     out["bert_large_int8_seq384_shard32"] = {"ms_per_step": round(us / 1e3, 3), "sequences_per_s": round(32 / us * 1e6, 1),
                                              "launches": enc.launches_per_forward,
                                              "workload": "BASELINE.json configs[4], the 32-sequence shard one of 8 GPUs holds"}
+    try:  # the same shard unpadded (projection GEMM on the packed rows, attention from the offsets)
+        enc.capture_unpadded(32, LARGE_SEQ, Int8Encoder.unpadded_capacity(lens.tolist(), LARGE_SEQ))
+        enc.set_inputs(torch.from_numpy(ids).to(dev), torch.from_numpy(lens).to(dev))
+        for _ in range(3):
+            enc.replay()
+        us_u = _event_us(torch, enc.replay, 9, flush)
+        out["bert_large_int8_seq384_shard32"].update({"unpadded_ms_per_step": round(us_u / 1e3, 3),
+                                                      "valid_tokens": int(lens.sum()), "padded_tokens": int(ids.size)})
+    except Exception as exc:
+        out["bert_large_int8_seq384_shard32"]["unpadded_error"] = str(exc)
     return out
 
 
