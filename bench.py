@@ -251,9 +251,11 @@ def run_reference_arm(args) -> None:
     if rank != 0:
         return
     wl = workload_of(args, 1)
-    # one step = the same batch a GPU gets in a step of the other arm (32 sequences; BERT-large: a 4-sequence sample
-    # of its 256, a pass over all of them takes minutes on host cores)
-    sample = BATCH if not wl["large"] else 4
+    # One step = the batch a GPU gets in a step of the other arm (32 sequences; BERT-large: a 4-sequence sample of
+    # its 256), as long as K such steps fit a few minutes of host time (about 2 sequences/s for BERT-base, 0.2 for
+    # BERT-large on these cores); beyond that the per-step sample shrinks so that the whole run stays bounded.
+    full, budget = (BATCH, 320) if not wl["large"] else (4, 36)
+    sample = max(1, min(full, budget // max(1, args.steps)))
     r = cpu_executor(sample, max(1, args.steps), 1 if args.warmup > 0 else 0, large=wl["large"])
     line = {
         "impl": "reference", "metric": wl["metric"], "value": r["seq_per_s"], "unit": "sequences/s", "n_gpus": args.gpus,
